@@ -1,0 +1,186 @@
+/*
+ * b200lmk.h — C ABI of libb200lmk.so: landmark attention kernels for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer owned by the caller unless stated otherwise; the library
+ *     never allocates or frees device memory and keeps no state between calls (except a per-thread
+ *     error string).
+ *   - Tensors are row-major with a contiguous last dimension.  q/k/v take explicit element strides
+ *     {batch, head, row}; all other tensors are dense in the documented shape.
+ *   - dtype: LMK_F32, LMK_F16 or LMK_BF16 (all of q, k, v, o, dO, dQ, dK, dV share it).
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *   - Return value: LMK_OK (0) or a negative LMK_ERR_* code.  Nothing is launched when an argument
+ *     check fails.  lmk_last_error() returns a description of the calling thread's last failure.
+ *
+ * Each entry point names the interface of epfml/landmark-attention it replaces (file:line relative to
+ * that project's root).
+ */
+#ifndef B200LMK_H
+#define B200LMK_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LMK_VERSION 100
+
+enum { LMK_F32 = 0, LMK_F16 = 1, LMK_BF16 = 2 };
+
+enum {
+  LMK_OK = 0,
+  LMK_ERR_INVALID = -1,     /* bad shape / pointer / flag (the reference raises AssertionError / ValueError) */
+  LMK_ERR_UNSUPPORTED = -2, /* valid request that no kernel in this build covers */
+  LMK_ERR_CUDA = -3,        /* a CUDA runtime or driver call failed */
+  LMK_ERR_WORKSPACE = -4,   /* workspace missing or too small */
+  LMK_ERR_DEVICE = -5       /* a kernel reported a device-side error (bounded wait expired) */
+};
+
+/* Kernel family selection for the fused attention entry points. */
+enum {
+  LMK_PATH_AUTO = 0,    /* tcgen05 path when the shape qualifies, otherwise the general path */
+  LMK_PATH_GENERAL = 1, /* CUDA-core fp32-accumulate kernels: any dtype, D <= 128, block <= 128 */
+  LMK_PATH_TCGEN05 = 2  /* TMA + tcgen05/TMEM kernels: bf16/fp16, D == 128, block == 64, full 128-row tiles */
+};
+
+int lmk_version(void);
+const char* lmk_last_error(void);
+
+/* 1 if the (shape, dtype) is handled by the tcgen05 kernels, else 0. */
+int lmk_attn_tcgen05_supported(int B, int H, int Lq, int Lk, int D, int block, int dtype);
+
+/*
+ * Fused landmark attention, forward.
+ * Replaces FusedLandmarkAttention.forward + _fwd_kernel
+ *   (llama/ltriton/flash_landmark_attention.py:6-122, 311-353).
+ *   q [B,H,Lq,D], k,v [B,H,Lk,D] (strided), o [B,H,Lq,D] dense, L and M [B*H, Lq] fp32
+ *   (sum of exponentials and maximum of the outer softmax, as the reference stores them).
+ *   Landmark = last key of each `block`; (Lk-Lq) must be a multiple of block (:396-397); D <= 128 (:321).
+ */
+int lmk_attn_fwd(const void* q, const void* k, const void* v, void* o, float* L, float* M,
+                 int B, int H, int Lq, int Lk, int D,
+                 const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                 int block, float sm_scale, int dtype, int path, void* stream);
+
+/*
+ * Bytes of scratch lmk_attn_bwd needs for this problem (0 is possible).
+ * Stands for the temporaries FusedLandmarkAttention.backward allocates
+ *   (fp32 dq, do_scaled, delta: flash_landmark_attention.py:363-367).
+ */
+size_t lmk_attn_bwd_workspace(int B, int H, int Lq, int Lk, int D, int block, int dtype, int path);
+
+/*
+ * Fused landmark attention, backward (recompute based).
+ * Replaces FusedLandmarkAttention.backward + _bwd_preprocess + _bwd_kernel
+ *   (llama/ltriton/flash_landmark_attention.py:125-305, 356-389).
+ *   o, dO, dQ [B,H,Lq,D] dense; dK, dV [B,H,Lk,D] dense; L, M from the forward call.
+ *   Lq and Lk must be multiples of block (:359-360).  workspace: >= lmk_attn_bwd_workspace(...) bytes,
+ *   256-byte aligned, contents irrelevant on entry.
+ */
+int lmk_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO,
+                 const float* L, const float* M, void* dQ, void* dK, void* dV,
+                 void* workspace, size_t workspace_bytes,
+                 int B, int H, int Lq, int Lk, int D,
+                 const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                 int block, float sm_scale, int dtype, int path, void* stream);
+
+/*
+ * Stand-alone landmark grouped softmax over the last dimension of x [B,H,Lq,Lk].
+ * Replaces LandmarkGroupedSoftmaxFunction.forward + landmark_grouped_softmax
+ *   (llama/llama_mem.py:168-243; lm_benchmark/models/landmark.py:37-119).
+ *   x: dtype `dtype`, element strides x_strides {b,h,row}, last dim contiguous.
+ *   is_mem, last_section, hidden (nullable): bool bytes, broadcastable, element strides {b,h,row,col}
+ *     (0 = broadcast).  `hidden` is the lm_benchmark attn_mask argument.
+ *   probs: fp32 dense [B,H,Lq,Lk].  group_prob (nullable): fp32 dense [B,H,Lq,max_mem_cnt]
+ *     (slot g = probability of the landmark closing group g, last slot = total last-section probability).
+ *   guards != 0 selects the lm_benchmark flavour (all -inf group -> 0 instead of NaN).
+ *   max_groups: upper bound on 1 + number of landmarks in any row (<= 2048).
+ */
+int lmk_grouped_softmax_fwd(const void* x, const int64_t x_strides[3],
+                            const uint8_t* is_mem, const int64_t is_mem_strides[4],
+                            const uint8_t* last_section, const int64_t last_strides[4],
+                            const uint8_t* hidden, const int64_t hidden_strides[4],
+                            float* probs, float* group_prob, int max_mem_cnt,
+                            int B, int H, int Lq, int Lk, int dtype, int guards, int max_groups, void* stream);
+
+/*
+ * Backward of the grouped softmax: grad_x (fp32 dense [B,H,Lq,Lk]) from grad_probs (fp32 dense), recomputing
+ * the probabilities from x.  Replaces LandmarkGroupedSoftmaxFunction.backward and the autograd chain through
+ * the group-probability multiply (llama/llama_mem.py:198-220, 238-240).
+ */
+int lmk_grouped_softmax_bwd(const void* x, const int64_t x_strides[3],
+                            const uint8_t* is_mem, const int64_t is_mem_strides[4],
+                            const uint8_t* last_section, const int64_t last_strides[4],
+                            const uint8_t* hidden, const int64_t hidden_strides[4],
+                            const float* grad_probs, float* grad_x,
+                            int B, int H, int Lq, int Lk, int dtype, int guards, int max_groups, void* stream);
+
+/* Rotary conventions for the retrieval kernels. */
+enum {
+  LMK_ROTARY_NONE = 0,
+  LMK_ROTARY_HALF = 1,       /* pairs (d, d+D/2): llama/llama_mem.py:127-149 */
+  LMK_ROTARY_INTERLEAVED = 2 /* pairs (2d, 2d+1): lm_benchmark/models/positional_encoders/rotary_utils.py:17-31 */
+};
+
+/*
+ * Description of a block cache of un-rotated keys/values split in landmark blocks of `block` tokens.
+ *   strides (elements): batch, head, block, row; last dim contiguous.
+ *   n_blocks: blocks currently held; ring_start: physical index of the OLDEST block (0 unless the cache is a
+ *   ring buffer, lm_benchmark/models/caches/mem_cache.py:53-56); top_k: number of blocks to retrieve;
+ *   pos_base: position of the first key of slot 0 (llama: prefix_len, llama_mem.py:361; lm_benchmark: 0).
+ * Slot rule shared by both call sites (llama_mem.py:362-365, mem_cache.py:58-59): a block whose logical age
+ * index is among the newest top_k is scored at slot 1 + (its rank among them), every other block at slot 0;
+ * its landmark key is rotated at position pos_base + slot*block + block-1.
+ */
+typedef struct {
+  int64_t stride_b, stride_h, stride_block, stride_row;
+  int n_blocks, ring_start, block, top_k;
+  int pos_base;
+} lmk_cache_desc;
+
+/*
+ * Landmark scores: scores[b,h,t,n] = sm_scale * q[b,h,t,:] . rot(K[b,h,n,block-1,:], slot position of n).
+ * Replaces llama/llama_mem.py:357-367 and lm_benchmark/models/caches/mem_cache.py:51-61.
+ *   q [B,H,T,D] dense (already rotated), k_cache per desc, cos/sin tables [n_pos, D] in `dtype` (NULL with
+ *   LMK_ROTARY_NONE), scores fp32 dense [B,H,T,n_blocks]; softmax != 0 applies a softmax over n in fp32
+ *   (mem_cache.py:62; llama_mem.py:376 mode B) and, when dtype is 16-bit, rounds it to dtype as the reference does.
+ */
+int lmk_landmark_scores(const void* q, const void* k_cache, const lmk_cache_desc* desc,
+                        const void* cos_table, const void* sin_table, int n_pos, int rotary,
+                        float* scores, int B, int H, int T, int D, float sm_scale, int softmax,
+                        int dtype, void* stream);
+
+/*
+ * Per-row top-k with ascending index output.  Replaces `topk(...)[1].sort(...)[0]`
+ *   (llama/llama_mem.py:384; mem_cache.py:72-83).
+ *   scores: fp32, logical shape [rows, reduce, n] addressed as scores[row*row_stride + r*reduce_stride + j];
+ *   each row's value at j is the maximum over r (reduce = 1: plain rows; reduce > 1 implements the
+ *   max_over_tokens / max_over_heads aggregation, mem_cache.py:63-70).  rows are decomposed as
+ *   row = outer*inner_count + inner with offset outer*outer_stride + inner*inner_stride.
+ *   idx_out int32 [rows, k]: indices of the k largest values (ties: lower index first), sorted ascending.
+ *   With ring_start != 0 the ascending order is by logical age (physical - ring_start mod n), as
+ *   mem_cache.py:73-83 does, but physical indices are returned.
+ */
+int lmk_topk_sorted(const float* scores, int32_t* idx_out, int64_t outer_count, int64_t inner_count,
+                    int64_t outer_stride, int64_t inner_stride, int reduce, int64_t reduce_stride,
+                    int n, int k, int ring_start, void* stream);
+
+/*
+ * Gather the selected blocks and rotate the gathered keys at their slot positions.
+ * Replaces llama/llama_mem.py:386-398,408-410 and mem_cache.py:85-98.
+ *   idx int32 dense [B,H,T,top_k] (physical block indices, ascending logical age);
+ *   k_out, v_out dense [B,H,T,top_k*block,D] in `dtype` (either may be NULL to skip it);
+ *   key position of row r of the i-th selected block: pos_base + (i + recent)*block + r, recent = 1 when the
+ *   block is among the newest top_k (llama_mem.py:386-388, mem_cache.py:92-94).
+ */
+int lmk_gather_kv(const void* k_cache, const void* v_cache, const lmk_cache_desc* kdesc,
+                  const lmk_cache_desc* vdesc, const int32_t* idx,
+                  const void* cos_table, const void* sin_table, int n_pos, int rotary,
+                  void* k_out, void* v_out, int B, int H, int T, int D, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200LMK_H */

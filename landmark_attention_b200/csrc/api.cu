@@ -1,0 +1,127 @@
+// extern "C" entry points of libb200lmk.so for the fused attention kernels, plus error reporting.
+// Argument checks mirror the assertions of the reference wrapper (llama/ltriton/flash_landmark_attention.py:319-324,
+// 359-360, 396-397) and are done on the host before anything is launched.
+#include "common.cuh"
+#include "attn_params.h"
+
+namespace lmk {
+
+char* error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+namespace {
+
+int check_common(const void* q, const void* k, const void* v, int B, int H, int Lq, int Lk, int D,
+                 const int64_t* qs, const int64_t* ks, const int64_t* vs, int block, int dtype, int path) {
+  LMK_CHECK_ARG(q && k && v, "attention: q, k or v is null");
+  LMK_CHECK_ARG(qs && ks && vs, "attention: stride arrays are required");
+  LMK_CHECK_ARG(B >= 1 && H >= 1 && Lq >= 1 && Lk >= 1, "attention: empty problem (B=%d H=%d Lq=%d Lk=%d)", B, H, Lq, Lk);
+  LMK_CHECK_ARG((int64_t)B * H <= 65535, "attention: B*H = %lld exceeds 65535", (long long)B * H);
+  LMK_CHECK_ARG(D <= 128, "FlashAttention only support head dimensions up to 128 (got %d)", D);
+  LMK_CHECK_ARG(D >= 8 && D % 8 == 0, "attention: head dim %d must be a multiple of 8", D);
+  LMK_CHECK_ARG(dtype == LMK_F32 || dtype == LMK_F16 || dtype == LMK_BF16, "attention: bad dtype %d", dtype);
+  LMK_CHECK_ARG(block >= 2, "attention: block size %d must be >= 2", block);
+  LMK_CHECK_ARG(Lk >= Lq && (Lk - Lq) % block == 0,
+                "attention: key history Lk-Lq = %d must be a non-negative multiple of block %d", Lk - Lq, block);
+  LMK_CHECK_ARG(path >= LMK_PATH_AUTO && path <= LMK_PATH_TCGEN05, "attention: bad path %d", path);
+  return LMK_OK;
+}
+
+void fill(AttnParams& p, const void* q, const void* k, const void* v, int B, int H, int Lq, int Lk, int D,
+          const int64_t* qs, const int64_t* ks, const int64_t* vs, int block, float scale) {
+  p.q = q; p.k = k; p.v = v;
+  p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk; p.D = D; p.block = block; p.scale = scale;
+  for (int i = 0; i < 3; ++i) {
+    p.qs[i] = qs[i];
+    p.ks[i] = ks[i];
+    p.vs[i] = vs[i];
+  }
+}
+
+// 1 = general, 2 = tcgen05, <0 = error
+int pick_path(int path, int B, int H, int Lq, int Lk, int D, int block, int dtype) {
+  const bool fast = attn_sm100_supported(B, H, Lq, Lk, D, block, dtype);
+  if (path == LMK_PATH_TCGEN05) {
+    if (!fast)
+      return fail(LMK_ERR_UNSUPPORTED,
+                  "tcgen05 path needs bf16/fp16, D=128, block=64 and Lq, Lk multiples of 128 (got dtype=%d D=%d "
+                  "block=%d Lq=%d Lk=%d)", dtype, D, block, Lq, Lk);
+    return LMK_PATH_TCGEN05;
+  }
+  if (path == LMK_PATH_AUTO && fast) return LMK_PATH_TCGEN05;
+  if (block > 128) return fail(LMK_ERR_UNSUPPORTED, "general path supports block sizes up to 128 (got %d)", block);
+  return LMK_PATH_GENERAL;
+}
+
+}  // namespace
+}  // namespace lmk
+
+using namespace lmk;
+
+extern "C" int lmk_version(void) { return LMK_VERSION; }
+
+extern "C" const char* lmk_last_error(void) { return error_buffer(); }
+
+extern "C" int lmk_attn_tcgen05_supported(int B, int H, int Lq, int Lk, int D, int block, int dtype) {
+  return attn_sm100_supported(B, H, Lq, Lk, D, block, dtype) ? 1 : 0;
+}
+
+extern "C" int lmk_attn_fwd(const void* q, const void* k, const void* v, void* o, float* L, float* M, int B, int H,
+                            int Lq, int Lk, int D, const int64_t q_strides[3], const int64_t k_strides[3],
+                            const int64_t v_strides[3], int block, float sm_scale, int dtype, int path,
+                            void* stream) {
+  int rc = check_common(q, k, v, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, block, dtype, path);
+  if (rc != LMK_OK) return rc;
+  LMK_CHECK_ARG(o && L && M, "attn_fwd: o, L or M is null");
+  int which = pick_path(path, B, H, Lq, Lk, D, block, dtype);
+  if (which < 0) return which;
+  AttnParams p{};
+  fill(p, q, k, v, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, block, sm_scale);
+  p.o = o; p.L = L; p.M = M;
+  if (which == LMK_PATH_TCGEN05) return attn_sm100_fwd(p, dtype, (cudaStream_t)stream);
+  return attn_general_fwd(p, dtype, (cudaStream_t)stream);
+}
+
+extern "C" size_t lmk_attn_bwd_workspace(int B, int H, int Lq, int Lk, int D, int block, int dtype, int path) {
+  if (B < 1 || H < 1 || Lq < 1 || Lk < 1) return 0;
+  const bool fast = attn_sm100_supported(B, H, Lq, Lk, D, block, dtype);
+  if (path == LMK_PATH_TCGEN05 || (path == LMK_PATH_AUTO && fast)) return attn_sm100_bwd_workspace(B, H, Lq, Lk, D);
+  return attn_general_bwd_workspace(B, H, Lq);
+}
+
+extern "C" int lmk_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO,
+                            const float* L, const float* M, void* dQ, void* dK, void* dV, void* workspace,
+                            size_t workspace_bytes, int B, int H, int Lq, int Lk, int D,
+                            const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                            int block, float sm_scale, int dtype, int path, void* stream) {
+  int rc = check_common(q, k, v, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, block, dtype, path);
+  if (rc != LMK_OK) return rc;
+  LMK_CHECK_ARG(o && dO && L && M && dQ && dK && dV, "attn_bwd: null tensor pointer");
+  LMK_CHECK_ARG(Lq % block == 0 && Lk % block == 0, "Backward supported only for full blocks (Lq=%d Lk=%d block=%d)",
+                Lq, Lk, block);
+  int which = pick_path(path, B, H, Lq, Lk, D, block, dtype);
+  if (which < 0) return which;
+  const size_t need = lmk_attn_bwd_workspace(B, H, Lq, Lk, D, block, dtype, which);
+  if (need > 0 && (workspace == nullptr || workspace_bytes < need))
+    return fail(LMK_ERR_WORKSPACE, "attn_bwd: workspace of %zu bytes required, %zu given", need, workspace_bytes);
+  LMK_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "attn_bwd: workspace must be 256-byte aligned");
+  AttnParams p{};
+  fill(p, q, k, v, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, block, sm_scale);
+  p.o = const_cast<void*>(o); p.dO = dO;
+  p.L = const_cast<float*>(L); p.M = const_cast<float*>(M);
+  p.dq = dQ; p.dk = dK; p.dv = dV;
+  p.workspace = workspace; p.workspace_bytes = workspace_bytes;
+  if (which == LMK_PATH_TCGEN05) return attn_sm100_bwd(p, dtype, (cudaStream_t)stream);
+  p.delta = reinterpret_cast<float*>(workspace);
+  return attn_general_bwd(p, dtype, (cudaStream_t)stream);
+}

@@ -1,0 +1,349 @@
+// Inference-time landmark retrieval: landmark scores, per-row top-k, and the gather of the selected KV blocks.
+//
+// Reference call sites: LlamaAttention.forward cache branch (llama/llama_mem.py:357-398, 408-410) and
+// MemLMCacheStorage.retrieve_for_query (lm_benchmark/models/caches/mem_cache.py:51-98).  Both rotate cached keys at
+// "slot" positions: the newest top_k blocks occupy slots 1..top_k, every older block shares slot 0.
+#include "common.cuh"
+
+namespace lmk {
+namespace {
+
+__host__ __device__ __forceinline__ int logical_age(int phys, int ring_start, int n) {
+  int l = phys - ring_start;
+  return l < 0 ? l + n : l;
+}
+// slot of a block given its logical age index (0 = oldest)
+__host__ __device__ __forceinline__ int slot_of(int logical, int n, int top_k) {
+  int first_recent = n - top_k;
+  return logical >= first_recent ? logical - first_recent + 1 : 0;
+}
+
+// One rotary output element computed the way torch computes `x*cos + rotate_half(x)*sin` in dtype T:
+// each product and the sum are rounded to T (no fused multiply-add).
+template <typename T>
+__device__ __forceinline__ float rotary_elem(float x, float partner_signed, float c, float s) {
+  float a = to_f32(from_f32<T>(__fmul_rn(x, c)));
+  float b = to_f32(from_f32<T>(__fmul_rn(partner_signed, s)));
+  return to_f32(from_f32<T>(__fadd_rn(a, b)));
+}
+
+// ------------------------------------------------------------------------------------------- landmark scores
+constexpr int kScTile = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(128) landmark_scores_kernel(const T* __restrict__ q, const T* __restrict__ kc,
+                                                              lmk_cache_desc desc, const T* __restrict__ cos_t,
+                                                              const T* __restrict__ sin_t, int n_pos, int rotary,
+                                                              float* __restrict__ scores, int H, int Tq, int D,
+                                                              float scale) {
+  extern __shared__ __align__(16) float sc_smem[];
+  const int DP = D + 1;
+  float* Qs = sc_smem;               // [32][D]
+  float* Ks = Qs + kScTile * D;      // [32][D+1], rotated landmark keys
+  const int tid = threadIdx.x, lane = tid & 31, ty = tid >> 5;
+  const int n0 = blockIdx.x * kScTile, t0 = blockIdx.y * kScTile;
+  const int bh = blockIdx.z, b = bh / H, h = bh - b * H;
+  const int N = desc.n_blocks, blk = desc.block;
+  const T* qp = q + ((int64_t)bh * Tq) * D;
+  for (int i = tid; i < kScTile * D; i += 128) {
+    int r = i / D, d = i - r * D;
+    Qs[i] = (t0 + r < Tq) ? to_f32(qp[(int64_t)(t0 + r) * D + d]) : 0.f;
+  }
+  for (int i = tid; i < kScTile * D; i += 128) {
+    int r = i / D, d = i - r * D;
+    int n = n0 + r;
+    float val = 0.f;
+    if (n < N) {
+      const T* row = kc + b * desc.stride_b + h * desc.stride_h + (int64_t)n * desc.stride_block +
+                     (int64_t)(blk - 1) * desc.stride_row;
+      float x = to_f32(row[d]);
+      if (rotary == LMK_ROTARY_NONE) {
+        val = x;
+      } else {
+        int slot = slot_of(logical_age(n, desc.ring_start, N), N, desc.top_k);
+        int pos = desc.pos_base + slot * blk + blk - 1;
+        pos = max(0, min(pos, n_pos - 1));
+        float c = to_f32(cos_t[(int64_t)pos * D + d]), s = to_f32(sin_t[(int64_t)pos * D + d]);
+        float partner;
+        if (rotary == LMK_ROTARY_HALF) partner = d < D / 2 ? -to_f32(row[d + D / 2]) : to_f32(row[d - D / 2]);
+        else partner = (d & 1) ? to_f32(row[d - 1]) : -to_f32(row[d + 1]);
+        val = rotary_elem<T>(x, partner, c, s);
+      }
+    }
+    Ks[r * DP + d] = val;
+  }
+  __syncthreads();
+  // thread: landmark n0+lane, tokens t0 + ty*8 .. +7
+  float acc[8];
+#pragma unroll
+  for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+  const float* krow = Ks + lane * DP;
+  const float* qrows = Qs + ty * 8 * D;
+  for (int d = 0; d < D; d += 4) {
+    float k0 = krow[d], k1 = krow[d + 1], k2 = krow[d + 2], k3 = krow[d + 3];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      float4 qv = *reinterpret_cast<const float4*>(qrows + r * D + d);
+      acc[r] = fmaf(qv.x, k0, acc[r]);
+      acc[r] = fmaf(qv.y, k1, acc[r]);
+      acc[r] = fmaf(qv.z, k2, acc[r]);
+      acc[r] = fmaf(qv.w, k3, acc[r]);
+    }
+  }
+  const int n = n0 + lane;
+  if (n < N) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      int t = t0 + ty * 8 + r;
+      if (t < Tq) {
+        // 16-bit inputs: the reference's matmul output and the scaling are each rounded to the input dtype
+        float v = to_f32(from_f32<T>(acc[r]));
+        v = to_f32(from_f32<T>(v * scale));
+        scores[((int64_t)bh * Tq + t) * N + n] = v;
+      }
+    }
+  }
+}
+
+// in-place softmax over the last dim, one warp per row, result rounded to T
+template <typename T>
+__global__ void __launch_bounds__(128) row_softmax_kernel(float* __restrict__ s, int64_t rows, int n) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float* r = s + row * n;
+  float mx = -INFINITY;
+  for (int j = lane; j < n; j += 32) mx = fmaxf(mx, r[j]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int j = lane; j < n; j += 32) sum += expf(r[j] - mx);
+  sum = warp_sum(sum);
+  for (int j = lane; j < n; j += 32) r[j] = to_f32(from_f32<T>(expf(r[j] - mx) / sum));
+}
+
+// ------------------------------------------------------------------------------------------- top-k
+constexpr int kTopkMaxK = 32;
+
+__global__ void __launch_bounds__(128) topk_sorted_kernel(const float* __restrict__ scores, int32_t* __restrict__ idx,
+                                                          int64_t rows, int64_t inner_count, int64_t outer_stride,
+                                                          int64_t inner_stride, int reduce, int64_t reduce_stride,
+                                                          int n, int k, int ring_start, int warps_per_cta) {
+  extern __shared__ float tk_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row = (int64_t)blockIdx.x * warps_per_cta + warp;
+  if (warp >= warps_per_cta || row >= rows) return;
+  float* vals = tk_smem + (size_t)warp * n;
+  const int64_t outer = row / inner_count, inner = row - outer * inner_count;
+  const float* src = scores + outer * outer_stride + inner * inner_stride;
+  for (int j = lane; j < n; j += 32) {
+    float v = src[j];
+    for (int r = 1; r < reduce; ++r) v = fmaxf(v, src[(int64_t)r * reduce_stride + j]);
+    vals[j] = (v != v) ? -INFINITY : v;   // NaN scores rank lowest
+  }
+  __syncwarp();
+  int mine = -1;   // lane i keeps the i-th pick
+  for (int it = 0; it < k; ++it) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int j = lane; j < n; j += 32) {
+      float v = vals[j];
+      if (v > best || (v == best && j < bi)) {
+        best = v;
+        bi = j;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (lane == it) mine = bi;
+    if (lane == 0) vals[bi] = __int_as_float(0x7fc00000);   // NaN marks a taken slot: it never compares true
+    __syncwarp();
+  }
+  // ascending order by logical age: rank = number of picks with a smaller age
+  int age = (lane < k) ? logical_age(mine, ring_start, n) : 0x7fffffff;
+  int rank = 0;
+  for (int u = 0; u < k; ++u) {
+    int a = __shfl_sync(0xffffffffu, age, u);
+    rank += (a < age) ? 1 : 0;
+  }
+  if (lane < k) idx[row * k + rank] = mine;
+}
+
+// ------------------------------------------------------------------------------------------- gather
+// One CTA per (selected block i, token t, batch*head): copies block*D elements of K (rotated) and V with 16-byte
+// vector accesses.
+template <typename T>
+__global__ void __launch_bounds__(128) gather_kv_kernel(const T* __restrict__ kc, const T* __restrict__ vc,
+                                                        lmk_cache_desc kd, lmk_cache_desc vd,
+                                                        const int32_t* __restrict__ idx, const T* __restrict__ cos_t,
+                                                        const T* __restrict__ sin_t, int n_pos, int rotary,
+                                                        T* __restrict__ k_out, T* __restrict__ v_out, int H, int Tq,
+                                                        int D) {
+  constexpr int VEC = 16 / sizeof(T);
+  struct __align__(16) Vec { T v[VEC]; };
+  const int i = blockIdx.x, t = blockIdx.y, bh = blockIdx.z;
+  const int b = bh / H, h = bh - b * H;
+  const int blk = kd.block, N = kd.n_blocks, top_k = kd.top_k;
+  const int sel = idx[((int64_t)bh * Tq + t) * top_k + i];
+  const bool recent = logical_age(sel, kd.ring_start, N) >= N - top_k;
+  const int pos0 = kd.pos_base + (i + (recent ? 1 : 0)) * blk;
+  const int vec_per_row = D / VEC;
+  const int64_t out_base = (((int64_t)bh * Tq + t) * top_k + i) * blk * D;
+  const T* ksrc = kc + b * kd.stride_b + h * kd.stride_h + (int64_t)sel * kd.stride_block;
+  const T* vsrc = vc ? vc + b * vd.stride_b + h * vd.stride_h + (int64_t)sel * vd.stride_block : nullptr;
+  for (int e = threadIdx.x; e < blk * vec_per_row; e += blockDim.x) {
+    const int r = e / vec_per_row, d0 = (e - r * vec_per_row) * VEC;
+    if (v_out != nullptr && vsrc != nullptr) {
+      Vec vv = *reinterpret_cast<const Vec*>(vsrc + (int64_t)r * vd.stride_row + d0);
+      *reinterpret_cast<Vec*>(v_out + out_base + (int64_t)r * D + d0) = vv;
+    }
+    if (k_out != nullptr) {
+      const T* krow = ksrc + (int64_t)r * kd.stride_row;
+      Vec x = *reinterpret_cast<const Vec*>(krow + d0);
+      Vec o = x;
+      if (rotary != LMK_ROTARY_NONE) {
+        int pos = max(0, min(pos0 + r, n_pos - 1));
+        Vec c = *reinterpret_cast<const Vec*>(cos_t + (int64_t)pos * D + d0);
+        Vec s = *reinterpret_cast<const Vec*>(sin_t + (int64_t)pos * D + d0);
+        if (rotary == LMK_ROTARY_HALF) {
+          const bool lo = d0 < D / 2;
+          Vec y = *reinterpret_cast<const Vec*>(krow + (lo ? d0 + D / 2 : d0 - D / 2));
+#pragma unroll
+          for (int u = 0; u < VEC; ++u) {
+            float partner = lo ? -to_f32(y.v[u]) : to_f32(y.v[u]);
+            o.v[u] = from_f32<T>(rotary_elem<T>(to_f32(x.v[u]), partner, to_f32(c.v[u]), to_f32(s.v[u])));
+          }
+        } else {
+#pragma unroll
+          for (int u = 0; u < VEC; ++u) {
+            float partner = (u & 1) ? to_f32(x.v[u - 1]) : -to_f32(x.v[u + 1]);
+            o.v[u] = from_f32<T>(rotary_elem<T>(to_f32(x.v[u]), partner, to_f32(c.v[u]), to_f32(s.v[u])));
+          }
+        }
+      }
+      *reinterpret_cast<Vec*>(k_out + out_base + (int64_t)r * D + d0) = o;
+    }
+  }
+}
+
+int check_desc(const lmk_cache_desc* d, const char* what) {
+  LMK_CHECK_ARG(d != nullptr, "%s: null cache descriptor", what);
+  LMK_CHECK_ARG(d->block >= 1 && d->n_blocks >= 1, "%s: block %d / n_blocks %d must be positive", what, d->block,
+                d->n_blocks);
+  LMK_CHECK_ARG(d->top_k >= 0 && d->top_k <= d->n_blocks, "%s: top_k %d outside [0, n_blocks=%d]", what, d->top_k,
+                d->n_blocks);
+  LMK_CHECK_ARG(d->ring_start >= 0 && d->ring_start < d->n_blocks, "%s: ring_start %d outside [0, %d)", what,
+                d->ring_start, d->n_blocks);
+  return LMK_OK;
+}
+
+}  // namespace
+}  // namespace lmk
+
+using namespace lmk;
+
+extern "C" int lmk_landmark_scores(const void* q, const void* k_cache, const lmk_cache_desc* desc,
+                                   const void* cos_table, const void* sin_table, int n_pos, int rotary, float* scores,
+                                   int B, int H, int T, int D, float sm_scale, int softmax, int dtype, void* stream) {
+  int rc = check_desc(desc, "landmark_scores");
+  if (rc != LMK_OK) return rc;
+  LMK_CHECK_ARG(q && k_cache && scores, "landmark_scores: null pointer");
+  LMK_CHECK_ARG(B >= 1 && H >= 1 && T >= 1, "landmark_scores: empty problem");
+  LMK_CHECK_ARG(D >= 8 && D <= 256 && D % 8 == 0, "landmark_scores: head dim %d must be a multiple of 8 in [8,256]", D);
+  LMK_CHECK_ARG(dtype == LMK_F32 || dtype == LMK_F16 || dtype == LMK_BF16, "landmark_scores: bad dtype %d", dtype);
+  LMK_CHECK_ARG(rotary >= LMK_ROTARY_NONE && rotary <= LMK_ROTARY_INTERLEAVED, "landmark_scores: bad rotary %d", rotary);
+  LMK_CHECK_ARG(rotary == LMK_ROTARY_NONE || (cos_table && sin_table && n_pos >= 1),
+                "landmark_scores: rotary tables missing");
+  LMK_CHECK_ARG((int64_t)B * H <= 65535 && (T + kScTile - 1) / kScTile <= 65535, "landmark_scores: grid too large");
+  cudaStream_t st = (cudaStream_t)stream;
+  size_t smem = sizeof(float) * ((size_t)kScTile * D + (size_t)kScTile * (D + 1));
+  dim3 grid((desc->n_blocks + kScTile - 1) / kScTile, (T + kScTile - 1) / kScTile, B * H);
+  const int64_t rows = (int64_t)B * H * T;
+#define LMK_SC_LAUNCH(TT)                                                                                          \
+  do {                                                                                                             \
+    LMK_CUDA(cudaFuncSetAttribute(landmark_scores_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                                  (int)smem));                                                                     \
+    landmark_scores_kernel<TT><<<grid, 128, smem, st>>>((const TT*)q, (const TT*)k_cache, *desc,                   \
+                                                        (const TT*)cos_table, (const TT*)sin_table, n_pos, rotary, \
+                                                        scores, H, T, D, sm_scale);                                \
+    if (softmax)                                                                                                   \
+      row_softmax_kernel<TT><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(scores, rows, desc->n_blocks);            \
+  } while (0)
+  if (dtype == LMK_F32) LMK_SC_LAUNCH(float);
+  else if (dtype == LMK_F16) LMK_SC_LAUNCH(__half);
+  else LMK_SC_LAUNCH(__nv_bfloat16);
+#undef LMK_SC_LAUNCH
+  LMK_CUDA(cudaGetLastError());
+  return LMK_OK;
+}
+
+extern "C" int lmk_topk_sorted(const float* scores, int32_t* idx_out, int64_t outer_count, int64_t inner_count,
+                               int64_t outer_stride, int64_t inner_stride, int reduce, int64_t reduce_stride, int n,
+                               int k, int ring_start, void* stream) {
+  LMK_CHECK_ARG(scores && idx_out, "topk_sorted: null pointer");
+  LMK_CHECK_ARG(outer_count >= 1 && inner_count >= 1 && reduce >= 1, "topk_sorted: empty problem");
+  LMK_CHECK_ARG(n >= 1 && n <= 49152, "topk_sorted: n %d outside [1, 49152]", n);
+  LMK_CHECK_ARG(k >= 1 && k <= kTopkMaxK && k <= n, "topk_sorted: k %d outside [1, min(n, %d)]", k, kTopkMaxK);
+  LMK_CHECK_ARG(ring_start >= 0 && ring_start < n, "topk_sorted: ring_start %d outside [0, n)", ring_start);
+  const int64_t rows = outer_count * inner_count;
+  int wpc = n <= 2048 ? 4 : (n <= 8192 ? 2 : 1);
+  size_t smem = sizeof(float) * (size_t)n * wpc;
+  LMK_CUDA(cudaFuncSetAttribute(topk_sorted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  topk_sorted_kernel<<<(unsigned)((rows + wpc - 1) / wpc), 128, smem, (cudaStream_t)stream>>>(
+      scores, idx_out, rows, inner_count, outer_stride, inner_stride, reduce, reduce_stride, n, k, ring_start, wpc);
+  LMK_CUDA(cudaGetLastError());
+  return LMK_OK;
+}
+
+extern "C" int lmk_gather_kv(const void* k_cache, const void* v_cache, const lmk_cache_desc* kdesc,
+                             const lmk_cache_desc* vdesc, const int32_t* idx, const void* cos_table,
+                             const void* sin_table, int n_pos, int rotary, void* k_out, void* v_out, int B, int H,
+                             int T, int D, int dtype, void* stream) {
+  int rc = check_desc(kdesc, "gather_kv");
+  if (rc != LMK_OK) return rc;
+  if (v_out != nullptr) {
+    rc = check_desc(vdesc, "gather_kv(v)");
+    if (rc != LMK_OK) return rc;
+    LMK_CHECK_ARG(v_cache != nullptr, "gather_kv: v_out given without v_cache");
+    LMK_CHECK_ARG(vdesc->block == kdesc->block && vdesc->n_blocks == kdesc->n_blocks && vdesc->top_k == kdesc->top_k,
+                  "gather_kv: key and value cache descriptors disagree");
+  }
+  LMK_CHECK_ARG(idx != nullptr && (k_out != nullptr || v_out != nullptr), "gather_kv: null pointer");
+  LMK_CHECK_ARG(k_out == nullptr || k_cache != nullptr, "gather_kv: k_out given without k_cache");
+  LMK_CHECK_ARG(kdesc->top_k >= 1, "gather_kv: top_k must be >= 1");
+  LMK_CHECK_ARG(B >= 1 && H >= 1 && T >= 1, "gather_kv: empty problem");
+  LMK_CHECK_ARG(dtype == LMK_F32 || dtype == LMK_F16 || dtype == LMK_BF16, "gather_kv: bad dtype %d", dtype);
+  const int vec = 16 / dtype_size(dtype);
+  LMK_CHECK_ARG(D >= 2 * vec && D % (2 * vec) == 0, "gather_kv: head dim %d must be a multiple of %d", D, 2 * vec);
+  LMK_CHECK_ARG(rotary >= LMK_ROTARY_NONE && rotary <= LMK_ROTARY_INTERLEAVED, "gather_kv: bad rotary %d", rotary);
+  LMK_CHECK_ARG(rotary == LMK_ROTARY_NONE || k_out == nullptr || (cos_table && sin_table && n_pos >= 1),
+                "gather_kv: rotary tables missing");
+  const lmk_cache_desc* descs[2] = {kdesc, v_out ? vdesc : kdesc};
+  for (const lmk_cache_desc* d : descs)
+    LMK_CHECK_ARG(d->stride_b % vec == 0 && d->stride_h % vec == 0 && d->stride_block % vec == 0 &&
+                      d->stride_row % vec == 0,
+                  "gather_kv: cache strides must be multiples of %d elements (16 bytes)", vec);
+  LMK_CHECK_ARG(((uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)k_out | (uintptr_t)v_out |
+                 (uintptr_t)cos_table | (uintptr_t)sin_table) % 16 == 0,
+                "gather_kv: pointers must be 16-byte aligned");
+  LMK_CHECK_ARG((int64_t)B * H <= 65535 && T <= 65535, "gather_kv: grid too large");
+  dim3 grid(kdesc->top_k, T, B * H);
+  cudaStream_t st = (cudaStream_t)stream;
+  lmk_cache_desc vd = v_out ? *vdesc : *kdesc;
+#define LMK_GA_LAUNCH(TT)                                                                                      \
+  gather_kv_kernel<TT><<<grid, 128, 0, st>>>((const TT*)k_cache, (const TT*)v_cache, *kdesc, vd, idx,          \
+                                             (const TT*)cos_table, (const TT*)sin_table, n_pos, rotary,        \
+                                             (TT*)k_out, (TT*)v_out, H, T, D)
+  if (dtype == LMK_F32) LMK_GA_LAUNCH(float);
+  else if (dtype == LMK_F16) LMK_GA_LAUNCH(__half);
+  else LMK_GA_LAUNCH(__nv_bfloat16);
+#undef LMK_GA_LAUNCH
+  LMK_CUDA(cudaGetLastError());
+  return LMK_OK;
+}

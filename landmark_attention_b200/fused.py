@@ -1,0 +1,109 @@
+"""Fused landmark attention: same Python API as the reference's `fused_landmark_attention`
+(llama/ltriton/flash_landmark_attention.py:391-403) and an SDPA-style alias.
+"""
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+
+
+class FusedLandmarkAttention(torch.autograd.Function):
+    """Mirrors FusedLandmarkAttention (flash_landmark_attention.py:308-389): forward keeps q, k, v, o and the
+    softmax statistics L, M; backward recomputes the probabilities."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, n_prefix_q, sm_scale, block_size, path=L.PATH_AUTO):
+        L.require_cuda(q, k, v)
+        batch, nheads, seqlen_q, d = q.shape
+        seqlen_k = k.shape[2]
+        assert k.shape == (batch, nheads, seqlen_k, d)
+        assert v.shape == (batch, nheads, seqlen_k, d)
+        assert d <= 128, 'FlashAttention only support head dimensions up to 128'
+        assert q.dtype == k.dtype == v.dtype, 'All tensors must have the same type'
+        assert seqlen_k - seqlen_q == n_prefix_q * block_size
+        q, k, v = [t if t.stride(3) == 1 else t.contiguous() for t in (q, k, v)]
+        o = torch.empty((batch, nheads, seqlen_q, d), device=q.device, dtype=q.dtype)
+        lse_l = torch.empty((batch * nheads, seqlen_q), device=q.device, dtype=torch.float32)
+        lse_m = torch.empty((batch * nheads, seqlen_q), device=q.device, dtype=torch.float32)
+        rc = L.lib().lmk_attn_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(lse_l), L.ptr(lse_m),
+                                  batch, nheads, seqlen_q, seqlen_k, d, L.strides3(q), L.strides3(k), L.strides3(v),
+                                  block_size, float(sm_scale), L.dtype_code(q), path, L.stream_ptr(q.device))
+        L.check(rc, "lmk_attn_fwd")
+        ctx.save_for_backward(q, k, v, o, lse_l, lse_m)
+        ctx.sm_scale, ctx.block, ctx.path = sm_scale, block_size, path
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse_l, lse_m = ctx.saved_tensors
+        block = ctx.block
+        assert q.shape[2] % block == 0, "Backward supported only for full blocks"
+        assert k.shape[2] % block == 0, "Backward supported only for full blocks"
+        batch, nheads, seqlen_q, d = q.shape
+        seqlen_k = k.shape[2]
+        do = do.contiguous()
+        if do.dtype != q.dtype:
+            do = do.to(q.dtype)
+        dq = torch.empty((batch, nheads, seqlen_q, d), device=q.device, dtype=q.dtype)
+        dk = torch.empty((batch, nheads, seqlen_k, d), device=q.device, dtype=q.dtype)
+        dv = torch.empty((batch, nheads, seqlen_k, d), device=q.device, dtype=q.dtype)
+        code = L.dtype_code(q)
+        need = L.lib().lmk_attn_bwd_workspace(batch, nheads, seqlen_q, seqlen_k, d, block, code, ctx.path)
+        ws = torch.empty(max(int(need), 256), device=q.device, dtype=torch.uint8)
+        rc = L.lib().lmk_attn_bwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(do), L.ptr(lse_l), L.ptr(lse_m),
+                                  L.ptr(dq), L.ptr(dk), L.ptr(dv), L.ptr(ws), ws.numel(),
+                                  batch, nheads, seqlen_q, seqlen_k, d, L.strides3(q), L.strides3(k), L.strides3(v),
+                                  block, float(ctx.sm_scale), code, ctx.path, L.stream_ptr(q.device))
+        L.check(rc, "lmk_attn_bwd")
+        return dq, dk, dv, None, None, None, None
+
+
+def fused_landmark_attention(q, k, v, is_mem=None, sm_scale=None, block_size=64, path=L.PATH_AUTO):
+    """Landmark attention over q [B,H,Lq,D], k/v [B,H,Lk,D]; the landmark is the last token of every block.
+
+    Same call as the reference's `fused_landmark_attention(q, k, v, is_mem, sm_scale=None, block_size=64)`.
+    `is_mem` may be None (fast path: no mask is read and the host is not synchronised); when given it must be the
+    regular pattern over the keys, as the reference asserts (flash_landmark_attention.py:393-394).
+    """
+    if is_mem is not None:
+        expected_is_mem = torch.arange(0, is_mem.shape[-1], device=is_mem.device) % block_size == (block_size - 1)
+        assert (is_mem == expected_is_mem).all()
+    n_history_kv = k.shape[-2] - q.shape[-2]
+    assert n_history_kv % block_size == 0
+    n_history_blocks = n_history_kv // block_size
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q.size(-1))
+    return FusedLandmarkAttention.apply(q, k, v, n_history_blocks, sm_scale, block_size, path)
+
+
+def landmark_sdpa(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=True, scale=None, *,
+                  is_mem: Optional[torch.Tensor] = None, block_size: int = 64):
+    """`torch.nn.functional.scaled_dot_product_attention` signature on top of fused landmark attention.
+    Landmark attention is causal by construction; masks and dropout are not part of the operator."""
+    if attn_mask is not None:
+        raise ValueError("landmark_sdpa does not take attn_mask (the landmark pattern defines the mask)")
+    if dropout_p != 0.0:
+        raise ValueError("landmark_sdpa does not support dropout")
+    if not is_causal:
+        raise ValueError("landmark attention is causal; pass is_causal=True")
+    return fused_landmark_attention(query, key, value, is_mem, sm_scale=scale, block_size=block_size)
+
+
+def attn_forward_with_stats(q, k, v, block_size=64, sm_scale=None, path=L.PATH_AUTO):
+    """Forward only; also returns the stored statistics (L, M) [B*H, Lq] for inspection and tests."""
+    L.require_cuda(q, k, v)
+    B, H, Lq, D = q.shape
+    Lk = k.shape[2]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    q, k, v = [t if t.stride(3) == 1 else t.contiguous() for t in (q, k, v)]
+    o = torch.empty((B, H, Lq, D), device=q.device, dtype=q.dtype)
+    l = torch.empty((B * H, Lq), device=q.device, dtype=torch.float32)
+    m = torch.empty((B * H, Lq), device=q.device, dtype=torch.float32)
+    rc = L.lib().lmk_attn_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(l), L.ptr(m), B, H, Lq, Lk, D,
+                              L.strides3(q), L.strides3(k), L.strides3(v), block_size, float(sm_scale),
+                              L.dtype_code(q), path, L.stream_ptr(q.device))
+    L.check(rc, "lmk_attn_fwd")
+    return o, l, m

@@ -1,0 +1,139 @@
+"""Landmark grouped softmax on materialised attention scores, with the reference's two signatures.
+
+llama flavour:        landmark_grouped_softmax(x, dim, is_mem, last_section_mask)           llama/llama_mem.py:222-243
+lm_benchmark flavour: landmark_grouped_softmax_lm(x, dim, is_mem, attn_mask, last_section_mask, return_group_prob,
+                                                  max_mem_cnt, p_group_dropout=None)       lm_benchmark/models/landmark.py:88-119
+Both return fp32 probabilities and are differentiable w.r.t. x.  Masks may be broadcast views; they are never
+expanded in memory and no int64 index tensor is built.
+"""
+import torch
+
+from . import _lib as L
+
+
+def _as_u8(mask):
+    if mask is None:
+        return None
+    if mask.dtype == torch.bool:
+        return mask.view(torch.uint8) if mask.is_contiguous() or mask.dim() == 0 else mask.to(torch.uint8)
+    return mask.to(torch.uint8)
+
+
+def _prep(x, is_mem, last, hidden):
+    if x.dim() != 4:
+        raise ValueError("expected scores of shape [B, H, Lq, Lk]")
+    if x.stride(3) != 1:
+        x = x.contiguous()
+    shape = x.shape
+    masks = []
+    for m in (is_mem, last, hidden):
+        if m is None:
+            masks.append((None, None))
+            continue
+        while m.dim() < 4:
+            m = m.unsqueeze(0)
+        m8 = _as_u8(m)
+        m8, st = L.strides4_broadcast(m8, shape)
+        masks.append((m8, st))
+    return x, masks
+
+
+class _GroupedSoftmax(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, is_mem, last, hidden, guards, max_groups, max_mem_cnt):
+        L.require_cuda(x, is_mem, last, hidden)
+        x, masks = _prep(x, is_mem, last, hidden)
+        B, H, Lq, Lk = x.shape
+        probs = torch.empty((B, H, Lq, Lk), device=x.device, dtype=torch.float32)
+        gp = torch.empty((B, H, Lq, max_mem_cnt), device=x.device, dtype=torch.float32) if max_mem_cnt else None
+        (m8, ms), (l8, ls), (h8, hs) = masks
+        rc = L.lib().lmk_grouped_softmax_fwd(L.ptr(x), L.strides3(x), L.ptr(m8), ms, L.ptr(l8), ls, L.ptr(h8), hs,
+                                             L.ptr(probs), L.ptr(gp), max_mem_cnt or 0, B, H, Lq, Lk,
+                                             L.dtype_code(x), int(guards), max_groups, L.stream_ptr(x.device))
+        L.check(rc, "lmk_grouped_softmax_fwd")
+        ctx.save_for_backward(x, is_mem, last, hidden if hidden is not None else torch.empty(0))
+        ctx.has_hidden = hidden is not None
+        ctx.guards, ctx.max_groups = guards, max_groups
+        if gp is not None:
+            ctx.mark_non_differentiable(gp)
+            return probs, gp
+        return probs, None
+
+    @staticmethod
+    def backward(ctx, gprobs, _ggp):
+        x, is_mem, last, hidden = ctx.saved_tensors
+        hidden = hidden if ctx.has_hidden else None
+        x, masks = _prep(x, is_mem, last, hidden)
+        B, H, Lq, Lk = x.shape
+        gprobs = gprobs.to(torch.float32).contiguous()
+        gx = torch.empty((B, H, Lq, Lk), device=x.device, dtype=torch.float32)
+        (m8, ms), (l8, ls), (h8, hs) = masks
+        rc = L.lib().lmk_grouped_softmax_bwd(L.ptr(x), L.strides3(x), L.ptr(m8), ms, L.ptr(l8), ls, L.ptr(h8), hs,
+                                             L.ptr(gprobs), L.ptr(gx), B, H, Lq, Lk, L.dtype_code(x),
+                                             int(ctx.guards), ctx.max_groups, L.stream_ptr(x.device))
+        L.check(rc, "lmk_grouped_softmax_bwd")
+        return gx.to(x.dtype), None, None, None, None, None, None
+
+
+def _check_dim(x, dim):
+    if dim not in (-1, x.dim() - 1):
+        raise NotImplementedError("the grouped softmax runs over the last dimension")
+
+
+def landmark_grouped_softmax(x, dim, is_mem, last_section_mask, max_groups=None):
+    """llama flavour (llama/llama_mem.py:222-243).  The reference hard-codes room for 63 landmarks per row
+    (max_mem_cnt = 64, :228); here `max_groups` (default: from the row length, at most 2048) bounds 1 + the number of
+    landmarks in a row."""
+    _check_dim(x, dim)
+    if max_groups is None:
+        max_groups = min(2048, x.shape[-1] + 1)
+    probs, _ = _GroupedSoftmax.apply(x, is_mem, last_section_mask, None, False, max_groups, 0)
+    return probs
+
+
+def landmark_grouped_softmax_lm(x, dim, is_mem, attn_mask, last_section_mask, return_group_prob, max_mem_cnt,
+                                p_group_dropout=None):
+    """lm_benchmark flavour (lm_benchmark/models/landmark.py:88-119).  Group dropout is a training-time
+    regulariser outside the measured path and is not implemented."""
+    _check_dim(x, dim)
+    if p_group_dropout is not None:
+        raise NotImplementedError("p_group_dropout is not supported")
+    max_groups = min(2048, max(int(max_mem_cnt), 2))
+    probs, gp = _GroupedSoftmax.apply(x, is_mem, last_section_mask, attn_mask, True, max_groups,
+                                      int(max_mem_cnt) if return_group_prob else 0)
+    return probs, (gp if return_group_prob else None)
+
+
+def prepare_landmark_masks(is_mem_row, attn_mask):
+    """Mask block of the call sites (lm_benchmark/models/landmark.py:210-224; llama/llama_mem.py:807-815).
+    is_mem_row: bool [B, Lk]; attn_mask: bool [..., Lq, Lk] (True = hidden).
+    Returns (mask, is_mem, last_section), bool [B, 1, Lq, Lk]."""
+    B, Lk = is_mem_row.shape
+    im = is_mem_row.view(B, 1, 1, Lk)
+    while attn_mask.dim() < 4:
+        attn_mask = attn_mask.unsqueeze(0)
+    imi = im.to(torch.int32)
+    before = torch.cumsum(imi, dim=-1) - imi
+    mem_ids = torch.where(attn_mask, torch.zeros_like(before), before)
+    last = mem_ids == mem_ids.amax(dim=-1, keepdim=True)
+    mask = attn_mask | (im & last)
+    last = last & ~mask
+    is_mem = im & ~mask
+    return mask, is_mem, last
+
+
+def lm_landmark_attention(q, k, v, is_mem_row, sm_scale=None, max_groups=None):
+    """Attention of lm_benchmark's CausalSelfAttention.forward without cache (landmark.py:196-236): q, k rotated,
+    landmarks at arbitrary per-row positions is_mem_row [B, T].  QK^T and PV are library matmuls; the grouped softmax
+    is this package's kernel."""
+    B, H, T, D = q.shape
+    if sm_scale is None:
+        sm_scale = 1.0 / (D ** 0.5)
+    att = torch.matmul(q, k.transpose(-2, -1)) * sm_scale
+    hidden = torch.ones(T, T, dtype=torch.bool, device=q.device).triu(1)
+    mask, is_mem, last = prepare_landmark_masks(is_mem_row, hidden)
+    att = att.masked_fill(mask, float("-inf"))
+    if max_groups is None:
+        max_groups = min(2048, T + 1)
+    probs, _ = _GroupedSoftmax.apply(att, is_mem, last, mask, True, max_groups, 0)
+    return torch.matmul(probs.to(v.dtype), v)

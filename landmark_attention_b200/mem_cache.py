@@ -1,0 +1,172 @@
+"""lm_benchmark's landmark block cache on this package's retrieval kernels.
+
+Same interface as the reference (lm_benchmark/models/caches/cache.py:17-35, mem_cache.py:21-217):
+`retrieve_for_query(q, cache_context, pos_emb_closure, start_index)`, `store_in_cache(keys, values_dict)`,
+`clear_state()`, and the id bookkeeping of `MemLMCache.forward / get_final_logits`.
+The ring buffer keeps the reference's layout [B, capacity, block, H, D]; selection, the gather and the rotation of
+gathered keys run in CUDA kernels; the rotary convention is lm_benchmark's interleaved one.
+"""
+import math
+
+import torch
+from torch import nn
+
+from . import _lib as L
+from .retrieval import gather_kv, landmark_scores, rotary_tables_interleaved, topk_sorted
+
+
+def _rotate_interleaved(x, cos, sin, positions):
+    c, s = cos[positions], sin[positions]
+    xr = x.reshape(*x.shape[:-1], x.shape[-1] // 2, 2)
+    rot = torch.stack((-xr[..., 1], xr[..., 0]), dim=-1).reshape(x.shape)
+    return x * c + rot * s
+
+
+class MemLMCacheStorage(nn.Module):
+    """Per-layer storage (mem_cache.py:21-158).  `config` needs batch_size, mem_cache_size, mem_cache_freq, n_head,
+    n_embd, cache_topk, cache_selection_method."""
+
+    def __init__(self, config, layer=None, dtype=torch.float32, device="cuda"):
+        super().__init__()
+        self.config = config
+        hs = config.n_embd // config.n_head
+        blk = config.mem_cache_freq + 1
+        shape = (config.batch_size, config.mem_cache_size, blk, config.n_head, hs)
+        self.register_buffer("cache_mem_k", torch.empty(shape, dtype=dtype, device=device), persistent=False)
+        self.register_buffer("cache_mem_v", torch.empty(shape, dtype=dtype, device=device), persistent=False)
+        tail = (config.batch_size, config.n_head, blk, hs)
+        self.register_buffer("last_incomplete_k", torch.empty(tail, dtype=dtype, device=device), persistent=False)
+        self.register_buffer("last_incomplete_v", torch.empty(tail, dtype=dtype, device=device), persistent=False)
+        self.register_buffer("last_incomplete_ismem",
+                             torch.empty((config.batch_size, blk), dtype=torch.bool, device=device), persistent=False)
+        self._tables = None
+        self.clear_state()
+
+    def clear_state(self):
+        self.last_incomplete_len = 0
+        self.cache_iter = 0
+        self.cache_size = 0
+
+    def _rotary(self, n_pos, dim, dtype, device):
+        if self._tables is None or self._tables[0].shape[0] < n_pos or self._tables[0].dtype != dtype:
+            self._tables = rotary_tables_interleaved(max(n_pos, 4096), dim, dtype, device)
+        return self._tables
+
+    def retrieve_for_query(self, q, cache_context, pos_emb_closure, start_index):
+        """mem_cache.py:41-109.  `pos_emb_closure` is accepted for interface parity; positions are applied with
+        lm_benchmark's rotary tables inside the kernels."""
+        B, nh, T, hs = q.shape
+        blk = self.cache_mem_k.shape[2]
+        cap = self.cache_mem_k.shape[1]
+        top_k = self.config.cache_topk
+        scale = 1.0 / math.sqrt(hs)
+        cos, sin = self._rotary(max(start_index + T, (top_k + 2) * blk) + 1, hs, q.dtype, q.device)
+        inc = self.last_incomplete_len
+        tail_pos = torch.arange(start_index - inc, start_index, device=q.device)
+        tail_k = _rotate_interleaved(self.last_incomplete_k[:B, :, :inc], cos, sin, tail_pos)
+        att_incomplete = (q @ tail_k.transpose(-2, -1)) * scale
+        last_v = self.last_incomplete_v[:B, :, :inc].unsqueeze(2).expand(B, nh, T, inc, hs)
+        last_mem = self.last_incomplete_ismem[:B, :inc]
+        if self.cache_size == 0 or top_k == 0:
+            return att_incomplete, {'v': last_v.clone(), 'is_mem': last_mem.clone()}
+        n = min(self.cache_size, cap)
+        ring_start = self.cache_iter % n if self.cache_size >= cap else 0
+        st = self.cache_mem_k.stride()      # [B, cap, blk, H, D] addressed as (b, h, block, row)
+        kdesc = L.CacheDesc(st[0], st[3], st[1], st[2], n, ring_start, blk, min(top_k, n), 0)
+        sv = self.cache_mem_v.stride()
+        vdesc = L.CacheDesc(sv[0], sv[3], sv[1], sv[2], n, ring_start, blk, min(top_k, n), 0)
+        scores = landmark_scores(q, self.cache_mem_k, kdesc, cos, sin, L.ROTARY_INTERLEAVED, scale, softmax=True)
+        sel = topk_sorted(scores, kdesc.top_k, self.config.cache_selection_method, ring_start)
+        if sel.shape != (B, nh, T, kdesc.top_k):
+            sel = sel.expand(B, nh, T, kdesc.top_k).contiguous()
+        mem_k, mem_v = gather_kv(self.cache_mem_k, self.cache_mem_v, kdesc, vdesc, sel, cos, sin,
+                                 L.ROTARY_INTERLEAVED, dim=hs)
+        att_k = (q.unsqueeze(3) @ mem_k.transpose(-2, -1)).squeeze(3) * scale
+        is_mem = torch.zeros((B, kdesc.top_k, blk), dtype=torch.bool, device=q.device)
+        is_mem[:, :, blk - 1] = True
+        att_prefix = torch.cat((att_k, att_incomplete), dim=-1)
+        v_prefix = torch.cat((mem_v, last_v), dim=-2)
+        is_mem_prefix = torch.cat((is_mem.view(B, -1), last_mem), dim=-1)
+        return att_prefix, {'v': v_prefix, 'is_mem': is_mem_prefix}
+
+    def store_in_cache(self, keys, values_dict):
+        """mem_cache.py:111-158: append whole blocks to the ring buffer, keep the unfinished tail aside."""
+        B = keys.shape[0]
+        blk, cap = self.cache_mem_k.shape[2], self.cache_mem_k.shape[1]
+        inc0 = self.last_incomplete_len
+        k = torch.cat((self.last_incomplete_k[:B, :, :inc0], keys), dim=-2)
+        v = torch.cat((self.last_incomplete_v[:B, :, :inc0], values_dict['v']), dim=-2)
+        is_mem = torch.cat((self.last_incomplete_ismem[:B, :inc0], values_dict['is_mem']), dim=-1)
+        _, nh, T, hs = k.shape
+        inc = T % blk
+        full = T - inc
+        self.last_incomplete_k[:B, :, :inc].copy_(k[:, :, full:])
+        self.last_incomplete_v[:B, :, :inc].copy_(v[:, :, full:])
+        self.last_incomplete_ismem[:B, :inc].copy_(is_mem[:, full:])
+        self.last_incomplete_len = inc
+        im = is_mem[:, :full].view(B, -1, blk)
+        assert im[..., -1].all()
+        assert not im[..., :-1].any()
+        added = im.shape[1]
+        kb = k[:, :, :full].transpose(1, 2).reshape(B, added, blk, nh, hs)
+        vb = v[:, :, :full].transpose(1, 2).reshape(B, added, blk, nh, hs)
+        dropped = max(0, added - cap)
+        kb, vb = kb[:, dropped:], vb[:, dropped:]
+        self.cache_iter = (self.cache_iter + dropped) % cap
+        self.cache_size += dropped
+        added -= dropped
+        first = min(added, cap - self.cache_iter)
+        self.cache_mem_k[:B, self.cache_iter:self.cache_iter + first].copy_(kb[:, :first])
+        self.cache_mem_v[:B, self.cache_iter:self.cache_iter + first].copy_(vb[:, :first])
+        if added > first:
+            self.cache_mem_k[:B, :added - first].copy_(kb[:, first:])
+            self.cache_mem_v[:B, :added - first].copy_(vb[:, first:])
+        self.cache_iter = (self.cache_iter + added) % cap if self.cache_iter + added >= cap else self.cache_iter + added
+        self.cache_size += added
+
+
+class MemLMCache(nn.Module):
+    """Token-id bookkeeping of the cache (mem_cache.py:166-223): inserts `landmark_id` after every
+    `mem_cache_freq` tokens across chunk boundaries and strips those positions from the outputs."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.last_incomplete_len = 0
+        self.total_len = 0
+
+    def forward(self, x):
+        freq = self.config.mem_cache_freq
+        prev = self.last_incomplete_len
+        B, T = x.shape
+        n_total = prev + T
+        n_full = n_total // freq
+        out_len = T + ((prev + T) // freq)
+        out = x.new_empty((B, out_len))
+        # position of source token t in the output: t + number of landmarks inserted before it
+        src = torch.arange(T, device=x.device)
+        dst = src + (src + prev) // freq
+        out[:, dst] = x
+        lm_pos = (torch.arange(1, n_full + 1, device=x.device) * freq - prev - 1)
+        lm_pos = lm_pos + (lm_pos + prev) // freq + 1
+        out[:, lm_pos] = self.config.landmark_id
+        self.last_incomplete_len = n_total % freq
+        prev_total = self.total_len
+        self.total_len += out_len
+        blk = freq + 1
+        start_index = min(prev_total // blk, self.config.cache_topk + 1) * blk + prev
+        return out, start_index, None
+
+    def get_final_logits(self, x):
+        freq = self.config.mem_cache_freq
+        B, T, C = x.shape
+        # carry before this chunk = (real tokens before it) mod freq, recovered from the running totals
+        blk = freq + 1
+        start = self.total_len - T
+        pos = torch.arange(start, start + T, device=x.device)
+        keep = (pos % blk) != blk - 1
+        return x[:, keep]
+
+    def clear_state(self):
+        self.last_incomplete_len = 0
+        self.total_len = 0

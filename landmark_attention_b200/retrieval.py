@@ -1,0 +1,163 @@
+"""Inference-time landmark retrieval: scores -> top-k -> gather, and the LLaMA cache branch built from them.
+
+Reference: LlamaAttention.forward cache branch, llama/llama_mem.py:318-430, 447-474.
+"""
+import ctypes
+import math
+
+import torch
+
+from . import _lib as L
+from .grouped_softmax import landmark_grouped_softmax, prepare_landmark_masks
+
+
+def rotary_tables_half(n_pos, dim, dtype, device, base=10000.0):
+    """cos/sin tables [n_pos, dim] built as LlamaRotaryEmbedding does (llama/llama_mem.py:96-122)."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, dim, 2, device=device).float() / dim))
+    t = torch.arange(n_pos, device=device, dtype=inv_freq.dtype)
+    freqs = torch.einsum("i,j->ij", t, inv_freq)
+    emb = torch.cat((freqs, freqs), dim=-1)
+    return emb.cos().to(dtype).contiguous(), emb.sin().to(dtype).contiguous()
+
+
+def rotary_tables_interleaved(n_pos, dim, dtype, device):
+    """cos/sin tables [n_pos, dim] for lm_benchmark's rotary (positional_encoders/rotary.py:24-55)."""
+    freqs = 10 ** (-4 * torch.arange(0, dim, 2, device=device)[: dim // 2].float() / dim)
+    t = torch.arange(n_pos, device=device, dtype=torch.float32)
+    ang = (t.unsqueeze(-1) * freqs.view(1, -1)).unsqueeze(-1).expand(n_pos, dim // 2, 2).reshape(n_pos, dim)
+    return ang.cos().to(dtype).contiguous(), ang.sin().to(dtype).contiguous()
+
+
+def apply_rotary_half(x, cos, sin, positions):
+    """x*cos + rotate_half(x)*sin with tables gathered at `positions` (llama/llama_mem.py:127-149)."""
+    c, s = cos[positions], sin[positions]
+    d = x.shape[-1]
+    rot = torch.cat((-x[..., d // 2:], x[..., : d // 2]), dim=-1)
+    return x * c + rot * s
+
+
+def make_desc(cache_view, block, n_blocks, top_k, ring_start=0, pos_base=0, strides=None):
+    """Cache descriptor for a tensor addressed as [b, h, block index, row, d]."""
+    if strides is None:
+        strides = cache_view.stride()[:4]
+    return L.CacheDesc(int(strides[0]), int(strides[1]), int(strides[2]), int(strides[3]),
+                       int(n_blocks), int(ring_start), int(block), int(top_k), int(pos_base))
+
+
+def landmark_scores(q, k_cache, desc, cos=None, sin=None, rotary=L.ROTARY_NONE, sm_scale=None, softmax=False):
+    """fp32 scores [B,H,T,n_blocks] of rotated queries against the cached landmark keys (rotated at slot positions)."""
+    L.require_cuda(q, k_cache)
+    q = q.contiguous()
+    B, H, T, D = q.shape
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    scores = torch.empty((B, H, T, desc.n_blocks), device=q.device, dtype=torch.float32)
+    n_pos = 0 if cos is None else cos.shape[0]
+    rc = L.lib().lmk_landmark_scores(L.ptr(q), L.ptr(k_cache), ctypes.byref(desc), L.ptr(cos), L.ptr(sin), n_pos,
+                                     rotary, L.ptr(scores), B, H, T, D, float(sm_scale), int(softmax),
+                                     L.dtype_code(q), L.stream_ptr(q.device))
+    L.check(rc, "lmk_landmark_scores")
+    return scores
+
+
+def topk_sorted(scores, k, mode="per_token_and_head", ring_start=0):
+    """Indices (int32, ascending logical age) of the k best blocks.
+    scores: fp32 [B,H,T,N].  mode: per_token_and_head -> [B,H,T,k]; max_over_tokens -> [B,H,1,k];
+    max_over_heads -> [B,1,T,k] (lm_benchmark/models/caches/mem_cache.py:63-70; llama/llama_mem.py:373-384)."""
+    L.require_cuda(scores)
+    assert scores.dtype == torch.float32 and scores.is_contiguous()
+    B, H, T, N = scores.shape
+    if mode == "per_token_and_head":
+        shape, args = (B, H, T, k), (B * H * T, 1, N, 0, 1, 0)
+    elif mode == "max_over_tokens":
+        shape, args = (B, H, 1, k), (B * H, 1, T * N, 0, T, N)
+    elif mode == "max_over_heads":
+        shape, args = (B, 1, T, k), (B, T, H * T * N, N, H, T * N)
+    else:
+        raise NotImplementedError(mode)
+    idx = torch.empty(shape, device=scores.device, dtype=torch.int32)
+    outer, inner, ostride, istride, reduce, rstride = args
+    rc = L.lib().lmk_topk_sorted(L.ptr(scores), L.ptr(idx), outer, inner, ostride, istride, reduce, rstride, N, k,
+                                 ring_start, L.stream_ptr(scores.device))
+    L.check(rc, "lmk_topk_sorted")
+    return idx
+
+
+def gather_kv(k_cache, v_cache, kdesc, vdesc, idx, cos=None, sin=None, rotary=L.ROTARY_NONE, dim=None):
+    """Gather the selected blocks: returns (k_sel rotated at slot positions, v_sel), each [B,H,T,top_k*block,D]."""
+    L.require_cuda(k_cache, v_cache, idx)
+    assert idx.dtype == torch.int32 and idx.is_contiguous()
+    B, H, T, top_k = idx.shape
+    D = dim if dim is not None else k_cache.shape[-1]
+    k_out = torch.empty((B, H, T, top_k * kdesc.block, D), device=idx.device, dtype=k_cache.dtype)
+    v_out = torch.empty_like(k_out)
+    n_pos = 0 if cos is None else cos.shape[0]
+    rc = L.lib().lmk_gather_kv(L.ptr(k_cache), L.ptr(v_cache), ctypes.byref(kdesc), ctypes.byref(vdesc), L.ptr(idx),
+                               L.ptr(cos), L.ptr(sin), n_pos, rotary, L.ptr(k_out), L.ptr(v_out), B, H, T, D,
+                               L.dtype_code(k_cache), L.stream_ptr(idx.device))
+    L.check(rc, "lmk_gather_kv")
+    return k_out, v_out
+
+
+def llama_retrieval_attention(q, k_new, v_new, past_k, past_v, mem_freq, cache_top_k, position_ids=None,
+                              chunk_is_mem=None, cos=None, sin=None, return_debug=False):
+    """Attention of one chunk against a landmark block cache, as LlamaAttention.forward does with
+    `mem_freq`/`cache_top_k` set and use_flash=False (llama/llama_mem.py:296-298, 318-430, 447-474).
+
+    q, k_new, v_new: [B,H,T,D] projections of the chunk BEFORE rotary; past_k/past_v: [B,H,C,D] un-rotated cache
+    (:424,436).  chunk_is_mem: bool [1,T] landmark flags of the chunk (default: regular in absolute position).
+    Returns (attn_output [B,H,T,D], new (past_k, past_v)).
+    """
+    B, H, T, D = q.shape
+    C = past_k.shape[2]
+    block = mem_freq + 1
+    dev = q.device
+    if position_ids is None:
+        position_ids = torch.arange(C, C + T, device=dev)
+    if cos is None:
+        cos, sin = rotary_tables_half(C + T + 1, D, q.dtype, dev)
+    scale = 1.0 / math.sqrt(D)
+    qr = apply_rotary_half(q, cos, sin, position_ids)
+    kr = apply_rotary_half(k_new, cos, sin, position_ids)
+    inc = C % block
+    full = C - inc
+    if inc > 0:
+        assert T + inc <= block
+    num_mems = full // block
+    top_k = min(cache_top_k, num_mems)
+    prefix_len = full - (top_k + 1) * block
+    past_k = past_k if past_k.stride(3) == 1 else past_k.contiguous()
+    past_v = past_v if past_v.stride(3) == 1 else past_v.contiguous()
+    kst, vst = past_k.stride(), past_v.stride()
+    kdesc = L.CacheDesc(kst[0], kst[1], kst[2] * block, kst[2], num_mems, 0, block, top_k, prefix_len)
+    vdesc = L.CacheDesc(vst[0], vst[1], vst[2] * block, vst[2], num_mems, 0, block, top_k, prefix_len)
+    scores = landmark_scores(qr, past_k, kdesc, cos, sin, L.ROTARY_HALF, scale)
+    sel = topk_sorted(scores, top_k)
+    sel_k, sel_v = gather_kv(past_k, past_v, kdesc, vdesc, sel, cos, sin, L.ROTARY_HALF, dim=D)
+    prefix = torch.matmul(qr.unsqueeze(3), sel_k.transpose(3, 4)).squeeze(3) * scale      # [B,H,T,top_k*block]
+
+    inc_pos = torch.arange(full, full + inc, device=dev)
+    k_inc = apply_rotary_half(past_k[:, :, full:], cos, sin, inc_pos)
+    keys = torch.cat((k_inc, kr), dim=2)
+    vals = torch.cat((past_v[:, :, full:], v_new), dim=2)
+    local = torch.matmul(qr, keys.transpose(2, 3)) * scale
+    if chunk_is_mem is None:
+        chunk_is_mem = (position_ids % block == block - 1).view(1, T)
+    hidden = torch.ones(T, T, dtype=torch.bool, device=dev).triu(1)
+    mask_c, is_mem_c, last_c = prepare_landmark_masks(chunk_is_mem, hidden)
+    fmin = torch.finfo(local.dtype).min
+    local = torch.cat((local[..., :inc], local[..., inc:].masked_fill(mask_c, fmin)), dim=-1)
+    pre_pat = torch.zeros(top_k, block, dtype=torch.bool, device=dev)
+    pre_pat[:, block - 1] = True
+    is_mem_full = torch.cat((pre_pat.view(1, 1, 1, -1).expand(1, 1, T, -1),
+                             torch.zeros(1, 1, T, inc, dtype=torch.bool, device=dev), is_mem_c), dim=-1)
+    last_full = torch.cat((torch.zeros(1, 1, T, top_k * block, dtype=torch.bool, device=dev),
+                           torch.ones(1, 1, T, inc, dtype=torch.bool, device=dev), last_c), dim=-1)
+    logits = torch.cat((prefix, local), dim=-1)
+    probs = landmark_grouped_softmax(logits, -1, is_mem_full, last_full).to(q.dtype)
+    p_prefix, p_local = probs[..., : top_k * block], probs[..., top_k * block:]
+    out = torch.matmul(p_local, vals) + torch.matmul(p_prefix.unsqueeze(3), sel_v).squeeze(3)
+    new_cache = (torch.cat((past_k, k_new), dim=2), torch.cat((past_v, v_new), dim=2))
+    if return_debug:
+        return out, new_cache, dict(scores=scores, sel=sel, sel_k=sel_k, sel_v=sel_v, probs=probs)
+    return out, new_cache

@@ -1,0 +1,71 @@
+"""Parity of the stand-alone grouped softmax kernels (both reference flavours) against the oracle and golden data."""
+import pytest
+import torch
+
+import landmark_attention_b200 as P
+from oracle import landmark_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def test_llama_flavour_against_golden(golden):
+    g = golden("gsm_llama.pt")
+    x = g["x"].to(DEV).detach().requires_grad_(True)
+    p = P.landmark_grouped_softmax(x, -1, g["is_mem"].to(DEV), g["last"].to(DEV))
+    assert (p.detach().cpu() - g["probs"]).abs().max().item() < 1e-6
+    (gx,) = torch.autograd.grad(p, [x], g["gprobs"].to(DEV))
+    assert (gx.cpu() - g["gx"]).abs().max().item() < 1e-5
+
+
+def test_lm_flavour_against_golden(golden):
+    g = golden("gsm_lm.pt")
+    x = g["x"].to(DEV).detach().requires_grad_(True)
+    p, gp = P.landmark_grouped_softmax_lm(x, -1, g["is_mem"].to(DEV), g["mask"].to(DEV), g["last"].to(DEV), True,
+                                          g["max_mem_cnt"])
+    assert (p.detach().cpu() - g["probs"]).abs().max().item() < 1e-6
+    assert (gp.cpu() - g["group_prob"]).abs().max().item() < 1e-6
+    (gx,) = torch.autograd.grad(p, [x], g["gprobs"].to(DEV))
+    assert (gx.cpu() - g["gx"]).abs().max().item() < 1e-5
+
+
+def test_lm_call_site_against_golden(golden):
+    g = golden("lm_attn.pt")
+    q, k, v = [g[n].to(DEV).detach().requires_grad_(True) for n in ("q_rot", "k_rot", "v")]
+    B, H, T, D = q.shape
+    y = P.lm_landmark_attention(q, k, v, g["is_mem_row"].to(DEV)).transpose(1, 2).reshape(B, T, H * D)
+    assert (y.detach().cpu() - g["y"]).abs().max().item() < 1e-5
+    dq, dk, dv = torch.autograd.grad(y, [q, k, v], g["gy"].to(DEV))
+    for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert (got.cpu() - g[key]).abs().max().item() < 2e-5
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-6), (torch.bfloat16, 1e-6)])
+def test_regular_pattern_equals_fused_probabilities(dtype, tol):
+    # on the regular landmark pattern the grouped softmax of masked scores is the fused kernel's probability matrix
+    torch.manual_seed(0)
+    B, H, L, D, blk = 1, 2, 320, 32, 64
+    q, k = torch.randn(B, H, L, D), torch.randn(B, H, L, D)
+    s = ((q @ k.transpose(-1, -2)) / D ** 0.5).to(dtype)
+    hidden = torch.ones(L, L, dtype=torch.bool).triu(1)
+    mask, is_mem, last = O.prepare_landmark_masks(O.regular_is_mem(L, blk).view(1, L), hidden)
+    x = s.masked_fill(mask, float("-inf"))
+    exp = O.grouped_softmax(x.float(), is_mem, last, attn_mask=mask, guards=True)
+    got, _ = P.landmark_grouped_softmax_lm(x.to(DEV), -1, is_mem.to(DEV), mask.to(DEV), last.to(DEV), False, L // blk + 3)
+    assert (got.cpu() - exp).abs().max().item() < tol
+    assert (got.sum(-1).cpu() - 1).abs().max().item() < 1e-5
+
+
+def test_long_rows_and_many_groups():
+    torch.manual_seed(1)
+    B, H, Lq, Lk = 1, 1, 8, 4096
+    is_mem_row = torch.zeros(1, Lk, dtype=torch.bool)
+    is_mem_row[0, 31::32] = True
+    x = torch.randn(B, H, Lq, Lk)
+    hidden = torch.zeros(Lq, Lk, dtype=torch.bool)
+    hidden[:, Lk - 5:] = True
+    mask, is_mem, last = O.prepare_landmark_masks(is_mem_row, hidden)
+    xm = x.masked_fill(mask, float("-inf"))
+    exp = O.grouped_softmax(xm, is_mem, last, attn_mask=mask, guards=True)
+    got, _ = P.landmark_grouped_softmax_lm(xm.to(DEV), -1, is_mem.to(DEV), mask.to(DEV), last.to(DEV), False, 130)
+    assert (got.cpu() - exp).abs().max().item() < 1e-6

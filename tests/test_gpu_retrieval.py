@@ -1,0 +1,125 @@
+"""Parity of the retrieval kernels: landmark scores, top-k (bit-exact indices on identical fp32 scores), block gather
+with rotary, the LLaMA cache branch and the lm_benchmark block cache."""
+import math
+
+import pytest
+import torch
+
+import landmark_attention_b200 as P
+from landmark_attention_b200 import _lib as L
+from oracle import landmark_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("n,k", [(5, 2), (64, 4), (1024, 4), (1000, 8), (4096, 4), (33, 32)])
+def test_topk_indices_bit_exact(n, k):
+    torch.manual_seed(n + k)
+    scores = torch.randn(2, 3, 17, n, device=DEV)
+    got = P.topk_sorted(scores, k)
+    exp = scores.topk(k, dim=-1).indices.sort(dim=-1).values
+    assert torch.equal(got.long(), exp)
+
+
+def test_topk_aggregations_and_ring_order():
+    torch.manual_seed(0)
+    s = torch.rand(2, 4, 9, 50, device=DEV)
+    got = P.topk_sorted(s, 3, "max_over_tokens")
+    exp = s.amax(dim=2, keepdim=True).topk(3, dim=-1).indices.sort(dim=-1).values
+    assert torch.equal(got.long(), exp)
+    got = P.topk_sorted(s, 3, "max_over_heads")
+    exp = s.amax(dim=1, keepdim=True).topk(3, dim=-1).indices.sort(dim=-1).values
+    assert torch.equal(got.long(), exp)
+    # ring buffer: ascending by logical age, physical indices returned (mem_cache.py:73-83)
+    ring = 20
+    got = P.topk_sorted(s, 4, ring_start=ring).long()
+    phys = s.topk(4, dim=-1).indices
+    logical = torch.where(phys < ring, phys + 50 - ring, phys - ring).sort(dim=-1).values
+    exp = torch.where(logical >= 50 - ring, logical - (50 - ring), logical + ring)
+    assert torch.equal(got, exp)
+
+
+def test_topk_with_ties_and_infinities():
+    s = torch.full((1, 1, 2, 16), float("-inf"), device=DEV)
+    s[0, 0, 0, 5] = 1.0
+    s[0, 0, 1, :] = 0.5
+    got = P.topk_sorted(s, 3)
+    assert got[0, 0, 0].tolist() == [0, 1, 5]      # one finite value, then lowest indices among the -inf ties
+    assert got[0, 0, 1].tolist() == [0, 1, 2]      # all equal: lowest indices
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_scores_and_gather_llama_layout(dtype):
+    torch.manual_seed(1)
+    B, H, T, D, blk, nblk, top_k = 1, 3, 10, 64, 8, 12, 3
+    C = nblk * blk
+    q = torch.randn(B, H, T, D).to(dtype)
+    pk = torch.randn(B, H, C, D).to(dtype)
+    pv = torch.randn(B, H, C, D).to(dtype)
+    prefix_len = C - (top_k + 1) * blk
+    cos, sin = P.rotary_tables_half(C + T + 1, D, dtype, DEV)
+    pkc, pvc = pk.to(DEV), pv.to(DEV)
+    st = pkc.stride()
+    desc = L.CacheDesc(st[0], st[1], st[2] * blk, st[2], nblk, 0, blk, top_k, prefix_len)
+    scores = P.landmark_scores(q.to(DEV), pkc, desc, cos, sin, L.ROTARY_HALF)
+    mem_pos, _ = O.llama_slot_positions(nblk, top_k, C, blk)
+    lm = O.rotary_half_split(pk.view(B, H, nblk, blk, D)[:, :, :, blk - 1], mem_pos.view(1, 1, nblk))
+    exp = torch.matmul(q.float(), lm.float().transpose(2, 3)) / math.sqrt(D)
+    tol = 1e-4 if dtype == torch.float32 else 6e-2
+    assert (scores.cpu() - exp).abs().max().item() < tol
+    sel = P.topk_sorted(scores, top_k)
+    assert torch.equal(sel.long(), scores.topk(top_k, dim=-1).indices.sort(dim=-1).values)
+    sk, sv = P.gather_kv(pkc, pvc, desc, desc, sel, cos, sin, L.ROTARY_HALF)
+    selc = sel.long().cpu()
+    kpos = O.llama_selected_key_positions(selc, nblk, top_k, prefix_len, blk)
+    gi = selc.view(B, H, T, top_k, 1, 1).expand(B, H, T, top_k, blk, D)
+    ek = torch.take_along_dim(pk.view(B, H, 1, nblk, blk, D).expand(B, H, T, nblk, blk, D), gi, dim=3)
+    ev = torch.take_along_dim(pv.view(B, H, 1, nblk, blk, D).expand(B, H, T, nblk, blk, D), gi, dim=3)
+    ek = ek.reshape(B, H, T, top_k * blk, D)
+    assert torch.equal(sv.cpu(), ev.reshape(B, H, T, top_k * blk, D))          # values: pure copy, bit-exact
+    from landmark_attention_b200.retrieval import apply_rotary_half
+    same_tables = apply_rotary_half(ek, cos.cpu(), sin.cpu(), kpos)            # torch arithmetic on the same tables
+    assert torch.equal(sk.cpu(), same_tables)                                  # keys: same rounding steps as torch
+    assert (sk.cpu().float() - O.rotary_half_split(ek.float(), kpos)).abs().max().item() < (1e-5 if dtype == torch.float32 else 4e-2)
+
+
+@pytest.mark.parametrize("name", ["llama_retr_blocks", "llama_retr_tail"])
+def test_llama_cache_branch_against_golden(golden, name):
+    g = golden(name + ".pt")
+    out, _ = P.llama_retrieval_attention(g["q"].to(DEV), g["k"].to(DEV), g["v"].to(DEV), g["past_k"].to(DEV),
+                                         g["past_v"].to(DEV), g["blk"] - 1, g["top_k"],
+                                         chunk_is_mem=g["is_mem_row"].to(DEV))
+    assert (out.cpu() - g["out"]).abs().max().item() < 1e-5
+
+
+def test_llama_cache_branch_selected_blocks_match_oracle():
+    torch.manual_seed(2)
+    B, H, T, D, blk, C, top_k = 1, 4, 16, 32, 16, 16 * 40, 4
+    q, k, v = [torch.randn(B, H, T, D) for _ in range(3)]
+    pk, pv = torch.randn(B, H, C, D), torch.randn(B, H, C, D)
+    out, _, dbg = P.llama_retrieval_attention(q.to(DEV), k.to(DEV), v.to(DEV), pk.to(DEV), pv.to(DEV), blk - 1, top_k,
+                                              return_debug=True)
+    exp, edbg = O.llama_retrieval_attention(q, k, v, pk, pv, blk, top_k, return_debug=True)
+    assert (dbg["scores"].cpu() - edbg["scores"]).abs().max().item() < 1e-4
+    assert torch.equal(dbg["sel"].long().cpu(), edbg["sel"])
+    assert (out.cpu() - exp).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("method", ["per_token_and_head", "max_over_heads", "max_over_tokens"])
+def test_block_cache_against_golden(golden, method):
+    g = golden(f"memcache_{method}.pt")
+    r0 = g["records"][0]
+    B, H, _, D = r0["q"].shape
+    cfg = type("C", (), dict(batch_size=B, mem_cache_size=g["capacity"], mem_cache_freq=g["blk"] - 1, n_head=H,
+                             n_embd=H * D, cache_topk=g["top_k"], cache_selection_method=method))()
+    store = P.MemLMCacheStorage(cfg, None, dtype=torch.float32, device=DEV)
+    for r in g["records"]:
+        att, d = store.retrieve_for_query(r["q"].to(DEV), None, None, r["start_index"])
+        assert att.shape == r["att_prefix"].shape
+        if att.numel():
+            assert (att.cpu() - r["att_prefix"]).abs().max().item() < 1e-5
+        assert torch.equal(d["is_mem"].cpu(), r["is_mem_prefix"])
+        assert torch.equal(d["v"].cpu(), r["v_prefix"])
+        assert (store.cache_iter, store.cache_size) == (r["cache_iter"], r["cache_size"])
+        store.store_in_cache(r["k"].to(DEV), {"v": r["v"].to(DEV), "is_mem": r["is_mem"].to(DEV)})
