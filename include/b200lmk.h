@@ -48,6 +48,13 @@ enum {
 int lmk_version(void);
 const char* lmk_last_error(void);
 
+/*
+ * Device-side status word of the current device.  Every wait inside the tcgen05 kernels is bounded; a wait that
+ * expires records a site code (> 0) here instead of hanging.  Synchronises the device, writes the code (0 = healthy)
+ * to *status and clears it when `clear` != 0.  No counterpart in the reference.
+ */
+int lmk_device_status(int* status, int clear);
+
 /* 1 if the (shape, dtype) is handled by the tcgen05 kernels, else 0. */
 int lmk_attn_tcgen05_supported(int B, int H, int Lq, int Lk, int D, int block, int dtype);
 

@@ -29,6 +29,7 @@ I64x4 = c_int64 * 4
 PROTOTYPES = {
     "lmk_version": (c_int, []),
     "lmk_last_error": (c_char_p, []),
+    "lmk_device_status": (c_int, [POINTER(c_int), c_int]),
     "lmk_attn_tcgen05_supported": (c_int, [c_int] * 7),
     "lmk_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_int, c_int, c_int, c_int, c_int, POINTER(c_int64), POINTER(c_int64), POINTER(c_int64),
@@ -68,6 +69,13 @@ def lib():
             fn.restype, fn.argtypes = res, args
         _lib = handle
     return _lib
+
+
+def device_status(clear: bool = True) -> int:
+    """Status word of the current device (0 = healthy); a non-zero value names the bounded wait that expired."""
+    v = c_int(0)
+    check(lib().lmk_device_status(ctypes.byref(v), int(clear)), "lmk_device_status")
+    return v.value
 
 
 def dtype_code(t: torch.Tensor) -> int:

@@ -72,6 +72,8 @@ extern "C" int lmk_version(void) { return LMK_VERSION; }
 
 extern "C" const char* lmk_last_error(void) { return error_buffer(); }
 
+extern "C" int lmk_device_status(int* status, int clear) { return device_status(status, clear); }
+
 extern "C" int lmk_attn_tcgen05_supported(int B, int H, int Lq, int Lk, int D, int block, int dtype) {
   return attn_sm100_supported(B, H, Lq, Lk, D, block, dtype) ? 1 : 0;
 }

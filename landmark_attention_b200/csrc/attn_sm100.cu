@@ -1,9 +1,411 @@
-// placeholder
+// Fused landmark attention for sm_100a: TMA-fed tcgen05 MMAs with TMEM accumulators.
+//
+// Shape contract: bf16 / fp16, head dim 128, landmark block 64, Lq a multiple of 128, Lk a multiple of 64.
+//
+// Forward, one CTA per (128 query rows, batch*head); rows 0-63 belong to landmark block `own0`, rows 64-127 to
+// `own0 + 1`.  Warps 0-3 run the softmax (thread = query row = TMEM lane), warp 4 issues TMA loads, warp 5 issues
+// the MMAs and owns the TMEM allocation.
+//   1. Pre-pass: S_lm = Q . K_lm^T against the landmark keys only (every 64th key, fetched with a strided 5-D TMA box)
+//      gives each row the maximum landmark score of its earlier blocks.  Together with the row maximum of the
+//      own (diagonal) block, which is processed first, this is the FINAL maximum of the outer softmax, so the O
+//      accumulator in TMEM is never rescaled.
+//   2. Main loop over key blocks n = own0+1 ... 0:  S = Q . K_n^T (N = 64);  the softmax threads read S from TMEM,
+//      form the block's weights  p_j = softmax_inside_block(s)_j * exp(l_n - m)  (own block: exp(s_j - m), causal),
+//      write them as bf16 into the shared-memory slot the K block just vacated (128-byte swizzled, K-major), and
+//      O += P . V_n runs with V as an MN-major operand straight from its row-major TMA tile.
+//   3. Epilogue: O / l -> global, plus the statistics L = l, M = m the backward pass needs.
+// Reference semantics: llama/ltriton/flash_landmark_attention.py:6-122.
 #include "common.cuh"
 #include "attn_params.h"
+#include "sm100_ptx.cuh"
+
 namespace lmk {
-bool attn_sm100_supported(int, int, int, int, int, int, int) { return false; }
-int attn_sm100_fwd(const AttnParams&, int, cudaStream_t) { return fail(LMK_ERR_UNSUPPORTED, "tcgen05 path not built"); }
-int attn_sm100_bwd(const AttnParams&, int, cudaStream_t) { return fail(LMK_ERR_UNSUPPORTED, "tcgen05 path not built"); }
-size_t attn_sm100_bwd_workspace(int, int, int, int, int) { return 0; }
+
+__device__ int g_lmk_status = 0;   // first bounded wait that expired (0 = none); see lmk_device_status()
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kD = 128;
+constexpr int kBlk = 64;
+constexpr int kQTile = 128;
+constexpr int kFwdStages = 2;
+constexpr int kFwdThreads = 192;
+constexpr uint32_t kTileBytes = 16384;   // one [128 x 64] or two [64 x 64] 16-bit tiles
+constexpr uint32_t kHalfTile = 8192;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// error sites reported through g_lmk_status
+enum { kErrFwdProducer = 101, kErrFwdMma = 102, kErrFwdSoftmax = 103, kErrFwdEpilogue = 104 };
+
+struct FwdSmem {
+  // tile storage is addressed manually from the 1024-byte aligned base; this struct holds the barriers only
+  uint64_t q_full;
+  uint64_t full[kFwdStages];
+  uint64_t empty[kFwdStages];
+  uint64_t p_ready[kFwdStages];
+  uint64_t s_full[2];
+  uint64_t s_free[2];
+  uint64_t o_full;
+  uint32_t tmem_base;
+};
+
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if (kBf16) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&t);
+  } else {
+    __half2 t = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
 }
+
+// write one row (64 16-bit values, given as 32 packed words) of a [128 x 64] K-major 128B-swizzled tile
+__device__ __forceinline__ void store_row_sw128(uint32_t tile_base, int row, const uint32_t (&w)[32]) {
+  const uint32_t row_addr = tile_base + row * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint32_t addr = row_addr + ((c ^ (row & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * c]), "r"(w[4 * c + 1]),
+                 "r"(w[4 * c + 2]), "r"(w[4 * c + 3])
+                 : "memory");
+  }
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kFwdThreads, 2)
+sm100_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_klm,
+                 void* __restrict__ o_ptr, float* __restrict__ L_ptr, float* __restrict__ M_ptr, int H, int Lq, int Lk,
+                 int lm_box, float scale_log2) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t q_tile = base;                                        // 32 KB: two [128 x 64] sub-tiles
+  auto k_slot = [&](int s) { return base + 32768u + (uint32_t)s * 32768u; };   // 16 KB: K block, later P
+  auto v_slot = [&](int s) { return base + 32768u + (uint32_t)s * 32768u + 16384u; };
+  FwdSmem* sm = reinterpret_cast<FwdSmem*>(smem_raw + (base - raw) + 32768u + kFwdStages * 32768u);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_tiles = Lq / kQTile;
+  const int t = n_tiles - 1 - (int)blockIdx.x;          // heaviest tiles first
+  const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
+  const int prefix_blocks = (Lk - Lq) / kBlk;
+  const int own0 = prefix_blocks + 2 * t;               // block of rows 0-63; rows 64-127 own own0+1
+  const int n_last = own0 + 1;
+  const int n_lm_tiles = (n_last + 63) / 64;            // landmarks 0 .. n_last-1
+  const int total = n_lm_tiles + n_last + 1;
+
+  if (tid == 0) {
+    mbar_init(smem_u32(&sm->q_full), 1);
+    for (int s = 0; s < kFwdStages; ++s) {
+      mbar_init(smem_u32(&sm->full[s]), 1);
+      mbar_init(smem_u32(&sm->empty[s]), 1);
+      mbar_init(smem_u32(&sm->p_ready[s]), 128);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&sm->s_full[s]), 1);
+      mbar_init(smem_u32(&sm->s_free[s]), 128);
+    }
+    mbar_init(smem_u32(&sm->o_full), 1);
+    mbar_init_fence();
+  }
+  if (warp == 5) tmem_alloc(smem_u32(&sm->tmem_base), 256);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm->tmem_base;
+  const uint32_t tmem_s0 = tmem, tmem_o = tmem + 128;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&tm_q);
+      prefetch_tensormap(&tm_k);
+      prefetch_tensormap(&tm_v);
+      prefetch_tensormap(&tm_klm);
+      const uint32_t qb = smem_u32(&sm->q_full);
+      mbar_arrive_expect_tx(qb, 2 * kTileBytes);
+      tma_load_4d(q_tile, &tm_q, qb, 0, t * kQTile, h, b);
+      tma_load_4d(q_tile + kTileBytes, &tm_q, qb, 64, t * kQTile, h, b);
+      for (int i = 0; i < total; ++i) {
+        const int s = i % kFwdStages;
+        const uint32_t ph = (i / kFwdStages) & 1;
+        mbar_wait(smem_u32(&sm->empty[s]), ph ^ 1, &g_lmk_status, kErrFwdProducer);
+        const uint32_t fb = smem_u32(&sm->full[s]);
+        if (i < n_lm_tiles) {
+          // the landmark box holds lm_box <= 64 keys; rows beyond it keep stale data and are never used
+          mbar_arrive_expect_tx(fb, (uint32_t)lm_box * 256u);
+          tma_load_5d(k_slot(s), &tm_klm, fb, 0, kBlk - 1, i * 64, h, b);
+          tma_load_5d(k_slot(s) + kHalfTile, &tm_klm, fb, 64, kBlk - 1, i * 64, h, b);
+        } else {
+          const int n = n_last - (i - n_lm_tiles);
+          mbar_arrive_expect_tx(fb, 2 * kTileBytes);
+          tma_load_4d(k_slot(s), &tm_k, fb, 0, n * kBlk, h, b);
+          tma_load_4d(k_slot(s) + kHalfTile, &tm_k, fb, 64, n * kBlk, h, b);
+          tma_load_4d(v_slot(s), &tm_v, fb, 0, n * kBlk, h, b);
+          tma_load_4d(v_slot(s) + kHalfTile, &tm_v, fb, 64, n * kBlk, h, b);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t fmt = kBf16 ? 1u : 0u;
+      constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);    // S = Q K^T
+      constexpr uint32_t idesc_o = instr_desc_f16(fmt, 128, 128, 0, 1);   // O += P V   (V is MN-major)
+      mbar_wait(smem_u32(&sm->q_full), 0, &g_lmk_status, kErrFwdMma);
+      auto issue_s = [&](int j) {
+        const int s = j % kFwdStages, sb = j & 1;
+        mbar_wait(smem_u32(&sm->full[s]), (j / kFwdStages) & 1, &g_lmk_status, kErrFwdMma);
+        if (j >= 2) mbar_wait(smem_u32(&sm->s_free[sb]), ((j / 2) & 1) ^ 1, &g_lmk_status, kErrFwdMma);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          // Q and K: two 64-column sub-tiles; a K-step of 16 elements is 32 bytes inside the swizzle atom
+          const uint32_t qa = q_tile + (kk >> 2) * kTileBytes + (kk & 3) * 32;
+          const uint32_t ka = k_slot(s) + (kk >> 2) * kHalfTile + (kk & 3) * 32;
+          mma_f16_ss(tmem_s0 + sb * 64, smem_desc_sw128(qa, 16, 1024), smem_desc_sw128(ka, 16, 1024), idesc_s,
+                     kk > 0);
+        }
+        mma_commit(smem_u32(&sm->s_full[sb]));
+      };
+      issue_s(0);
+      bool o_started = false;
+      for (int i = 0; i < total; ++i) {
+        if (i + 1 < total) issue_s(i + 1);
+        const int s = i % kFwdStages;
+        mbar_wait(smem_u32(&sm->p_ready[s]), (i / kFwdStages) & 1, &g_lmk_status, kErrFwdMma);
+        tc_fence_after();
+        if (i >= n_lm_tiles) {
+#pragma unroll
+          for (int kk = 0; kk < kBlk / 16; ++kk) {
+            // P: [128 x 64] K-major tile in the K slot.  V: two [64 keys x 64 features] sub-tiles, MN-major:
+            // 8-key groups 1024 B apart (SBO), the second 64-feature half 8192 B further (LBO); 16 keys = 2048 B.
+            const uint32_t pa = k_slot(s) + kk * 32;
+            const uint32_t va = v_slot(s) + kk * 2048;
+            mma_f16_ss(tmem_o, smem_desc_sw128(pa, 16, 1024), smem_desc_sw128(va, kHalfTile, 1024), idesc_o,
+                       (o_started || kk > 0) ? 1u : 0u);
+          }
+          o_started = true;
+        }
+        mma_commit(smem_u32(&sm->empty[s]));
+      }
+      mma_commit(smem_u32(&sm->o_full));
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax threads (row = tid)
+    const int row = tid;
+    const int half = row >> 6;
+    const int own = own0 + half;
+    const int vis = min(row & 63, kBlk - 2);
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    float m2 = -INFINITY;   // maximum of the outer softmax, log2 domain
+    float l = 0.f;
+    for (int i = 0; i < total; ++i) {
+      const int sb = i & 1, s = i % kFwdStages;
+      mbar_wait(smem_u32(&sm->s_full[sb]), (i / 2) & 1, &g_lmk_status, kErrFwdSoftmax);
+      tc_fence_after();
+      uint32_t ra[32], rb[32];
+      tmem_ld_32x32b_x32(tmem_s0 + sb * 64 + lane_base, ra);
+      tmem_ld_32x32b_x32(tmem_s0 + sb * 64 + 32 + lane_base, rb);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sm->s_free[sb]));
+      float sv[64];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        sv[j] = __uint_as_float(ra[j]) * scale_log2;
+        sv[32 + j] = __uint_as_float(rb[j]) * scale_log2;
+      }
+      if (i < n_lm_tiles) {
+        // landmark scores of blocks i*64 .. i*64+63; only blocks before the row's own block count
+        const int first = i * 64;
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          if (first + j < own) m2 = fmaxf(m2, sv[j]);
+      } else {
+        const int n = n_last - (i - n_lm_tiles);
+        uint32_t w[32];
+        if (n > own) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) w[j] = 0u;
+        } else if (n == own) {
+          float mx = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 64; ++j)
+            if (j <= vis) mx = fmaxf(mx, sv[j]);
+          m2 = fmaxf(m2, mx);
+          float sum = 0.f;
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            sv[j] = (j <= vis) ? ex2(sv[j] - m2) : 0.f;
+            sum += sv[j];
+          }
+          l += sum;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) w[j] = pack2<kBf16>(sv[2 * j], sv[2 * j + 1]);
+        } else {
+          const float lm = sv[63];
+          float mx = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 63; ++j) mx = fmaxf(mx, sv[j]);
+          float den = 0.f;
+#pragma unroll
+          for (int j = 0; j < 63; ++j) {
+            sv[j] = ex2(sv[j] - mx);
+            den += sv[j];
+          }
+          const float el = ex2(lm - m2);
+          l += el;
+          const float wgt = el / den;
+          sv[63] = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) w[j] = pack2<kBf16>(sv[2 * j] * wgt, sv[2 * j + 1] * wgt);
+        }
+        store_row_sw128(k_slot(s), row, w);
+        fence_proxy_async_smem();
+      }
+      mbar_arrive(smem_u32(&sm->p_ready[s]));
+    }
+    // ------------------------------------------------------------------ epilogue
+    mbar_wait(smem_u32(&sm->o_full), 0, &g_lmk_status, kErrFwdEpilogue);
+    tc_fence_after();
+    const float inv = 1.f / l;
+    const int grow = t * kQTile + row;
+    uint4* orow = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(o_ptr) + ((int64_t)bh * Lq + grow) * kD);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(tmem_o + c * 32 + lane_base, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int v4 = 0; v4 < 4; ++v4) {
+        uint4 pk;
+        pk.x = pack2<kBf16>(__uint_as_float(r[8 * v4 + 0]) * inv, __uint_as_float(r[8 * v4 + 1]) * inv);
+        pk.y = pack2<kBf16>(__uint_as_float(r[8 * v4 + 2]) * inv, __uint_as_float(r[8 * v4 + 3]) * inv);
+        pk.z = pack2<kBf16>(__uint_as_float(r[8 * v4 + 4]) * inv, __uint_as_float(r[8 * v4 + 5]) * inv);
+        pk.w = pack2<kBf16>(__uint_as_float(r[8 * v4 + 6]) * inv, __uint_as_float(r[8 * v4 + 7]) * inv);
+        orow[c * 4 + v4] = pk;
+      }
+    }
+    L_ptr[(int64_t)bh * Lq + grow] = l;
+    M_ptr[(int64_t)bh * Lq + grow] = m2 * (1.f / kLog2e);
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// [B, H, L, 128] tensor with element strides {b, h, row}; box = 64 features x `box_rows` rows, 128-byte swizzle
+int make_map_4d(CUtensorMap* m, const void* ptr, int dtype, int B, int H, int L, const int64_t st[3], int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(LMK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)st[2] * 2, (cuuint64_t)st[1] * 2, (cuuint64_t)st[0] * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(m, dtype == LMK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LMK_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed with %d", (int)r);
+  return LMK_OK;
+}
+
+// landmark keys: k viewed as [B, H, L/64, 64, 128]; box = 64 features x 1 row-in-block x 64 blocks
+int make_map_landmarks(CUtensorMap* m, const void* ptr, int dtype, int B, int H, int L, const int64_t st[3],
+                       int lm_box) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(LMK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[5] = {(cuuint64_t)kD, (cuuint64_t)kBlk, (cuuint64_t)(L / kBlk), (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[4] = {(cuuint64_t)st[2] * 2, (cuuint64_t)st[2] * 2 * kBlk, (cuuint64_t)st[1] * 2,
+                           (cuuint64_t)st[0] * 2};
+  cuuint32_t box[5] = {64, 1, (cuuint32_t)lm_box, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = enc(m, dtype == LMK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
+                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LMK_ERR_CUDA, "cuTensorMapEncodeTiled (landmarks) failed with %d", (int)r);
+  return LMK_OK;
+}
+
+bool tma_ok(const void* p, const int64_t st[3]) {
+  return ((uintptr_t)p % 16 == 0) && st[0] % 8 == 0 && st[1] % 8 == 0 && st[2] % 8 == 0 && st[2] >= kD;
+}
+
+}  // namespace
+
+bool attn_sm100_supported(int B, int H, int Lq, int Lk, int D, int block, int dtype) {
+  return (dtype == LMK_BF16 || dtype == LMK_F16) && D == kD && block == kBlk && Lq >= kQTile && Lq % kQTile == 0 &&
+         Lk % kBlk == 0 && Lk >= Lq && B >= 1 && H >= 1;
+}
+
+int attn_sm100_fwd(const AttnParams& p, int dtype, cudaStream_t st) {
+  if (!tma_ok(p.q, p.qs) || !tma_ok(p.k, p.ks) || !tma_ok(p.v, p.vs))
+    return fail(LMK_ERR_UNSUPPORTED, "tcgen05 path needs 16-byte aligned q/k/v with strides that are multiples of 8");
+  CUtensorMap tq, tk, tv, tl;
+  int rc;
+  if ((rc = make_map_4d(&tq, p.q, dtype, p.B, p.H, p.Lq, p.qs, kQTile)) != LMK_OK) return rc;
+  if ((rc = make_map_4d(&tk, p.k, dtype, p.B, p.H, p.Lk, p.ks, kBlk)) != LMK_OK) return rc;
+  if ((rc = make_map_4d(&tv, p.v, dtype, p.B, p.H, p.Lk, p.vs, kBlk)) != LMK_OK) return rc;
+  const int lm_box = (p.Lk / kBlk) < 64 ? (p.Lk / kBlk) : 64;
+  if ((rc = make_map_landmarks(&tl, p.k, dtype, p.B, p.H, p.Lk, p.ks, lm_box)) != LMK_OK) return rc;
+  const size_t smem = 1024 + 32768 + kFwdStages * 32768 + sizeof(FwdSmem);
+  dim3 grid(p.Lq / kQTile, p.B * p.H);
+  const float scale_log2 = p.scale * kLog2e;
+  if (dtype == LMK_BF16) {
+    LMK_CUDA(cudaFuncSetAttribute(sm100_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    sm100_fwd_kernel<true><<<grid, kFwdThreads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk, lm_box,
+                                                             scale_log2);
+  } else {
+    LMK_CUDA(cudaFuncSetAttribute(sm100_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    sm100_fwd_kernel<false><<<grid, kFwdThreads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk, lm_box,
+                                                             scale_log2);
+  }
+  LMK_CUDA(cudaGetLastError());
+  return LMK_OK;
+}
+
+int attn_sm100_bwd(const AttnParams&, int, cudaStream_t) {
+  return fail(LMK_ERR_UNSUPPORTED, "tcgen05 backward is not built yet");
+}
+
+size_t attn_sm100_bwd_workspace(int, int, int, int, int) { return 0; }
+
+int device_status(int* out, int clear) {
+  int v = 0;
+  LMK_CUDA(cudaDeviceSynchronize());
+  LMK_CUDA(cudaMemcpyFromSymbol(&v, g_lmk_status, sizeof(int)));
+  if (clear && v != 0) {
+    int z = 0;
+    LMK_CUDA(cudaMemcpyToSymbol(g_lmk_status, &z, sizeof(int)));
+  }
+  if (out) *out = v;
+  return LMK_OK;
+}
+
+}  // namespace lmk

@@ -1,0 +1,68 @@
+"""Parity of the tcgen05/TMEM fused landmark attention kernels (through the C ABI) against the CPU oracle.
+bf16/fp16 tolerances: 2e-2 max-abs and 1e-2 relative L2 for outputs and gradients."""
+import pytest
+import torch
+
+import landmark_attention_b200 as P
+from landmark_attention_b200 import _lib as L
+from oracle import landmark_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel_l2(a, b):
+    return ((a - b).norm() / b.norm().clamp_min(1e-20)).item()
+
+
+def make(B, H, Lq, Lk, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = (torch.randn(B, H, Lq, 128, generator=g) * 0.5).to(dtype)
+    k = (torch.randn(B, H, Lk, 128, generator=g) * 0.5).to(dtype)
+    v = (torch.randn(B, H, Lk, 128, generator=g) * 0.5).to(dtype)
+    do = torch.randn(B, H, Lq, 128, generator=g).to(dtype)
+    return q, k, v, do
+
+
+FWD_SHAPES = [(1, 1, 128, 128), (1, 2, 256, 256), (2, 2, 512, 512), (1, 2, 128, 320), (1, 1, 256, 448),
+              (1, 1, 1024, 1024)]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", FWD_SHAPES)
+def test_forward_against_oracle(shape, dtype):
+    B, H, Lq, Lk = shape
+    q, k, v, _ = make(B, H, Lq, Lk, dtype, 7)
+    out, l, m = P.attn_forward_with_stats(q.to(DEV), k.to(DEV), v.to(DEV), 64, path=P.PATH_TCGEN05)
+    assert L.device_status() == 0
+    exp, em, el = O.landmark_attention(q.float(), k.float(), v.float(), 64, return_stats=True)
+    got = out.float().cpu()
+    assert (got - exp).abs().max().item() < 2e-2
+    assert rel_l2(got, exp) < 1e-2
+    assert (m.cpu().view_as(em) - em).abs().max().item() < 1e-3
+    assert ((l.cpu().view_as(el) - el).abs() / el).max().item() < 2e-3
+
+
+def test_forward_matches_general_path_and_known_answers():
+    q, k, v, _ = make(1, 4, 512, 512, torch.bfloat16, 8)
+    q, k, v = q.to(DEV), k.to(DEV), v.to(DEV)
+    a = P.fused_landmark_attention(q, k, v, None, path=P.PATH_TCGEN05)
+    b = P.fused_landmark_attention(q, k, v, None, path=P.PATH_GENERAL)
+    assert (a.float() - b.float()).abs().max().item() < 1.5e-2
+    ones = torch.ones_like(v)
+    o = P.fused_landmark_attention(q, k, ones, None, path=P.PATH_TCGEN05)
+    assert (o.float() - 1).abs().max().item() < 1e-2                       # rows of P sum to one
+    assert torch.equal(a[:, :, 0], v[:, :, 0])                            # first row sees only the first key
+    assert L.device_status() == 0
+
+
+def test_forward_strided_views():
+    g = torch.Generator().manual_seed(9)
+    B, H, Lq = 2, 3, 256
+    q, k, v = [(torch.randn(B, Lq, H, 128, generator=g) * 0.5).to(torch.bfloat16).to(DEV).transpose(1, 2)
+               for _ in range(3)]
+    out = P.fused_landmark_attention(q, k, v, None, path=P.PATH_TCGEN05)
+    exp = O.landmark_attention(q.float().cpu().contiguous(), k.float().cpu().contiguous(),
+                               v.float().cpu().contiguous(), 64)
+    assert (out.float().cpu() - exp).abs().max().item() < 2e-2
+    assert L.device_status() == 0
