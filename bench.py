@@ -1,0 +1,343 @@
+#!/usr/bin/env python
+"""Benchmark of the landmark-attention hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W          # this repo's CUDA kernels
+    python bench.py --impl reference ...                   # the CPU restatement of the reference, host cores only
+
+One step = one forward + backward pass of fused landmark attention at the configuration the headline metric is
+quoted on (B=1, H=32, L=2048, D=128, bf16, block 64, causal, no mask) on every GPU; with N GPUs each rank owns its own
+(batch, head) shard of the same size and there is no collective on the data path (weak scaling).  Rank 0 prints ONE
+JSON line.  FLOPs follow the flash-attention convention for causal attention: 2*B*H*L^2*D forward, 7*B*H*L^2*D forward
+plus backward (matmuls only, causal-halved).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(B=1, H=32, L=2048, D=128, block=64, dtype="bf16")
+RETRIEVAL = dict(H=32, D=128, cache_len=32768, block=32, chunk=258, top_k=4, layers=32, raw_tokens=250)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(bf16_tflops=p["bf16_tflops"], hbm_gbs=p["hbm_gbs"], source="measured")
+    return dict(bf16_tflops=1590.0, hbm_gbs=6650.0, source="fallback")
+
+
+def attn_flops(B, H, L, D, backward=True):
+    return (7 if backward else 2) * B * H * L * L * D
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def dist_setup(n_gpus, cpu_only=False):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        dist.init_process_group("nccl" if (torch.cuda.is_available() and not cpu_only) else "gloo",
+                                rank=rank, world_size=world)
+    return world, rank, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def max_over_ranks(x, world, device):
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return x
+
+
+def shard_heads(total_bh, world, rank):
+    """Contiguous (batch*head) shard of a job of total_bh heads; used for the strong-scaling view and by the tests."""
+    per, rem = divmod(total_bh, world)
+    start = rank * per + min(rank, rem)
+    return start, start + per + (1 if rank < rem else 0)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+def cpu_oracle_attn(heads, threads, steps=1, warmup=0):
+    """fwd+bwd of the CPU restatement on `heads` heads of the workload (fp32); returns (TFLOP/s, seconds per step)."""
+    from oracle import landmark_oracle as O
+    torch.set_num_threads(threads)
+    w = WORKLOAD
+    g = torch.Generator().manual_seed(0)
+    q, k, v = [(torch.randn(1, heads, w["L"], w["D"], generator=g) * 0.5) for _ in range(3)]
+    do = torch.randn(1, heads, w["L"], w["D"], generator=g)
+    ts = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.landmark_attention_grads(q, k, v, do, w["block"])
+        if i >= warmup:
+            ts.append(time.perf_counter() - t0)
+    sec = sum(ts) / len(ts)
+    return attn_flops(1, heads, w["L"], w["D"]) / sec / 1e12, sec
+
+
+def run_reference(args, world, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    heads = 2
+    tf, sec = cpu_oracle_attn(heads, threads, steps=args.steps, warmup=min(args.warmup, 1))
+    w = WORKLOAD
+    line = {
+        "impl": "reference", "metric": "landmark attn fwd+bwd TFLOP/s at L=2048 D=128", "value": tf, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "fused landmark attention fwd+bwd B=1 H=32 L=2048 D=128 block=64 causal",
+                   "sample": f"{heads} of {w['H']} heads per step"},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"CPU restatement of the reference's high-level path, {heads} of {w['H']} heads, fp32"},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+def run_ours(args, world, rank, local):
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this package has no CPU path")
+    import landmark_attention_b200 as P
+    from landmark_attention_b200 import _lib as L
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    peaks = measured_peaks()
+    w = WORKLOAD
+    B, H, Lq, D, blk = w["B"], w["H"], w["L"], w["D"], w["block"]
+    g = torch.Generator().manual_seed(1234 + rank)
+    host = [(torch.randn(B, H, Lq, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory() for _ in range(3)]
+    host.append(torch.randn(B, H, Lq, D, generator=g).to(torch.bfloat16).pin_memory())
+    q, k, v, do = [t.to(dev) for t in host]
+    q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    flush = torch.empty(384 * 1024 * 1024, dtype=torch.uint8, device=dev)      # 3x the 126 MB L2
+    flops_fwd, flops_all = attn_flops(B, H, Lq, D, False), attn_flops(B, H, Lq, D, True)
+
+    def step():
+        out = P.fused_landmark_attention(q, k, v, None, block_size=blk)
+        return out, torch.autograd.grad(out, [q, k, v], do)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if L.device_status() != 0:
+        raise SystemExit("device status word is non-zero after warm-up: a bounded wait expired")
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    marks = []
+    barrier(world); torch.cuda.synchronize()
+    if rank == 0:
+        sampler.start()
+    wall0 = time.perf_counter()
+    for _ in range(args.steps):
+        flush.zero_()                                   # evict q/k/v/o from L2; outside the per-step events
+        e0, e1, e2 = ev(), ev(), ev()
+        e0.record()
+        out = P.fused_landmark_attention(q, k, v, None, block_size=blk)
+        e1.record()
+        torch.autograd.grad(out, [q, k, v], do)
+        e2.record()
+        marks.append((e0, e1, e2))
+    torch.cuda.synchronize(); barrier(world)
+    wall = time.perf_counter() - wall0
+    clocks = sampler.stop() if rank == 0 else None
+    fwd_ms = [a.elapsed_time(b) for a, b, _ in marks]
+    bwd_ms = [b.elapsed_time(c) for _, b, c in marks]
+    step_ms = statistics.fmean([a.elapsed_time(c) for a, _, c in marks])
+    step_ms = max_over_ranks(step_ms, world, dev)
+    value = world * flops_all / (step_ms * 1e-3) / 1e12
+
+    # end to end through the public API: pinned host inputs in, outputs and gradients back to the host
+    outs_host = [torch.empty(B, H, Lq, D, dtype=torch.bfloat16).pin_memory() for _ in range(4)]
+    dq_, dk_, dv_ = [torch.empty(B, H, Lq, D, dtype=torch.bfloat16, device=dev) for _ in range(3)]
+
+    def e2e_step():
+        qd, kd, vd, dod = [h.to(dev, non_blocking=True) for h in host]
+        qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
+        o = P.fused_landmark_attention(qd, kd, vd, None, block_size=blk)
+        grads = torch.autograd.grad(o, [qd, kd, vd], dod)
+        for dst, src in zip(outs_host, (o.detach(), *grads)):
+            dst.copy_(src, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier(world); torch.cuda.synchronize()
+    a, b_ = ev(), ev()
+    a.record()
+    for _ in range(args.steps):
+        e2e_step()
+    b_.record()
+    torch.cuda.synchronize(); barrier(world)
+    e2e_ms = max_over_ranks(a.elapsed_time(b_) / args.steps, world, dev)
+    tensor_bytes = B * H * Lq * D * 2
+
+    extra = {}
+    if rank == 0 and not args.no_retrieval:
+        extra = bench_retrieval(P, L, dev, peaks)
+    if L.device_status() != 0:
+        raise SystemExit("device status word is non-zero after the timed region: a bounded wait expired")
+    if rank != 0:
+        return
+    fwd_avg, bwd_avg = statistics.fmean(fwd_ms), statistics.fmean(bwd_ms)
+    dominant = "backward" if bwd_avg >= fwd_avg else "forward"
+    dom_flops = (flops_all - flops_fwd) if dominant == "backward" else flops_fwd
+    dom_ms = bwd_avg if dominant == "backward" else fwd_avg
+    achieved = dom_flops / (dom_ms * 1e-3) / 1e12
+    cpu_threads = os.cpu_count() or 1
+    cpu_tf, cpu_sec = (None, None)
+    if world == 1 and not args.no_cpu_baseline:
+        cpu_tf, cpu_sec = cpu_oracle_attn(2, cpu_threads, steps=2, warmup=1)
+    line = {
+        "metric": "landmark attn fwd+bwd TFLOP/s at L=2048 D=128", "value": value, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "fused landmark attention fwd+bwd B=1 H=32 L=2048 D=128 block=64 causal, no mask "
+                               "(per GPU; (batch,head)-sharded, no collective)",
+                   "l2": "384 MB buffer written between timed steps", "flops": "7*B*H*L^2*D per step"},
+        "pct_of_bf16_peak": 100.0 * value / world / peaks["bf16_tflops"], "peak_source": peaks["source"],
+        "kernels": {"forward_ms": fwd_avg, "backward_ms": bwd_avg,
+                    "forward_tflops": flops_fwd / (fwd_avg * 1e-3) / 1e12,
+                    "backward_tflops": (flops_all - flops_fwd) / (bwd_avg * 1e-3) / 1e12},
+        "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                     "peak_source": peaks["source"]},
+        "e2e": {"value": world * flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": 4 * tensor_bytes, "d2h_bytes_per_step": 4 * tensor_bytes},
+        "gpu_launches": args.steps * 4,
+        "clocks": clocks, "wall_s": wall,
+    }
+    if cpu_tf is not None:
+        line["cpu_baseline"] = {"value": cpu_tf, "unit": "TFLOP/s", "cores": cpu_threads, "kind": "port",
+                                "sample": "CPU restatement of the reference's high-level path, 2 of 32 heads, fp32, "
+                                          f"{cpu_sec:.2f} s per pass"}
+    line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+def bench_retrieval(P, L, dev, peaks):
+    """Attention part of one layer of long-context retrieval (LLaMA-7B head shape): landmark scores, per-(head, token)
+    top-4 of 1024 cached blocks, gather of the selected KV blocks with rotary.  tok/s = raw tokens / (layers * time)."""
+    r = RETRIEVAL
+    H, D, C, blk, T, top_k = r["H"], r["D"], r["cache_len"], r["block"], r["chunk"], r["top_k"]
+    g = torch.Generator().manual_seed(7)
+    pk = torch.randn(1, H, C, D, generator=g).to(torch.bfloat16).to(dev)
+    pv = torch.randn(1, H, C, D, generator=g).to(torch.bfloat16).to(dev)
+    q = torch.randn(1, H, T, D, generator=g).to(torch.bfloat16).to(dev)
+    nblk = C // blk
+    cos, sin = P.rotary_tables_half(C + T + 1, D, torch.bfloat16, dev)
+    st = pk.stride()
+    desc = L.CacheDesc(st[0], st[1], st[2] * blk, st[2], nblk, 0, blk, top_k, C - (top_k + 1) * blk)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    flush = torch.empty(384 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    times = {"scores": [], "topk": [], "gather": []}
+    for it in range(8):
+        flush.zero_()
+        e = [ev() for _ in range(4)]
+        e[0].record()
+        scores = P.landmark_scores(q, pk, desc, cos, sin, L.ROTARY_HALF)
+        e[1].record()
+        sel = P.topk_sorted(scores, top_k)
+        e[2].record()
+        sk, sv = P.gather_kv(pk, pv, desc, desc, sel, cos, sin, L.ROTARY_HALF)
+        e[3].record()
+        torch.cuda.synchronize()
+        if it >= 3:
+            for name, (a, b) in zip(times, ((e[0], e[1]), (e[1], e[2]), (e[2], e[3]))):
+                times[name].append(a.elapsed_time(b))
+    ms = {k: statistics.fmean(v) for k, v in times.items()}
+    total_ms = sum(ms.values())
+    gather_bytes = 2 * 2 * H * T * top_k * blk * D * 2          # K and V, read + write
+    gbs = gather_bytes / (ms["gather"] * 1e-3) / 1e9
+    return {"retrieval": {
+        "metric": "retrieval attention-side tok/s (scores + top-k + gather, 32 layers)",
+        "value": r["raw_tokens"] / (r["layers"] * total_ms * 1e-3), "unit": "tok/s", "ms_per_layer": ms,
+        "config": {"workload": "H=32 D=128 cache 32768 tokens in blocks of 32, chunk 258, top-k 4 per (head, token)"},
+        "roofline": {"bound": "hbm", "kernel": "gather_kv", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]}}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-retrieval", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    world, rank, local = dist_setup(args.gpus, cpu_only=args.impl == "reference")
+    try:
+        if args.impl == "reference":
+            run_reference(args, world, rank)
+        else:
+            run_ours(args, world, rank, local)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

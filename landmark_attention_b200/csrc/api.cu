@@ -50,7 +50,7 @@ void fill(AttnParams& p, const void* q, const void* k, const void* v, int B, int
 
 // 1 = general, 2 = tcgen05, <0 = error
 int pick_path(int path, int B, int H, int Lq, int Lk, int D, int block, int dtype) {
-  const bool fast = attn_sm100_supported(B, H, Lq, Lk, D, block, dtype);
+  const bool fast = attn_sm100_supported(B, H, Lq, Lk, D, block, dtype);   // shape only; any finite scale works
   if (path == LMK_PATH_TCGEN05) {
     if (!fast)
       return fail(LMK_ERR_UNSUPPORTED,
