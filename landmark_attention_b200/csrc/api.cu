@@ -49,13 +49,14 @@ void fill(AttnParams& p, const void* q, const void* k, const void* v, int B, int
 }
 
 // 1 = general, 2 = tcgen05, <0 = error
-int pick_path(int path, int B, int H, int Lq, int Lk, int D, int block, int dtype) {
-  const bool fast = attn_sm100_supported(B, H, Lq, Lk, D, block, dtype);   // shape only; any finite scale works
+int pick_path(int path, int B, int H, int Lq, int Lk, int D, int block, int dtype, float scale) {
+  // the tcgen05 kernels take maxima on raw dot products, which needs a positive softmax scale
+  const bool fast = attn_sm100_supported(B, H, Lq, Lk, D, block, dtype) && scale > 0.f;
   if (path == LMK_PATH_TCGEN05) {
     if (!fast)
       return fail(LMK_ERR_UNSUPPORTED,
-                  "tcgen05 path needs bf16/fp16, D=128, block=64 and Lq, Lk multiples of 128 (got dtype=%d D=%d "
-                  "block=%d Lq=%d Lk=%d)", dtype, D, block, Lq, Lk);
+                  "tcgen05 path needs bf16/fp16, D=128, block=64, Lq a multiple of 128 and a positive scale (got "
+                  "dtype=%d D=%d block=%d Lq=%d Lk=%d scale=%g)", dtype, D, block, Lq, Lk, (double)scale);
     return LMK_PATH_TCGEN05;
   }
   if (path == LMK_PATH_AUTO && fast) return LMK_PATH_TCGEN05;
@@ -85,7 +86,7 @@ extern "C" int lmk_attn_fwd(const void* q, const void* k, const void* v, void* o
   int rc = check_common(q, k, v, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, block, dtype, path);
   if (rc != LMK_OK) return rc;
   LMK_CHECK_ARG(o && L && M, "attn_fwd: o, L or M is null");
-  int which = pick_path(path, B, H, Lq, Lk, D, block, dtype);
+  int which = pick_path(path, B, H, Lq, Lk, D, block, dtype, sm_scale);
   if (which < 0) return which;
   AttnParams p{};
   fill(p, q, k, v, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, block, sm_scale);
@@ -111,7 +112,7 @@ extern "C" int lmk_attn_bwd(const void* q, const void* k, const void* v, const v
   LMK_CHECK_ARG(o && dO && L && M && dQ && dK && dV, "attn_bwd: null tensor pointer");
   LMK_CHECK_ARG(Lq % block == 0 && Lk % block == 0, "Backward supported only for full blocks (Lq=%d Lk=%d block=%d)",
                 Lq, Lk, block);
-  int which = pick_path(path, B, H, Lq, Lk, D, block, dtype);
+  int which = pick_path(path, B, H, Lq, Lk, D, block, dtype, sm_scale);
   if (which < 0) return which;
   const size_t need = lmk_attn_bwd_workspace(B, H, Lq, Lk, D, block, dtype, which);
   if (need > 0 && (workspace == nullptr || workspace_bytes < need))

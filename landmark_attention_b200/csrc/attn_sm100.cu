@@ -317,6 +317,280 @@ sm100_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 }
 
 
+// ---------------------------------------------------------------------------------------------- forward, two tiles
+// Same algorithm with TWO adjacent 128-row query tiles per CTA (one CTA per SM): softmax warpgroup 0 owns tile A
+// (rows 256u .. 256u+127), warpgroup 1 owns tile B (the next 128 rows).  Both tiles consume the same K/V stream, so
+// every K/V block is fetched from L2 once per 256 query rows, and the two softmax pipelines overlap with each
+// other and with the MMAs.  Tile A skips the two newest key blocks (they lie after its own blocks).
+constexpr int kFwd2Stages = 4;
+constexpr int kFwd2Threads = 320;
+enum { kErrFwd2Producer = 111, kErrFwd2Mma = 112, kErrFwd2Softmax = 113, kErrFwd2Epilogue = 114 };
+
+struct Fwd2Smem {
+  uint64_t q_full;
+  uint64_t full[kFwd2Stages];
+  uint64_t empty[kFwd2Stages];
+  uint64_t s_full[2][2];    // [tile][S buffer]
+  uint64_t s_free[2][2];
+  uint64_t p_ready[2];
+  uint64_t p_free[2];
+  uint64_t o_full;
+  uint32_t tmem_base;
+};
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kFwd2Threads, 1)
+sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_klm,
+                  void* __restrict__ o_ptr, float* __restrict__ L_ptr, float* __restrict__ M_ptr, int H, int Lq, int Lk,
+                  int lm_box, float scale_log2) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  auto q_tile = [&](int w) { return base + (uint32_t)w * 32768u; };
+  auto k_slot = [&](int s) { return base + 65536u + (uint32_t)s * 32768u; };
+  auto v_slot = [&](int s) { return base + 65536u + (uint32_t)s * 32768u + 16384u; };
+  auto p_tile = [&](int w) { return base + 65536u + kFwd2Stages * 32768u + (uint32_t)w * 16384u; };
+  Fwd2Smem* sm = reinterpret_cast<Fwd2Smem*>(smem_raw + (base - raw) + 65536u + kFwd2Stages * 32768u + 32768u);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_pairs = Lq / (2 * kQTile);
+  const int u = n_pairs - 1 - (int)blockIdx.x;          // heaviest pairs first
+  const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
+  const int prefix_blocks = (Lk - Lq) / kBlk;
+  const int own0_a = prefix_blocks + 4 * u;             // tile A: blocks own0_a, own0_a+1; tile B: +2, +3
+  const int n_last = own0_a + 3;                        // newest block of the pair
+  const int n_lm_tiles = (n_last + 63) / 64;            // landmarks 0 .. n_last-1
+  const int total = n_lm_tiles + n_last + 1;
+  // tile A takes part in item i unless it is one of the first two main items
+  auto active = [&](int w, int i) { return w == 1 || i < n_lm_tiles || i >= n_lm_tiles + 2; };
+
+  if (tid == 0) {
+    mbar_init(smem_u32(&sm->q_full), 1);
+    for (int s = 0; s < kFwd2Stages; ++s) {
+      mbar_init(smem_u32(&sm->full[s]), 1);
+      mbar_init(smem_u32(&sm->empty[s]), 1);
+    }
+    for (int w = 0; w < 2; ++w) {
+      for (int s = 0; s < 2; ++s) {
+        mbar_init(smem_u32(&sm->s_full[w][s]), 1);
+        mbar_init(smem_u32(&sm->s_free[w][s]), 128);
+      }
+      mbar_init(smem_u32(&sm->p_ready[w]), 128);
+      mbar_init(smem_u32(&sm->p_free[w]), 1);
+    }
+    mbar_init(smem_u32(&sm->o_full), 1);
+    mbar_init_fence();
+  }
+  if (warp == 9) tmem_alloc(smem_u32(&sm->tmem_base), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm->tmem_base;
+  auto tmem_s = [&](int w, int sb) { return tmem + (uint32_t)(w * 128 + sb * 64); };
+  auto tmem_o = [&](int w) { return tmem + 256u + (uint32_t)w * 128u; };
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&tm_q);
+      prefetch_tensormap(&tm_k);
+      prefetch_tensormap(&tm_v);
+      prefetch_tensormap(&tm_klm);
+      const uint32_t qb = smem_u32(&sm->q_full);
+      mbar_arrive_expect_tx(qb, 4 * kTileBytes);
+      for (int w = 0; w < 2; ++w) {
+        tma_load_4d(q_tile(w), &tm_q, qb, 0, (2 * u + w) * kQTile, h, b);
+        tma_load_4d(q_tile(w) + kTileBytes, &tm_q, qb, 64, (2 * u + w) * kQTile, h, b);
+      }
+      for (int i = 0; i < total; ++i) {
+        const int s = i % kFwd2Stages;
+        mbar_wait(smem_u32(&sm->empty[s]), ((i / kFwd2Stages) & 1) ^ 1, &g_lmk_status, kErrFwd2Producer);
+        const uint32_t fb = smem_u32(&sm->full[s]);
+        if (i < n_lm_tiles) {
+          mbar_arrive_expect_tx(fb, (uint32_t)lm_box * 256u);
+          tma_load_5d(k_slot(s), &tm_klm, fb, 0, kBlk - 1, i * 64, h, b);
+          tma_load_5d(k_slot(s) + kHalfTile, &tm_klm, fb, 64, kBlk - 1, i * 64, h, b);
+        } else {
+          const int n = n_last - (i - n_lm_tiles);
+          mbar_arrive_expect_tx(fb, 2 * kTileBytes);
+          tma_load_4d(k_slot(s), &tm_k, fb, 0, n * kBlk, h, b);
+          tma_load_4d(k_slot(s) + kHalfTile, &tm_k, fb, 64, n * kBlk, h, b);
+          tma_load_4d(v_slot(s), &tm_v, fb, 0, n * kBlk, h, b);
+          tma_load_4d(v_slot(s) + kHalfTile, &tm_v, fb, 64, n * kBlk, h, b);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t fmt = kBf16 ? 1u : 0u;
+      constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);
+      constexpr uint32_t idesc_o = instr_desc_f16(fmt, 128, 128, 0, 1);
+      mbar_wait(smem_u32(&sm->q_full), 0, &g_lmk_status, kErrFwd2Mma);
+      int ks[2] = {0, 0};      // S MMAs issued per tile
+      int kp[2] = {0, 0};      // items retired per tile
+      auto issue_s = [&](int j) {
+        const int s = j % kFwd2Stages;
+        mbar_wait(smem_u32(&sm->full[s]), (j / kFwd2Stages) & 1, &g_lmk_status, kErrFwd2Mma);
+        for (int w = 0; w < 2; ++w) {
+          if (!active(w, j)) continue;
+          const int k = ks[w]++, sb = k & 1;
+          if (k >= 2) mbar_wait(smem_u32(&sm->s_free[w][sb]), ((k / 2) & 1) ^ 1, &g_lmk_status, kErrFwd2Mma);
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < kD / 16; ++kk) {
+            const uint32_t qa = q_tile(w) + (kk >> 2) * kTileBytes + (kk & 3) * 32;
+            const uint32_t ka = k_slot(s) + (kk >> 2) * kHalfTile + (kk & 3) * 32;
+            mma_f16_ss(tmem_s(w, sb), smem_desc_sw128(qa, 16, 1024), smem_desc_sw128(ka, 16, 1024), idesc_s, kk > 0);
+          }
+          mma_commit(smem_u32(&sm->s_full[w][sb]));
+        }
+      };
+      issue_s(0);
+      bool o_started[2] = {false, false};
+      for (int i = 0; i < total; ++i) {
+        if (i + 1 < total) issue_s(i + 1);
+        const int s = i % kFwd2Stages;
+        for (int w = 0; w < 2; ++w) {
+          if (!active(w, i)) continue;
+          const int k = kp[w]++;
+          mbar_wait(smem_u32(&sm->p_ready[w]), k & 1, &g_lmk_status, kErrFwd2Mma);
+          tc_fence_after();
+          if (i >= n_lm_tiles) {
+#pragma unroll
+            for (int kk = 0; kk < kBlk / 16; ++kk)
+              mma_f16_ss(tmem_o(w), smem_desc_sw128(p_tile(w) + kk * 32, 16, 1024),
+                         smem_desc_sw128(v_slot(s) + kk * 2048, kHalfTile, 1024), idesc_o,
+                         (o_started[w] || kk > 0) ? 1u : 0u);
+            o_started[w] = true;
+          }
+          mma_commit(smem_u32(&sm->p_free[w]));
+        }
+        mma_commit(smem_u32(&sm->empty[s]));
+      }
+      mma_commit(smem_u32(&sm->o_full));
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups
+    const int w = warp >> 2;                       // 0: tile A, 1: tile B
+    const int row = tid & 127;
+    const int half = row >> 6;
+    const int own = own0_a + 2 * w + half;
+    const int vis = min(row & 63, kBlk - 2);
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    float m2 = -INFINITY, l = 0.f;
+    int k = 0;
+    for (int i = 0; i < total; ++i) {
+      if (!active(w, i)) continue;
+      const int sb = k & 1;
+      mbar_wait(smem_u32(&sm->s_full[w][sb]), (k / 2) & 1, &g_lmk_status, kErrFwd2Softmax);
+      tc_fence_after();
+      float sv[64];
+      {
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32b_x32(tmem_s(w, sb) + lane_base, ra);
+        tmem_ld_32x32b_x32(tmem_s(w, sb) + 32 + lane_base, rb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          sv[j] = __uint_as_float(ra[j]);
+          sv[32 + j] = __uint_as_float(rb[j]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sm->s_free[w][sb]));
+      uint32_t wgt[32];
+      bool write_p = false;
+      if (i < n_lm_tiles) {
+        const int first = i * 64;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          if (first + j < own) mx = fmaxf(mx, sv[j]);
+        m2 = fmaxf(m2, mx * scale_log2);
+      } else {
+        const int n = n_last - (i - n_lm_tiles);
+        write_p = true;
+        if (n > own) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) wgt[j] = 0u;
+        } else if (n == own) {
+          float mx = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 64; ++j)
+            if (j <= vis) mx = fmaxf(mx, sv[j]);
+          m2 = fmaxf(m2, mx * scale_log2);
+          float sum = 0.f;
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            sv[j] = (j <= vis) ? ex2(fmaf(sv[j], scale_log2, -m2)) : 0.f;
+            sum += sv[j];
+          }
+          l += sum;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) wgt[j] = pack2<kBf16>(sv[2 * j], sv[2 * j + 1]);
+        } else {
+          float mx = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 63; ++j) mx = fmaxf(mx, sv[j]);
+          const float nmx = -mx * scale_log2;
+          const float el = ex2(fmaf(sv[63], scale_log2, -m2));
+          float den = 0.f;
+#pragma unroll
+          for (int j = 0; j < 63; ++j) {
+            sv[j] = ex2(fmaf(sv[j], scale_log2, nmx));
+            den += sv[j];
+          }
+          l += el;
+          const float wg = __fdividef(el, den);
+          sv[63] = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) wgt[j] = pack2<kBf16>(sv[2 * j] * wg, sv[2 * j + 1] * wg);
+        }
+      }
+      if (k > 0) mbar_wait(smem_u32(&sm->p_free[w]), (k - 1) & 1, &g_lmk_status, kErrFwd2Softmax);
+      if (write_p) {
+        store_row_sw128(p_tile(w), row, wgt);
+        fence_proxy_async_smem();
+      }
+      mbar_arrive(smem_u32(&sm->p_ready[w]));
+      ++k;
+    }
+    // ------------------------------------------------------------------ epilogue
+    mbar_wait(smem_u32(&sm->o_full), 0, &g_lmk_status, kErrFwd2Epilogue);
+    tc_fence_after();
+    const float inv = 1.f / l;
+    const int grow = (2 * u + w) * kQTile + row;
+    uint4* orow = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(o_ptr) + ((int64_t)bh * Lq + grow) * kD);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(tmem_o(w) + c * 32 + lane_base, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int v4 = 0; v4 < 4; ++v4) {
+        uint4 pk;
+        pk.x = pack2<kBf16>(__uint_as_float(r[8 * v4 + 0]) * inv, __uint_as_float(r[8 * v4 + 1]) * inv);
+        pk.y = pack2<kBf16>(__uint_as_float(r[8 * v4 + 2]) * inv, __uint_as_float(r[8 * v4 + 3]) * inv);
+        pk.z = pack2<kBf16>(__uint_as_float(r[8 * v4 + 4]) * inv, __uint_as_float(r[8 * v4 + 5]) * inv);
+        pk.w = pack2<kBf16>(__uint_as_float(r[8 * v4 + 6]) * inv, __uint_as_float(r[8 * v4 + 7]) * inv);
+        orow[c * 4 + v4] = pk;
+      }
+    }
+    L_ptr[(int64_t)bh * Lq + grow] = l;
+    M_ptr[(int64_t)bh * Lq + grow] = m2 * (1.f / kLog2e);
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- backward: delta
 template <bool kBf16>
 __global__ void __launch_bounds__(256) sm100_delta_kernel(const uint2* __restrict__ o, const uint2* __restrict__ dO,
@@ -808,8 +1082,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // Driver-API calls need the device's primary context current on the calling thread; autograd worker threads
-// arrive here before any runtime call has bound it.
-inline void bind_context() { (void)cudaFree(nullptr); }
+// arrive here before any runtime call has bound it.  cudaSetDevice binds it without synchronising the device.
+inline void bind_context() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) (void)cudaSetDevice(dev);
+}
 
 EncodeTiledFn get_encode() {
   static EncodeTiledFn fn = nullptr;
@@ -877,17 +1154,31 @@ int attn_sm100_fwd(const AttnParams& p, int dtype, cudaStream_t st) {
   if ((rc = make_map_4d(&tv, p.v, dtype, p.B, p.H, p.Lk, p.vs, kBlk)) != LMK_OK) return rc;
   const int lm_box = (p.Lk / kBlk) < 64 ? (p.Lk / kBlk) : 64;
   if ((rc = make_map_landmarks(&tl, p.k, dtype, p.B, p.H, p.Lk, p.ks, lm_box)) != LMK_OK) return rc;
-  const size_t smem = 1024 + 32768 + kFwdStages * 32768 + sizeof(FwdSmem);
-  dim3 grid(p.Lq / kQTile, p.B * p.H);
   const float scale_log2 = p.scale * kLog2e;
-  if (dtype == LMK_BF16) {
-    LMK_CUDA(cudaFuncSetAttribute(sm100_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    sm100_fwd_kernel<true><<<grid, kFwdThreads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk, lm_box,
-                                                             scale_log2);
+  if (p.Lq % (2 * kQTile) == 0) {
+    const size_t smem = 1024 + 65536 + kFwd2Stages * 32768 + 32768 + sizeof(Fwd2Smem);
+    dim3 grid(p.Lq / (2 * kQTile), p.B * p.H);
+    if (dtype == LMK_BF16) {
+      LMK_CUDA(cudaFuncSetAttribute(sm100_fwd2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      sm100_fwd2_kernel<true><<<grid, kFwd2Threads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk,
+                                                                lm_box, scale_log2);
+    } else {
+      LMK_CUDA(cudaFuncSetAttribute(sm100_fwd2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      sm100_fwd2_kernel<false><<<grid, kFwd2Threads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk,
+                                                                 lm_box, scale_log2);
+    }
   } else {
-    LMK_CUDA(cudaFuncSetAttribute(sm100_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    sm100_fwd_kernel<false><<<grid, kFwdThreads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk, lm_box,
-                                                             scale_log2);
+    const size_t smem = 1024 + 32768 + kFwdStages * 32768 + sizeof(FwdSmem);
+    dim3 grid(p.Lq / kQTile, p.B * p.H);
+    if (dtype == LMK_BF16) {
+      LMK_CUDA(cudaFuncSetAttribute(sm100_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      sm100_fwd_kernel<true><<<grid, kFwdThreads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk, lm_box,
+                                                              scale_log2);
+    } else {
+      LMK_CUDA(cudaFuncSetAttribute(sm100_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      sm100_fwd_kernel<false><<<grid, kFwdThreads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk, lm_box,
+                                                               scale_log2);
+    }
   }
   LMK_CUDA(cudaGetLastError());
   return LMK_OK;

@@ -1,0 +1,81 @@
+"""Kernel-level timing of the fused attention entry points through the C ABI (no autograd, no allocation in the loop).
+
+    python -m landmark_attention_b200.kernel_bench --L 2048 --B 1 --H 32 [--path 2] [--iters 30] [--only fwd|bwd]
+
+Prints one line with the average device time of lmk_attn_fwd and lmk_attn_bwd (CUDA events around back-to-back
+calls) and the algorithmic TFLOP/s (2*B*H*L^2*D forward, 5*B*H*L^2*D backward).  This is the command the ncu
+summaries under profiles/ were captured with.
+"""
+import argparse
+
+import torch
+
+from . import _lib as L
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--L", type=int, default=2048)
+    ap.add_argument("--B", type=int, default=1)
+    ap.add_argument("--H", type=int, default=32)
+    ap.add_argument("--D", type=int, default=128)
+    ap.add_argument("--block", type=int, default=64)
+    ap.add_argument("--path", type=int, default=L.PATH_AUTO)
+    ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--only", default="both", choices=["both", "fwd", "bwd"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
+    a = ap.parse_args()
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[a.dtype]
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(0)
+    B, H, Lq, D = a.B, a.H, a.L, a.D
+    q, k, v = [(torch.randn(B, H, Lq, D, generator=g) * 0.5).to(dt).to(dev) for _ in range(3)]
+    do = torch.randn(B, H, Lq, D, generator=g).to(dt).to(dev)
+    o = torch.empty_like(q)
+    l = torch.empty(B * H, Lq, device=dev)
+    m = torch.empty(B * H, Lq, device=dev)
+    dq, dk, dv = [torch.empty_like(q) for _ in range(3)]
+    lib = L.lib()
+    code = L.dtype_code(q)
+    need = lib.lmk_attn_bwd_workspace(B, H, Lq, Lq, D, a.block, code, a.path)
+    ws = torch.empty(max(int(need), 256), dtype=torch.uint8, device=dev)
+    st, s3 = L.stream_ptr(dev), L.strides3(q)
+    scale = D ** -0.5
+
+    def fwd():
+        L.check(lib.lmk_attn_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(l), L.ptr(m), B, H, Lq, Lq, D, s3, s3, s3,
+                                 a.block, scale, code, a.path, st), "lmk_attn_fwd")
+
+    def bwd():
+        L.check(lib.lmk_attn_bwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(o), L.ptr(do), L.ptr(l), L.ptr(m), L.ptr(dq),
+                                 L.ptr(dk), L.ptr(dv), L.ptr(ws), ws.numel(), B, H, Lq, Lq, D, s3, s3, s3, a.block,
+                                 scale, code, a.path, st), "lmk_attn_bwd")
+
+    def timeit(f):
+        for _ in range(a.warmup):
+            f()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.iters):
+            f()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / a.iters * 1e3
+
+    fwd()
+    fl = B * H * Lq * Lq * D
+    parts = [f"B={B} H={H} L={Lq} D={D} {a.dtype}"]
+    if a.only in ("both", "fwd"):
+        t = timeit(fwd)
+        parts.append(f"fwd {t:.1f} us ({2 * fl / t / 1e6:.0f} TFLOP/s)")
+    if a.only in ("both", "bwd"):
+        t = timeit(bwd)
+        parts.append(f"bwd {t:.1f} us ({5 * fl / t / 1e6:.0f} TFLOP/s)")
+    parts.append(f"status {L.device_status()}")
+    print("  ".join(parts))
+
+
+if __name__ == "__main__":
+    main()
