@@ -8,7 +8,8 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 
 import torch
 
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libb200lmk.so")
+LIB_PATH = os.environ.get("B200LMK_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib",
+                                                          "libb200lmk.so")
 
 LMK_F32, LMK_F16, LMK_BF16 = 0, 1, 2
 LMK_OK, LMK_ERR_INVALID, LMK_ERR_UNSUPPORTED, LMK_ERR_CUDA, LMK_ERR_WORKSPACE, LMK_ERR_DEVICE = 0, -1, -2, -3, -4, -5

@@ -35,6 +35,14 @@ namespace lmk {
 
 __device__ int g_lmk_status = 0;   // first bounded wait that expired (0 = none); see lmk_device_status()
 
+#ifdef LMK_TRACE
+__device__ long long* g_trace = nullptr;   // development aid: per-item clock64 stamps of CTA (0,0)
+#define LMK_STAMP(slot, item) \
+  do { if (g_trace && blockIdx.x == 0 && blockIdx.y == 0 && (item) < 64) g_trace[(slot) * 64 + (item)] = clock64(); } while (0)
+#else
+#define LMK_STAMP(slot, item) do { } while (0)
+#endif
+
 namespace {
 
 using namespace ptx;
@@ -84,6 +92,48 @@ __device__ __forceinline__ void store_row_sw128(uint32_t tile_base, int row, con
                  "r"(w[4 * c + 2]), "r"(w[4 * c + 3])
                  : "memory");
   }
+}
+
+// Row reductions with four independent chains: one softmax thread has little other work in flight, so a single
+// 63-deep dependent chain of max / add would expose the ALU latency on every step.
+template <int N>
+__device__ __forceinline__ float row_max(const float (&v)[64]) {
+  float a = -INFINITY, b = -INFINITY, c = -INFINITY, d = -INFINITY;
+#pragma unroll
+  for (int j = 0; j + 3 < N; j += 4) {
+    a = fmaxf(a, v[j]);
+    b = fmaxf(b, v[j + 1]);
+    c = fmaxf(c, v[j + 2]);
+    d = fmaxf(d, v[j + 3]);
+  }
+#pragma unroll
+  for (int j = N & ~3; j < N; ++j) a = fmaxf(a, v[j]);
+  return fmaxf(fmaxf(a, b), fmaxf(c, d));
+}
+__device__ __forceinline__ float row_max_upto(const float (&v)[64], int last) {
+  float a = -INFINITY, b = -INFINITY, c = -INFINITY, d = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 64; j += 4) {
+    a = fmaxf(a, j <= last ? v[j] : -INFINITY);
+    b = fmaxf(b, j + 1 <= last ? v[j + 1] : -INFINITY);
+    c = fmaxf(c, j + 2 <= last ? v[j + 2] : -INFINITY);
+    d = fmaxf(d, j + 3 <= last ? v[j + 3] : -INFINITY);
+  }
+  return fmaxf(fmaxf(a, b), fmaxf(c, d));
+}
+template <int N>
+__device__ __forceinline__ float row_sum(const float (&v)[64]) {
+  float a = 0.f, b = 0.f, c = 0.f, d = 0.f;
+#pragma unroll
+  for (int j = 0; j + 3 < N; j += 4) {
+    a += v[j];
+    b += v[j + 1];
+    c += v[j + 2];
+    d += v[j + 3];
+  }
+#pragma unroll
+  for (int j = N & ~3; j < N; ++j) a += v[j];
+  return (a + b) + (c + d);
 }
 
 template <bool kBf16>
@@ -170,19 +220,20 @@ sm100_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);    // S = Q K^T
       constexpr uint32_t idesc_o = instr_desc_f16(fmt, 128, 128, 0, 1);   // O += P V   (V is MN-major)
       mbar_wait(smem_u32(&sm->q_full), 0, &g_lmk_status, kErrFwdMma);
+      // Q and K: two 64-column sub-tiles; a K-step of 16 elements is 32 bytes inside the swizzle atom
+      const uint64_t dq = smem_desc_sw128(q_tile, 16, 1024);
+      const uint64_t dk0 = smem_desc_sw128(k_slot(0), 16, 1024);
+      const uint64_t dv0 = smem_desc_sw128(v_slot(0), kHalfTile, 1024);
       auto issue_s = [&](int j) {
         const int s = j % kFwdStages, sb = j & 1;
         mbar_wait(smem_u32(&sm->full[s]), (j / kFwdStages) & 1, &g_lmk_status, kErrFwdMma);
         if (j >= 2) mbar_wait(smem_u32(&sm->s_free[sb]), ((j / 2) & 1) ^ 1, &g_lmk_status, kErrFwdMma);
         tc_fence_after();
+        const uint64_t dk = desc_advance(dk0, (uint32_t)s * 32768u);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
-          // Q and K: two 64-column sub-tiles; a K-step of 16 elements is 32 bytes inside the swizzle atom
-          const uint32_t qa = q_tile + (kk >> 2) * kTileBytes + (kk & 3) * 32;
-          const uint32_t ka = k_slot(s) + (kk >> 2) * kHalfTile + (kk & 3) * 32;
-          mma_f16_ss(tmem_s0 + sb * 64, smem_desc_sw128(qa, 16, 1024), smem_desc_sw128(ka, 16, 1024), idesc_s,
-                     kk > 0);
-        }
+        for (int kk = 0; kk < kD / 16; ++kk)
+          mma_f16_ss(tmem_s0 + sb * 64, desc_advance(dq, kmajor_step(kk, kTileBytes)),
+                     desc_advance(dk, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
         mma_commit(smem_u32(&sm->s_full[sb]));
       };
       issue_s(0);
@@ -193,15 +244,14 @@ sm100_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         mbar_wait(smem_u32(&sm->p_ready[s]), (i / kFwdStages) & 1, &g_lmk_status, kErrFwdMma);
         tc_fence_after();
         if (i >= n_lm_tiles) {
+          // P: [128 x 64] K-major tile in the K slot.  V: two [64 keys x 64 features] sub-tiles, MN-major:
+          // 8-key groups 1024 B apart (SBO), the second 64-feature half 8192 B further (LBO); 16 keys = 2048 B.
+          const uint64_t dp = desc_advance(dk0, (uint32_t)s * 32768u);
+          const uint64_t dv = desc_advance(dv0, (uint32_t)s * 32768u);
 #pragma unroll
-          for (int kk = 0; kk < kBlk / 16; ++kk) {
-            // P: [128 x 64] K-major tile in the K slot.  V: two [64 keys x 64 features] sub-tiles, MN-major:
-            // 8-key groups 1024 B apart (SBO), the second 64-feature half 8192 B further (LBO); 16 keys = 2048 B.
-            const uint32_t pa = k_slot(s) + kk * 32;
-            const uint32_t va = v_slot(s) + kk * 2048;
-            mma_f16_ss(tmem_o, smem_desc_sw128(pa, 16, 1024), smem_desc_sw128(va, kHalfTile, 1024), idesc_o,
+          for (int kk = 0; kk < kBlk / 16; ++kk)
+            mma_f16_ss(tmem_o, desc_advance(dp, kk * 32), desc_advance(dv, kk * 2048), idesc_o,
                        (o_started || kk > 0) ? 1u : 0u);
-          }
           o_started = true;
         }
         mma_commit(smem_u32(&sm->empty[s]));
@@ -323,7 +373,7 @@ sm100_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 // every K/V block is fetched from L2 once per 256 query rows, and the two softmax pipelines overlap with each
 // other and with the MMAs.  Tile A skips the two newest key blocks (they lie after its own blocks).
 constexpr int kFwd2Stages = 4;
-constexpr int kFwd2Threads = 320;
+constexpr int kFwd2Threads = 352;
 enum { kErrFwd2Producer = 111, kErrFwd2Mma = 112, kErrFwd2Softmax = 113, kErrFwd2Epilogue = 114 };
 
 struct Fwd2Smem {
@@ -423,52 +473,69 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
     __syncwarp();
   } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ MMA issuer 1: S = Q K^T
+    // Two issuer threads keep the scalar bookkeeping between tcgen05.mma instructions short, and the S MMAs of the
+    // next key block never queue behind a wait for the softmax of the current one.
     if (lane == 0) {
       constexpr uint32_t fmt = kBf16 ? 1u : 0u;
       constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);
-      constexpr uint32_t idesc_o = instr_desc_f16(fmt, 128, 128, 0, 1);
       mbar_wait(smem_u32(&sm->q_full), 0, &g_lmk_status, kErrFwd2Mma);
-      int ks[2] = {0, 0};      // S MMAs issued per tile
-      int kp[2] = {0, 0};      // items retired per tile
-      auto issue_s = [&](int j) {
-        const int s = j % kFwd2Stages;
-        mbar_wait(smem_u32(&sm->full[s]), (j / kFwd2Stages) & 1, &g_lmk_status, kErrFwd2Mma);
+      const uint64_t dq0 = smem_desc_sw128(q_tile(0), 16, 1024);
+      const uint64_t dk0 = smem_desc_sw128(k_slot(0), 16, 1024);
+      int ks[2] = {0, 0};
+      int s = 0;
+      uint32_t ph = 0;
+      for (int j = 0; j < total; ++j) {
+        mbar_wait(smem_u32(&sm->full[s]), ph, &g_lmk_status, kErrFwd2Mma);
+        const uint64_t dk = desc_advance(dk0, (uint32_t)s * 32768u);
+#pragma unroll
         for (int w = 0; w < 2; ++w) {
           if (!active(w, j)) continue;
           const int k = ks[w]++, sb = k & 1;
-          if (k >= 2) mbar_wait(smem_u32(&sm->s_free[w][sb]), ((k / 2) & 1) ^ 1, &g_lmk_status, kErrFwd2Mma);
+          if (k >= 2) mbar_wait(smem_u32(&sm->s_free[w][sb]), ((k >> 1) & 1) ^ 1, &g_lmk_status, kErrFwd2Mma);
           tc_fence_after();
+          const uint64_t dq = desc_advance(dq0, (uint32_t)w * 32768u);
 #pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk) {
-            const uint32_t qa = q_tile(w) + (kk >> 2) * kTileBytes + (kk & 3) * 32;
-            const uint32_t ka = k_slot(s) + (kk >> 2) * kHalfTile + (kk & 3) * 32;
-            mma_f16_ss(tmem_s(w, sb), smem_desc_sw128(qa, 16, 1024), smem_desc_sw128(ka, 16, 1024), idesc_s, kk > 0);
-          }
+          for (int kk = 0; kk < kD / 16; ++kk)
+            mma_f16_ss(tmem_s(w, sb), desc_advance(dq, kmajor_step(kk, kTileBytes)),
+                       desc_advance(dk, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
           mma_commit(smem_u32(&sm->s_full[w][sb]));
         }
-      };
-      issue_s(0);
+        if (++s == kFwd2Stages) { s = 0; ph ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ MMA issuer 2: O += P V
+    if (lane == 0) {
+      constexpr uint32_t fmt = kBf16 ? 1u : 0u;
+      constexpr uint32_t idesc_o = instr_desc_f16(fmt, 128, 128, 0, 1);
+      const uint64_t dv0 = smem_desc_sw128(v_slot(0), kHalfTile, 1024);
+      const uint64_t dp0 = smem_desc_sw128(p_tile(0), 16, 1024);
+      int kp[2] = {0, 0};
       bool o_started[2] = {false, false};
+      int s = 0;
       for (int i = 0; i < total; ++i) {
-        if (i + 1 < total) issue_s(i + 1);
-        const int s = i % kFwd2Stages;
+        const uint64_t dv = desc_advance(dv0, (uint32_t)s * 32768u);
+#pragma unroll
         for (int w = 0; w < 2; ++w) {
           if (!active(w, i)) continue;
           const int k = kp[w]++;
           mbar_wait(smem_u32(&sm->p_ready[w]), k & 1, &g_lmk_status, kErrFwd2Mma);
           tc_fence_after();
           if (i >= n_lm_tiles) {
+            const uint64_t dp = desc_advance(dp0, (uint32_t)w * 16384u);
 #pragma unroll
             for (int kk = 0; kk < kBlk / 16; ++kk)
-              mma_f16_ss(tmem_o(w), smem_desc_sw128(p_tile(w) + kk * 32, 16, 1024),
-                         smem_desc_sw128(v_slot(s) + kk * 2048, kHalfTile, 1024), idesc_o,
+              mma_f16_ss(tmem_o(w), desc_advance(dp, kk * 32), desc_advance(dv, kk * 2048), idesc_o,
                          (o_started[w] || kk > 0) ? 1u : 0u);
             o_started[w] = true;
           }
           mma_commit(smem_u32(&sm->p_free[w]));
         }
+        // the stage is free once both P V products are done; each of them waited for its S product to be read
         mma_commit(smem_u32(&sm->empty[s]));
+        if (++s == kFwd2Stages) s = 0;
       }
       mma_commit(smem_u32(&sm->o_full));
     }
@@ -486,7 +553,9 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int i = 0; i < total; ++i) {
       if (!active(w, i)) continue;
       const int sb = k & 1;
+      if (row == 0) LMK_STAMP(w * 5 + 0, k);
       mbar_wait(smem_u32(&sm->s_full[w][sb]), (k / 2) & 1, &g_lmk_status, kErrFwd2Softmax);
+      if (row == 0) LMK_STAMP(w * 5 + 1, k);
       tc_fence_after();
       float sv[64];
       {
@@ -505,12 +574,7 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t wgt[32];
       bool write_p = false;
       if (i < n_lm_tiles) {
-        const int first = i * 64;
-        float mx = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < 64; ++j)
-          if (first + j < own) mx = fmaxf(mx, sv[j]);
-        m2 = fmaxf(m2, mx * scale_log2);
+        m2 = fmaxf(m2, row_max_upto(sv, own - 1 - i * 64) * scale_log2);
       } else {
         const int n = n_last - (i - n_lm_tiles);
         write_p = true;
@@ -518,45 +582,43 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 32; ++j) wgt[j] = 0u;
         } else if (n == own) {
-          float mx = -INFINITY;
+          m2 = fmaxf(m2, row_max_upto(sv, vis) * scale_log2);
 #pragma unroll
-          for (int j = 0; j < 64; ++j)
-            if (j <= vis) mx = fmaxf(mx, sv[j]);
-          m2 = fmaxf(m2, mx * scale_log2);
-          float sum = 0.f;
-#pragma unroll
-          for (int j = 0; j < 64; ++j) {
-            sv[j] = (j <= vis) ? ex2(fmaf(sv[j], scale_log2, -m2)) : 0.f;
-            sum += sv[j];
-          }
-          l += sum;
+          for (int j = 0; j < 64; ++j) sv[j] = (j <= vis) ? ex2(fmaf(sv[j], scale_log2, -m2)) : 0.f;
+          l += row_sum<64>(sv);
 #pragma unroll
           for (int j = 0; j < 32; ++j) wgt[j] = pack2<kBf16>(sv[2 * j], sv[2 * j + 1]);
         } else {
-          float mx = -INFINITY;
+#ifdef LMK_EXP_NOCOMPUTE
 #pragma unroll
-          for (int j = 0; j < 63; ++j) mx = fmaxf(mx, sv[j]);
-          const float nmx = -mx * scale_log2;
+          for (int j = 0; j < 32; ++j) wgt[j] = __float_as_uint(sv[2 * j] + sv[2 * j + 1]);
+          l += 1.f;
+          if (false) {
+#endif
+          const float nmx = -row_max<63>(sv) * scale_log2;
           const float el = ex2(fmaf(sv[63], scale_log2, -m2));
-          float den = 0.f;
 #pragma unroll
-          for (int j = 0; j < 63; ++j) {
-            sv[j] = ex2(fmaf(sv[j], scale_log2, nmx));
-            den += sv[j];
-          }
+          for (int j = 0; j < 63; ++j) sv[j] = ex2(fmaf(sv[j], scale_log2, nmx));
+          const float den = row_sum<63>(sv);
           l += el;
           const float wg = __fdividef(el, den);
           sv[63] = 0.f;
 #pragma unroll
           for (int j = 0; j < 32; ++j) wgt[j] = pack2<kBf16>(sv[2 * j] * wg, sv[2 * j + 1] * wg);
+#ifdef LMK_EXP_NOCOMPUTE
+          }
+#endif
         }
       }
+      if (row == 0) LMK_STAMP(w * 5 + 2, k);
       if (k > 0) mbar_wait(smem_u32(&sm->p_free[w]), (k - 1) & 1, &g_lmk_status, kErrFwd2Softmax);
+      if (row == 0) LMK_STAMP(w * 5 + 3, k);
       if (write_p) {
         store_row_sw128(p_tile(w), row, wgt);
         fence_proxy_async_smem();
       }
       mbar_arrive(smem_u32(&sm->p_ready[w]));
+      if (row == 0) LMK_STAMP(w * 5 + 4, k);
       ++k;
     }
     // ------------------------------------------------------------------ epilogue
@@ -617,49 +679,111 @@ __global__ void __launch_bounds__(256) sm100_delta_kernel(const uint2* __restric
   if (lane == 0) delta[row] = acc;
 }
 
-// Weights of one (query row, key block) pair from the raw scores S and dP = dO . V^T.
-//   kind 0: block after the row's own block -> everything zero
-//   kind 1: own block (causal, landmark hidden);  kind 2: earlier block (grouped)
-// Outputs: ds[] (always) and p[] (when kNeedP) as fp32 in place of sv[] / dp[].
-template <bool kNeedP>
-__device__ __forceinline__ void bwd_weights(float (&sv)[64], float (&dp)[64], int kind, int vis, float scale_log2,
-                                            float scale, float M2, float Linv, float delta) {
+// One (query row, key block) pair of the backward pass, staged to keep the softmax threads below 168 registers
+// (so that two softmax warpgroups fit): S is read once, dP twice (once to reduce nD = sum_j s_j dP_j, once to form dS),
+// and each result row is stored as soon as it is complete.
+//   kind 0: block after the row's own block -> zeros;  kind 1: own block (causal, landmark hidden);
+//   kind 2: earlier block (grouped).
+// Writes the P row (kNeedP) into p_dst and the dS row into ds_dst ([128 x 64] 128B-swizzled tiles), arrives on
+// `free_bar` once the TMEM buffer has been read for the last time, and calls wait_dst() before the first store.
+__device__ __forceinline__ void store_half_row_sw128(uint32_t tile_base, int row, int half, const uint32_t (&w)[16]) {
+  const uint32_t row_addr = tile_base + row * 128;
 #pragma unroll
-  for (int j = 0; j < 64; ++j) sv[j] *= scale_log2;
+  for (int c = 0; c < 4; ++c) {
+    uint32_t addr = row_addr + (((half * 4 + c) ^ (row & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * c]), "r"(w[4 * c + 1]),
+                 "r"(w[4 * c + 2]), "r"(w[4 * c + 3])
+                 : "memory");
+  }
+}
+
+template <bool kBf16, bool kNeedP, typename WaitFn>
+__device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t free_bar, int kind, int vis, float c,
+                                         float scale, float M2, float Linv, float delta, uint32_t p_dst,
+                                         uint32_t ds_dst, int row, WaitFn wait_dst) {
+  float sv[64];
+  {
+    uint32_t ra[32], rb[32];
+    tmem_ld_32x32b_x32(ts, ra);
+    tmem_ld_32x32b_x32(ts + 32, rb);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      sv[j] = __uint_as_float(ra[j]);
+      sv[32 + j] = __uint_as_float(rb[j]);
+    }
+  }
+  float sub = delta, lm_ds = 0.f;
   if (kind == 0) {
 #pragma unroll
-    for (int j = 0; j < 64; ++j) sv[j] = dp[j] = 0.f;
+    for (int j = 0; j < 64; ++j) sv[j] = 0.f;
   } else if (kind == 1) {
 #pragma unroll
-    for (int j = 0; j < 64; ++j) {
-      const float pj = (j <= vis) ? ex2(sv[j] - M2) * Linv : 0.f;
-      dp[j] = pj * (dp[j] - delta) * scale;
-      sv[j] = pj;
-    }
+    for (int j = 0; j < 64; ++j) sv[j] = (j <= vis) ? ex2(fmaf(sv[j], c, -M2)) * Linv : 0.f;
   } else {
-    const float lm = sv[63];
-    float mx = -INFINITY;
+    const float nmx = -row_max<63>(sv) * c;
+    const float lm2 = sv[63] * c;
 #pragma unroll
-    for (int j = 0; j < 63; ++j) mx = fmaxf(mx, sv[j]);
-    float den = 0.f, nd = 0.f;
+    for (int j = 0; j < 63; ++j) sv[j] = ex2(fmaf(sv[j], c, nmx));
+    sv[63] = 0.f;
+    const float den = row_sum<63>(sv);
+    float nd0 = 0.f, nd1 = 0.f, nd2 = 0.f, nd3 = 0.f;
 #pragma unroll
-    for (int j = 0; j < 63; ++j) {
-      sv[j] = ex2(sv[j] - mx);
-      den += sv[j];
-      nd = fmaf(sv[j], dp[j], nd);
+    for (int hf = 0; hf < 2; ++hf) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(tdp + hf * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        nd0 = fmaf(sv[hf * 32 + j], __uint_as_float(r[j]), nd0);
+        nd1 = fmaf(sv[hf * 32 + j + 1], __uint_as_float(r[j + 1]), nd1);
+        nd2 = fmaf(sv[hf * 32 + j + 2], __uint_as_float(r[j + 2]), nd2);
+        nd3 = fmaf(sv[hf * 32 + j + 3], __uint_as_float(r[j + 3]), nd3);
+      }
     }
-    const float rden = 1.f / den;
-    nd *= rden;
-    const float g = ex2(lm - M2) * Linv;
+    const float rden = __fdividef(1.f, den);
+    const float nd = ((nd0 + nd1) + (nd2 + nd3)) * rden;
+    const float g = ex2(lm2 - M2) * Linv;
     const float w = g * rden;
 #pragma unroll
-    for (int j = 0; j < 63; ++j) {
-      const float pj = sv[j] * w;
-      dp[j] = pj * (dp[j] - nd) * scale;
-      sv[j] = pj;
+    for (int j = 0; j < 63; ++j) sv[j] *= w;
+    sub = nd;
+    lm_ds = g * (nd - delta) * scale;
+  }
+  wait_dst();
+  if (kNeedP) {
+    uint32_t wp[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) wp[j] = pack2<kBf16>(sv[2 * j], sv[2 * j + 1]);
+    store_row_sw128(p_dst, row, wp);
+  }
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    uint32_t wd[16];
+    if (kind == 0) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) wd[j] = 0u;
+    } else {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(tdp + hf * 32, r);
+      tmem_ld_wait();
+      if (hf == 1) {
+        tc_fence_before();
+        mbar_arrive(free_bar);
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float d0 = sv[hf * 32 + 2 * j] * (__uint_as_float(r[2 * j]) - sub) * scale;
+        float d1 = sv[hf * 32 + 2 * j + 1] * (__uint_as_float(r[2 * j + 1]) - sub) * scale;
+        if (hf == 1 && j == 15 && kind == 2) d1 = lm_ds;
+        wd[j] = pack2<kBf16>(d0, d1);
+      }
     }
-    dp[63] = g * (nd - delta) * scale;
-    sv[63] = 0.f;
+    store_half_row_sw128(ds_dst, row, hf, wd);
+  }
+  if (kind == 0) {
+    tc_fence_before();
+    mbar_arrive(free_bar);
   }
 }
 
@@ -667,22 +791,30 @@ enum { kErrDkvProducer = 201, kErrDkvMma = 202, kErrDkvSoftmax = 203, kErrDkvEpi
        kErrDqProducer = 301, kErrDqMma = 302, kErrDqSoftmax = 303, kErrDqEpilogue = 304 };
 
 // ---------------------------------------------------------------------------------------------- backward: dK, dV
+// Thread roles (both backward kernels): warps 0-3 and 4-7 are two softmax warpgroups that take alternate items
+// (the backward pass carries no state from one item to the next), warp 8 issues TMA loads, warp 9 issues the
+// S / dP MMAs and owns the TMEM allocation, warp 10 issues the accumulating MMAs.  Two issuer threads keep the
+// products of the next item from queueing behind a wait for the current one.  (Registers are granted to 4 warps at
+// a time, so 9 to 12 warps all leave 168 registers per thread.)
+constexpr int kBwdGroups = 2;                       // softmax warpgroups (items are dealt round-robin)
+constexpr int kBwdThreads = (kBwdGroups * 4 + 3) * 32;
+constexpr int kSdpBufs = 3;                         // S / dP buffers in TMEM: 3 x (64 + 64) columns
 constexpr int kDkvStages = 2;
 
 struct DkvSmem {
   uint64_t kv_full;
   uint64_t full[kDkvStages];
   uint64_t empty[kDkvStages];
-  uint64_t sdp_full[2];
-  uint64_t sdp_free[2];
-  uint64_t pds_ready;
-  uint64_t pds_free;
+  uint64_t sdp_full[kSdpBufs];
+  uint64_t sdp_free[kSdpBufs];
+  uint64_t pds_ready[2];
+  uint64_t pds_free[2];
   uint64_t acc_full;
   uint32_t tmem_base;
 };
 
 template <bool kBf16>
-__global__ void __launch_bounds__(kFwdThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                      const float* __restrict__ L_ptr, const float* __restrict__ M_ptr,
@@ -694,9 +826,9 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t k_tile = base, v_tile = base + 16384u;
   auto q_slot = [&](int s) { return base + 32768u + (uint32_t)s * 65536u; };
   auto do_slot = [&](int s) { return base + 32768u + (uint32_t)s * 65536u + 32768u; };
-  const uint32_t p_tile = base + 32768u + kDkvStages * 65536u;
-  const uint32_t ds_tile = p_tile + 16384u;
-  DkvSmem* sm = reinterpret_cast<DkvSmem*>(smem_raw + (base - raw) + 32768u + kDkvStages * 65536u + 32768u);
+  auto p_tile = [&](int g) { return base + 32768u + kDkvStages * 65536u + (uint32_t)g * 32768u; };
+  auto ds_tile = [&](int g) { return base + 32768u + kDkvStages * 65536u + (uint32_t)g * 32768u + 16384u; };
+  DkvSmem* sm = reinterpret_cast<DkvSmem*>(smem_raw + (base - raw) + 32768u + kDkvStages * 65536u + 65536u);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = blockIdx.x;                              // key block; low blocks see the most query tiles
@@ -712,23 +844,25 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(smem_u32(&sm->full[s]), 1);
       mbar_init(smem_u32(&sm->empty[s]), 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&sm->sdp_full[s]), 1);
-      mbar_init(smem_u32(&sm->sdp_free[s]), 128);
+    for (int g = 0; g < kSdpBufs; ++g) {
+      mbar_init(smem_u32(&sm->sdp_full[g]), 1);
+      mbar_init(smem_u32(&sm->sdp_free[g]), 128);
     }
-    mbar_init(smem_u32(&sm->pds_ready), 128);
-    mbar_init(smem_u32(&sm->pds_free), 1);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(smem_u32(&sm->pds_ready[g]), 128);
+      mbar_init(smem_u32(&sm->pds_free[g]), 1);
+    }
     mbar_init(smem_u32(&sm->acc_full), 1);
     mbar_init_fence();
   }
-  if (warp == 5) tmem_alloc(smem_u32(&sm->tmem_base), 512);
+  if (warp == kBwdGroups * 4 + 1) tmem_alloc(smem_u32(&sm->tmem_base), 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
-  const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dv = tmem + 256, tmem_dk = tmem + 320;
+  const uint32_t tmem_s = tmem, tmem_dp = tmem + 192, tmem_dv = tmem + 384, tmem_dk = tmem + 448;
 
-  if (warp == 4) {
+  if (warp == kBwdGroups * 4) {
     if (lane == 0) {
       prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_k);
@@ -753,148 +887,133 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == kBwdGroups * 4 + 1) {
+    // S = Q K^T and dP = dO V^T of item j into TMEM buffer j & 1
     if (lane == 0) {
       constexpr uint32_t fmt = kBf16 ? 1u : 0u;
-      constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);   // S = Q K^T, dP = dO V^T
-      constexpr uint32_t idesc_t = instr_desc_f16(fmt, 128, 64, 1, 1);   // dV^T += dO^T P, dK^T += Q^T dS
+      constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);
       mbar_wait(smem_u32(&sm->kv_full), 0, &g_lmk_status, kErrDkvMma);
-      auto issue_sdp = [&](int j) {
-        const int s = j % kDkvStages, sb = j & 1;
+      const uint64_t dkt = smem_desc_sw128(k_tile, 16, 1024), dvt = smem_desc_sw128(v_tile, 16, 1024);
+      const uint64_t dq0 = smem_desc_sw128(q_slot(0), 16, 1024), ddo0 = smem_desc_sw128(do_slot(0), 16, 1024);
+      for (int j = 0; j < n_items; ++j) {
+        const int s = j % kDkvStages, sb = j % kSdpBufs;
         mbar_wait(smem_u32(&sm->full[s]), (j / kDkvStages) & 1, &g_lmk_status, kErrDkvMma);
-        if (j >= 2) mbar_wait(smem_u32(&sm->sdp_free[sb]), ((j / 2) & 1) ^ 1, &g_lmk_status, kErrDkvMma);
+        if (j >= kSdpBufs)
+          mbar_wait(smem_u32(&sm->sdp_free[sb]), ((j / kSdpBufs) & 1) ^ 1, &g_lmk_status, kErrDkvMma);
         tc_fence_after();
+        const uint64_t dq = desc_advance(dq0, (uint32_t)s * 65536u), ddo = desc_advance(ddo0, (uint32_t)s * 65536u);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
-          const uint32_t off_a = (kk >> 2) * kTileBytes + (kk & 3) * 32;
-          const uint32_t off_b = (kk >> 2) * kHalfTile + (kk & 3) * 32;
-          mma_f16_ss(tmem_s + sb * 64, smem_desc_sw128(q_slot(s) + off_a, 16, 1024),
-                     smem_desc_sw128(k_tile + off_b, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < kD / 16; ++kk)
+          mma_f16_ss(tmem_s + sb * 64, desc_advance(dq, kmajor_step(kk, kTileBytes)),
+                     desc_advance(dkt, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
-          const uint32_t off_a = (kk >> 2) * kTileBytes + (kk & 3) * 32;
-          const uint32_t off_b = (kk >> 2) * kHalfTile + (kk & 3) * 32;
-          mma_f16_ss(tmem_dp + sb * 64, smem_desc_sw128(do_slot(s) + off_a, 16, 1024),
-                     smem_desc_sw128(v_tile + off_b, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < kD / 16; ++kk)
+          mma_f16_ss(tmem_dp + sb * 64, desc_advance(ddo, kmajor_step(kk, kTileBytes)),
+                     desc_advance(dvt, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
         mma_commit(smem_u32(&sm->sdp_full[sb]));
-      };
-      issue_sdp(0);
+      }
+    }
+    __syncwarp();
+  } else if (warp == kBwdGroups * 4 + 2) {
+    if (lane == 0) {
+      // dV^T += dO^T P and dK^T += Q^T dS.  A = dO^T / Q^T: MN-major view of the row-major [128 q x 128 d] tile
+      // (second 64-feature half 16 KB further); B = P / dS: MN-major view of the [128 q x 64 k] tile; a K-step is 16
+      // query rows = 2048 bytes.
+      constexpr uint32_t fmt = kBf16 ? 1u : 0u;
+      constexpr uint32_t idesc_t = instr_desc_f16(fmt, 128, 64, 1, 1);
+      const uint64_t dq0t = smem_desc_sw128(q_slot(0), kTileBytes, 1024);
+      const uint64_t ddo0t = smem_desc_sw128(do_slot(0), kTileBytes, 1024);
+      const uint64_t dp0 = smem_desc_sw128(p_tile(0), 16, 1024), dds0 = smem_desc_sw128(ds_tile(0), 16, 1024);
       for (int i = 0; i < n_items; ++i) {
-        if (i + 1 < n_items) issue_sdp(i + 1);
-        const int s = i % kDkvStages;
-        mbar_wait(smem_u32(&sm->pds_ready), i & 1, &g_lmk_status, kErrDkvMma);
+        const int s = i % kDkvStages, g = i & 1;
+        mbar_wait(smem_u32(&sm->pds_ready[g]), (i >> 1) & 1, &g_lmk_status, kErrDkvMma);
         tc_fence_after();
-        // A = dO^T / Q^T: MN-major from the row-major [128 q x 128 d] tile (two 64-feature halves 16 KB apart);
-        // B = P / dS: MN-major from the [128 q x 64 k] tile.  A K-step is 16 query rows = 2048 bytes.
+        const uint64_t ddot = desc_advance(ddo0t, (uint32_t)s * 65536u), dqt = desc_advance(dq0t, (uint32_t)s * 65536u);
+        const uint64_t dpt = desc_advance(dp0, (uint32_t)g * 32768u), ddst = desc_advance(dds0, (uint32_t)g * 32768u);
 #pragma unroll
         for (int kk = 0; kk < kQTile / 16; ++kk)
-          mma_f16_ss(tmem_dv, smem_desc_sw128(do_slot(s) + kk * 2048, kTileBytes, 1024),
-                     smem_desc_sw128(p_tile + kk * 2048, 16, 1024), idesc_t, (i > 0 || kk > 0) ? 1u : 0u);
+          mma_f16_ss(tmem_dv, desc_advance(ddot, kk * 2048), desc_advance(dpt, kk * 2048), idesc_t,
+                     (i > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < kQTile / 16; ++kk)
-          mma_f16_ss(tmem_dk, smem_desc_sw128(q_slot(s) + kk * 2048, kTileBytes, 1024),
-                     smem_desc_sw128(ds_tile + kk * 2048, 16, 1024), idesc_t, (i > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(smem_u32(&sm->pds_free));
+          mma_f16_ss(tmem_dk, desc_advance(dqt, kk * 2048), desc_advance(ddst, kk * 2048), idesc_t,
+                     (i > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(smem_u32(&sm->pds_free[g]));
         mma_commit(smem_u32(&sm->empty[s]));
       }
       mma_commit(smem_u32(&sm->acc_full));
     }
     __syncwarp();
   } else {
-    const int row = tid;
+    const int g = warp >> 2;                       // warpgroup: handles items i with i % kBwdGroups == g
+    const int row = tid & 127;
     const int half = row >> 6;
     const int vis = min(row & 63, kBlk - 2);
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    for (int i = 0; i < n_items; ++i) {
-      const int sb = i & 1;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    for (int i = g; i < n_items; i += kBwdGroups) {
       const int tq = tq0 + i;
       const int own = prefix_blocks + 2 * tq + half;
       const int64_t grow = (int64_t)bh * Lq + tq * kQTile + row;
       const float M2 = M_ptr[grow] * kLog2e, Linv = 1.f / L_ptr[grow], delta = delta_ptr[grow];
-      mbar_wait(smem_u32(&sm->sdp_full[sb]), (i / 2) & 1, &g_lmk_status, kErrDkvSoftmax);
+      const int sb = i % kSdpBufs, pb = i & 1;
+      mbar_wait(smem_u32(&sm->sdp_full[sb]), (i / kSdpBufs) & 1, &g_lmk_status, kErrDkvSoftmax);
       tc_fence_after();
-      float sv[64], dp[64];
-      {
-        uint32_t ra[32], rb[32];
-        tmem_ld_32x32b_x32(tmem_s + sb * 64 + lane_base, ra);
-        tmem_ld_32x32b_x32(tmem_s + sb * 64 + 32 + lane_base, rb);
+      const int kind = n > own ? 0 : (n == own ? 1 : 2);
+      bwd_item<kBf16, true>(tmem_s + sb * 64 + lane_base, tmem_dp + sb * 64 + lane_base, smem_u32(&sm->sdp_free[sb]),
+                            kind, vis, scale_log2, scale, M2, Linv, delta, p_tile(pb), ds_tile(pb), row, [&]() {
+                              if (i >= 2)
+                                mbar_wait(smem_u32(&sm->pds_free[pb]), ((i >> 1) - 1) & 1, &g_lmk_status,
+                                          kErrDkvSoftmax);
+                            });
+      fence_proxy_async_smem();
+      mbar_arrive(smem_u32(&sm->pds_ready[pb]));
+    }
+    // epilogue (warpgroup 0): thread = feature d, TMEM column = key j  ->  dV[key][d], dK[key][d]
+    if (g == 0) {
+      mbar_wait(smem_u32(&sm->acc_full), 0, &g_lmk_status, kErrDkvEpilogue);
+      tc_fence_after();
+      uint16_t* dvp = reinterpret_cast<uint16_t*>(dv_ptr) + ((int64_t)bh * Lk + (int64_t)n * kBlk) * kD + row;
+      uint16_t* dkp = reinterpret_cast<uint16_t*>(dk_ptr) + ((int64_t)bh * Lk + (int64_t)n * kBlk) * kD + row;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_dv + c * 32 + lane_base, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          sv[j] = __uint_as_float(ra[j]);
-          sv[32 + j] = __uint_as_float(rb[j]);
-        }
-        tmem_ld_32x32b_x32(tmem_dp + sb * 64 + lane_base, ra);
-        tmem_ld_32x32b_x32(tmem_dp + sb * 64 + 32 + lane_base, rb);
+        for (int j = 0; j < 32; ++j)
+          dvp[(int64_t)(c * 32 + j) * kD] = (uint16_t)(pack2<kBf16>(__uint_as_float(r[j]), 0.f) & 0xffffu);
+        tmem_ld_32x32b_x32(tmem_dk + c * 32 + lane_base, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          dp[j] = __uint_as_float(ra[j]);
-          dp[32 + j] = __uint_as_float(rb[j]);
-        }
+        for (int j = 0; j < 32; ++j)
+          dkp[(int64_t)(c * 32 + j) * kD] = (uint16_t)(pack2<kBf16>(__uint_as_float(r[j]), 0.f) & 0xffffu);
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(&sm->sdp_free[sb]));
-      const int kind = n > own ? 0 : (n == own ? 1 : 2);
-      bwd_weights<true>(sv, dp, kind, vis, scale_log2, scale, M2, Linv, delta);
-      uint32_t wp[32], wd[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        wp[j] = pack2<kBf16>(sv[2 * j], sv[2 * j + 1]);
-        wd[j] = pack2<kBf16>(dp[2 * j], dp[2 * j + 1]);
-      }
-      if (i > 0) mbar_wait(smem_u32(&sm->pds_free), (i - 1) & 1, &g_lmk_status, kErrDkvSoftmax);
-      store_row_sw128(p_tile, row, wp);
-      store_row_sw128(ds_tile, row, wd);
-      fence_proxy_async_smem();
-      mbar_arrive(smem_u32(&sm->pds_ready));
     }
-    // epilogue: thread = feature d, TMEM column = key j  ->  dV[key][d], dK[key][d]
-    mbar_wait(smem_u32(&sm->acc_full), 0, &g_lmk_status, kErrDkvEpilogue);
-    tc_fence_after();
-    uint16_t* dvp = reinterpret_cast<uint16_t*>(dv_ptr) + ((int64_t)bh * Lk + (int64_t)n * kBlk) * kD + row;
-    uint16_t* dkp = reinterpret_cast<uint16_t*>(dk_ptr) + ((int64_t)bh * Lk + (int64_t)n * kBlk) * kD + row;
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(tmem_dv + c * 32 + lane_base, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        dvp[(int64_t)(c * 32 + j) * kD] = (uint16_t)(pack2<kBf16>(__uint_as_float(r[j]), 0.f) & 0xffffu);
-      tmem_ld_32x32b_x32(tmem_dk + c * 32 + lane_base, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        dkp[(int64_t)(c * 32 + j) * kD] = (uint16_t)(pack2<kBf16>(__uint_as_float(r[j]), 0.f) & 0xffffu);
-    }
-    tc_fence_before();
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kBwdGroups * 4 + 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
 }
 
 // ---------------------------------------------------------------------------------------------- backward: dQ
-constexpr int kDqStages = 3;
+constexpr int kDqStages = 4;
 
 struct DqSmem {
   uint64_t qdo_full;
   uint64_t full[kDqStages];
   uint64_t empty[kDqStages];
   uint64_t ds_ready[kDqStages];
-  uint64_t sdp_full[2];
-  uint64_t sdp_free[2];
+  uint64_t sdp_full[kSdpBufs];
+  uint64_t sdp_free[kSdpBufs];
   uint64_t acc_full;
   uint32_t tmem_base;
 };
 
 template <bool kBf16>
-__global__ void __launch_bounds__(kFwdThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                     const float* __restrict__ L_ptr, const float* __restrict__ M_ptr,
@@ -924,21 +1043,21 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_init(smem_u32(&sm->empty[s]), 1);
       mbar_init(smem_u32(&sm->ds_ready[s]), 128);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kSdpBufs; ++s) {
       mbar_init(smem_u32(&sm->sdp_full[s]), 1);
       mbar_init(smem_u32(&sm->sdp_free[s]), 128);
     }
     mbar_init(smem_u32(&sm->acc_full), 1);
     mbar_init_fence();
   }
-  if (warp == 5) tmem_alloc(smem_u32(&sm->tmem_base), 512);
+  if (warp == kBwdGroups * 4 + 1) tmem_alloc(smem_u32(&sm->tmem_base), 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
-  const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dq = tmem + 256;
+  const uint32_t tmem_s = tmem, tmem_dp = tmem + 192, tmem_dq = tmem + 384;
 
-  if (warp == 4) {
+  if (warp == kBwdGroups * 4) {
     if (lane == 0) {
       prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_k);
@@ -963,114 +1082,99 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == kBwdGroups * 4 + 1) {
     if (lane == 0) {
       constexpr uint32_t fmt = kBf16 ? 1u : 0u;
       constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);
-      constexpr uint32_t idesc_q = instr_desc_f16(fmt, 128, 128, 0, 1);   // dQ += dS K  (K is MN-major)
       mbar_wait(smem_u32(&sm->qdo_full), 0, &g_lmk_status, kErrDqMma);
-      auto issue_sdp = [&](int j) {
-        const int s = j % kDqStages, sb = j & 1;
+      const uint64_t dqd = smem_desc_sw128(q_tile, 16, 1024), ddo = smem_desc_sw128(do_tile, 16, 1024);
+      const uint64_t dk0 = smem_desc_sw128(k_slot(0), 16, 1024), dv0 = smem_desc_sw128(v_slot(0), 16, 1024);
+      for (int j = 0; j < total; ++j) {
+        const int s = j % kDqStages, sb = j % kSdpBufs;
         mbar_wait(smem_u32(&sm->full[s]), (j / kDqStages) & 1, &g_lmk_status, kErrDqMma);
-        if (j >= 2) mbar_wait(smem_u32(&sm->sdp_free[sb]), ((j / 2) & 1) ^ 1, &g_lmk_status, kErrDqMma);
+        if (j >= kSdpBufs)
+          mbar_wait(smem_u32(&sm->sdp_free[sb]), ((j / kSdpBufs) & 1) ^ 1, &g_lmk_status, kErrDqMma);
         tc_fence_after();
+        const uint64_t dk = desc_advance(dk0, (uint32_t)s * 32768u), dv = desc_advance(dv0, (uint32_t)s * 32768u);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
-          const uint32_t off_a = (kk >> 2) * kTileBytes + (kk & 3) * 32;
-          const uint32_t off_b = (kk >> 2) * kHalfTile + (kk & 3) * 32;
-          mma_f16_ss(tmem_s + sb * 64, smem_desc_sw128(q_tile + off_a, 16, 1024),
-                     smem_desc_sw128(k_slot(s) + off_b, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < kD / 16; ++kk)
+          mma_f16_ss(tmem_s + sb * 64, desc_advance(dqd, kmajor_step(kk, kTileBytes)),
+                     desc_advance(dk, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
-          const uint32_t off_a = (kk >> 2) * kTileBytes + (kk & 3) * 32;
-          const uint32_t off_b = (kk >> 2) * kHalfTile + (kk & 3) * 32;
-          mma_f16_ss(tmem_dp + sb * 64, smem_desc_sw128(do_tile + off_a, 16, 1024),
-                     smem_desc_sw128(v_slot(s) + off_b, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < kD / 16; ++kk)
+          mma_f16_ss(tmem_dp + sb * 64, desc_advance(ddo, kmajor_step(kk, kTileBytes)),
+                     desc_advance(dv, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
         mma_commit(smem_u32(&sm->sdp_full[sb]));
-      };
-      issue_sdp(0);
+      }
+    }
+    __syncwarp();
+  } else if (warp == kBwdGroups * 4 + 2) {
+    if (lane == 0) {
+      constexpr uint32_t fmt = kBf16 ? 1u : 0u;
+      constexpr uint32_t idesc_q = instr_desc_f16(fmt, 128, 128, 0, 1);   // dQ += dS K  (K is MN-major)
+      const uint64_t dv0 = smem_desc_sw128(v_slot(0), 16, 1024);
+      const uint64_t dk0t = smem_desc_sw128(k_slot(0), kHalfTile, 1024);
       for (int i = 0; i < total; ++i) {
-        if (i + 1 < total) issue_sdp(i + 1);
         const int s = i % kDqStages;
         mbar_wait(smem_u32(&sm->ds_ready[s]), (i / kDqStages) & 1, &g_lmk_status, kErrDqMma);
         tc_fence_after();
+        const uint64_t dds = desc_advance(dv0, (uint32_t)s * 32768u), dkt = desc_advance(dk0t, (uint32_t)s * 32768u);
 #pragma unroll
         for (int kk = 0; kk < kBlk / 16; ++kk)
-          mma_f16_ss(tmem_dq, smem_desc_sw128(v_slot(s) + kk * 32, 16, 1024),
-                     smem_desc_sw128(k_slot(s) + kk * 2048, kHalfTile, 1024), idesc_q, (i > 0 || kk > 0) ? 1u : 0u);
+          mma_f16_ss(tmem_dq, desc_advance(dds, kk * 32), desc_advance(dkt, kk * 2048), idesc_q,
+                     (i > 0 || kk > 0) ? 1u : 0u);
         mma_commit(smem_u32(&sm->empty[s]));
       }
       mma_commit(smem_u32(&sm->acc_full));
     }
     __syncwarp();
   } else {
-    const int row = tid;
+    const int g = warp >> 2;
+    const int row = tid & 127;
     const int half = row >> 6;
     const int own = own0 + half;
     const int vis = min(row & 63, kBlk - 2);
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const int64_t grow = (int64_t)bh * Lq + t * kQTile + row;
     const float M2 = M_ptr[grow] * kLog2e, Linv = 1.f / L_ptr[grow], delta = delta_ptr[grow];
-    for (int i = 0; i < total; ++i) {
-      const int sb = i & 1, s = i % kDqStages;
+    for (int i = g; i < total; i += kBwdGroups) {
+      const int s = i % kDqStages;
       const int n = n_last - i;
-      mbar_wait(smem_u32(&sm->sdp_full[sb]), (i / 2) & 1, &g_lmk_status, kErrDqSoftmax);
+      const int sb = i % kSdpBufs;
+      mbar_wait(smem_u32(&sm->sdp_full[sb]), (i / kSdpBufs) & 1, &g_lmk_status, kErrDqSoftmax);
       tc_fence_after();
-      float sv[64], dp[64];
-      {
-        uint32_t ra[32], rb[32];
-        tmem_ld_32x32b_x32(tmem_s + sb * 64 + lane_base, ra);
-        tmem_ld_32x32b_x32(tmem_s + sb * 64 + 32 + lane_base, rb);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          sv[j] = __uint_as_float(ra[j]);
-          sv[32 + j] = __uint_as_float(rb[j]);
-        }
-        tmem_ld_32x32b_x32(tmem_dp + sb * 64 + lane_base, ra);
-        tmem_ld_32x32b_x32(tmem_dp + sb * 64 + 32 + lane_base, rb);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          dp[j] = __uint_as_float(ra[j]);
-          dp[32 + j] = __uint_as_float(rb[j]);
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&sm->sdp_free[sb]));
       const int kind = n > own ? 0 : (n == own ? 1 : 2);
-      bwd_weights<false>(sv, dp, kind, vis, scale_log2, scale, M2, Linv, delta);
-      uint32_t wd[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) wd[j] = pack2<kBf16>(dp[2 * j], dp[2 * j + 1]);
-      store_row_sw128(v_slot(s), row, wd);
+      // dS replaces the V tile of this stage, which dP = dO V^T has finished reading
+      bwd_item<kBf16, false>(tmem_s + sb * 64 + lane_base, tmem_dp + sb * 64 + lane_base,
+                             smem_u32(&sm->sdp_free[sb]), kind, vis, scale_log2, scale, M2, Linv, delta, 0u,
+                             v_slot(s), row, []() {});
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(&sm->ds_ready[s]));
     }
-    mbar_wait(smem_u32(&sm->acc_full), 0, &g_lmk_status, kErrDqEpilogue);
-    tc_fence_after();
-    uint4* orow = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dq_ptr) + grow * kD);
+    if (g == 0) {
+      mbar_wait(smem_u32(&sm->acc_full), 0, &g_lmk_status, kErrDqEpilogue);
+      tc_fence_after();
+      uint4* orow = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dq_ptr) + grow * kD);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(tmem_dq + c * 32 + lane_base, r);
-      tmem_ld_wait();
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_dq + c * 32 + lane_base, r);
+        tmem_ld_wait();
 #pragma unroll
-      for (int v4 = 0; v4 < 4; ++v4) {
-        uint4 pk;
-        pk.x = pack2<kBf16>(__uint_as_float(r[8 * v4 + 0]), __uint_as_float(r[8 * v4 + 1]));
-        pk.y = pack2<kBf16>(__uint_as_float(r[8 * v4 + 2]), __uint_as_float(r[8 * v4 + 3]));
-        pk.z = pack2<kBf16>(__uint_as_float(r[8 * v4 + 4]), __uint_as_float(r[8 * v4 + 5]));
-        pk.w = pack2<kBf16>(__uint_as_float(r[8 * v4 + 6]), __uint_as_float(r[8 * v4 + 7]));
-        orow[c * 4 + v4] = pk;
+        for (int v4 = 0; v4 < 4; ++v4) {
+          uint4 pk;
+          pk.x = pack2<kBf16>(__uint_as_float(r[8 * v4 + 0]), __uint_as_float(r[8 * v4 + 1]));
+          pk.y = pack2<kBf16>(__uint_as_float(r[8 * v4 + 2]), __uint_as_float(r[8 * v4 + 3]));
+          pk.z = pack2<kBf16>(__uint_as_float(r[8 * v4 + 4]), __uint_as_float(r[8 * v4 + 5]));
+          pk.w = pack2<kBf16>(__uint_as_float(r[8 * v4 + 6]), __uint_as_float(r[8 * v4 + 7]));
+          orow[c * 4 + v4] = pk;
+        }
       }
+      tc_fence_before();
     }
-    tc_fence_before();
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kBwdGroups * 4 + 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -1200,7 +1304,7 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
   float* delta = reinterpret_cast<float*>(p.workspace);
   const int64_t rows = (int64_t)p.B * p.H * p.Lq;
   const float scale_log2 = p.scale * kLog2e;
-  const size_t smem_dkv = 1024 + 32768 + kDkvStages * 65536 + 32768 + sizeof(DkvSmem);
+  const size_t smem_dkv = 1024 + 32768 + kDkvStages * 65536 + 65536 + sizeof(DkvSmem);
   const size_t smem_dq = 1024 + 65536 + kDqStages * 32768 + sizeof(DqSmem);
   dim3 grid_dkv(p.Lk / kBlk, p.B * p.H), grid_dq(p.Lq / kQTile, p.B * p.H);
 #define LMK_BWD_LAUNCH(BF)                                                                                          \
@@ -1209,11 +1313,11 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
         reinterpret_cast<const uint2*>(p.o), reinterpret_cast<const uint2*>(p.dO), delta, rows);                    \
     LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dkv_kernel<BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
                                   (int)smem_dkv));                                                                  \
-    sm100_bwd_dkv_kernel<BF><<<grid_dkv, kFwdThreads, smem_dkv, st>>>(tq, tk, tv, tdo, p.L, p.M, delta, p.dk, p.dv, \
+    sm100_bwd_dkv_kernel<BF><<<grid_dkv, kBwdThreads, smem_dkv, st>>>(tq, tk, tv, tdo, p.L, p.M, delta, p.dk, p.dv, \
                                                                      p.H, p.Lq, p.Lk, p.scale, scale_log2);         \
     LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dq_kernel<BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
                                   (int)smem_dq));                                                                   \
-    sm100_bwd_dq_kernel<BF><<<grid_dq, kFwdThreads, smem_dq, st>>>(tq, tk, tv, tdo, p.L, p.M, delta, p.dq, p.H,     \
+    sm100_bwd_dq_kernel<BF><<<grid_dq, kBwdThreads, smem_dq, st>>>(tq, tk, tv, tdo, p.L, p.M, delta, p.dq, p.H,     \
                                                                    p.Lq, p.Lk, p.scale, scale_log2);                \
   } while (0)
   if (dtype == LMK_BF16) LMK_BWD_LAUNCH(true);
@@ -1224,6 +1328,12 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
 }
 
 size_t attn_sm100_bwd_workspace(int B, int H, int Lq, int, int) { return sizeof(float) * (size_t)B * H * Lq; }
+
+#ifdef LMK_TRACE
+extern "C" int lmk_trace_set(long long* buf) {
+  return cudaMemcpyToSymbol(g_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : -3;
+}
+#endif
 
 int device_status(int* out, int clear) {
   int v = 0;

@@ -133,6 +133,17 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_
   return d;
 }
 
+// The MMA issuer is ONE thread: every ALU instruction it executes between two tcgen05.mma costs a full dependent-issue
+// latency.  Descriptors are therefore built once per tile and advanced by adding a constant to the 14-bit address
+// field (shared-memory addresses are below 256 KB, so the add never carries out of the field).
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t byte_offset) {
+  return desc + (uint64_t)(byte_offset >> 4);
+}
+// byte offset of K-step kk (16 elements) inside a K-major operand made of 64-column sub-tiles `subtile_bytes` apart
+__host__ __device__ constexpr uint32_t kmajor_step(int kk, uint32_t subtile_bytes) {
+  return (uint32_t)(kk >> 2) * subtile_bytes + (uint32_t)(kk & 3) * 32u;
+}
+
 // Instruction descriptor for kind::f16: fp32 accumulator, A/B both `fmt` (0 = f16, 1 = bf16), majorness bits
 // (0 = K-major, 1 = MN-major), N >> 3 at bit 17, M >> 4 at bit 24.
 __host__ __device__ constexpr uint32_t instr_desc_f16(uint32_t fmt, uint32_t m, uint32_t n, uint32_t a_mn_major,
@@ -142,9 +153,13 @@ __host__ __device__ constexpr uint32_t instr_desc_f16(uint32_t fmt, uint32_t m, 
 }
 
 __device__ __forceinline__ float ex2(float x) {
+#ifdef LMK_EXP_NOEX2
+  return x * 0.001f;
+#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+#endif
 }
 
 }  // namespace ptx
