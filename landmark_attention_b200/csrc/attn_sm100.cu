@@ -152,8 +152,10 @@ sm100_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = Lq / kQTile;
-  const int t = n_tiles - 1 - (int)blockIdx.x;          // heaviest tiles first
-  const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
+  // grid = (batch*head, tile): consecutive CTAs are different heads of the same tile, heaviest tiles first, so the
+  // hardware's in-order block dispatch is a longest-job-first schedule over the whole launch
+  const int t = n_tiles - 1 - (int)blockIdx.y;
+  const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
   const int prefix_blocks = (Lk - Lq) / kBlk;
   const int own0 = prefix_blocks + 2 * t;               // block of rows 0-63; rows 64-127 own own0+1
   const int n_last = own0 + 1;
@@ -405,8 +407,8 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_pairs = Lq / (2 * kQTile);
-  const int u = n_pairs - 1 - (int)blockIdx.x;          // heaviest pairs first
-  const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
+  const int u = n_pairs - 1 - (int)blockIdx.y;          // heaviest pairs first, across all heads
+  const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
   const int prefix_blocks = (Lk - Lq) / kBlk;
   const int own0_a = prefix_blocks + 4 * u;             // tile A: blocks own0_a, own0_a+1; tile B: +2, +3
   const int n_last = own0_a + 3;                        // newest block of the pair
@@ -831,8 +833,8 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   DkvSmem* sm = reinterpret_cast<DkvSmem*>(smem_raw + (base - raw) + 32768u + kDkvStages * 65536u + 65536u);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n = blockIdx.x;                              // key block; low blocks see the most query tiles
-  const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
+  const int n = blockIdx.y;                              // key block; low blocks see the most query tiles
+  const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
   const int prefix_blocks = (Lk - Lq) / kBlk;
   const int n_tiles = Lq / kQTile;
   const int tq0 = n > prefix_blocks ? (n - prefix_blocks) / 2 : 0;
@@ -1029,8 +1031,8 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = Lq / kQTile;
-  const int t = n_tiles - 1 - (int)blockIdx.x;
-  const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
+  const int t = n_tiles - 1 - (int)blockIdx.y;
+  const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
   const int prefix_blocks = (Lk - Lq) / kBlk;
   const int own0 = prefix_blocks + 2 * t;
   const int n_last = own0 + 1;
@@ -1261,7 +1263,7 @@ int attn_sm100_fwd(const AttnParams& p, int dtype, cudaStream_t st) {
   const float scale_log2 = p.scale * kLog2e;
   if (p.Lq % (2 * kQTile) == 0) {
     const size_t smem = 1024 + 65536 + kFwd2Stages * 32768 + 32768 + sizeof(Fwd2Smem);
-    dim3 grid(p.Lq / (2 * kQTile), p.B * p.H);
+    dim3 grid(p.B * p.H, p.Lq / (2 * kQTile));
     if (dtype == LMK_BF16) {
       LMK_CUDA(cudaFuncSetAttribute(sm100_fwd2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       sm100_fwd2_kernel<true><<<grid, kFwd2Threads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk,
@@ -1273,7 +1275,7 @@ int attn_sm100_fwd(const AttnParams& p, int dtype, cudaStream_t st) {
     }
   } else {
     const size_t smem = 1024 + 32768 + kFwdStages * 32768 + sizeof(FwdSmem);
-    dim3 grid(p.Lq / kQTile, p.B * p.H);
+    dim3 grid(p.B * p.H, p.Lq / kQTile);
     if (dtype == LMK_BF16) {
       LMK_CUDA(cudaFuncSetAttribute(sm100_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       sm100_fwd_kernel<true><<<grid, kFwdThreads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk, lm_box,
@@ -1306,7 +1308,7 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
   const float scale_log2 = p.scale * kLog2e;
   const size_t smem_dkv = 1024 + 32768 + kDkvStages * 65536 + 65536 + sizeof(DkvSmem);
   const size_t smem_dq = 1024 + 65536 + kDqStages * 32768 + sizeof(DqSmem);
-  dim3 grid_dkv(p.Lk / kBlk, p.B * p.H), grid_dq(p.Lq / kQTile, p.B * p.H);
+  dim3 grid_dkv(p.B * p.H, p.Lk / kBlk), grid_dq(p.B * p.H, p.Lq / kQTile);
 #define LMK_BWD_LAUNCH(BF)                                                                                          \
   do {                                                                                                              \
     sm100_delta_kernel<BF><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(                                             \
