@@ -139,7 +139,7 @@ def run_reference(args, world, rank):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    heads = 8
+    heads = int(os.environ.get("LMK_BENCH_CPU_HEADS", "8"))       # bounded sample of the 32-head workload
     tf, sec = cpu_oracle_attn(heads, threads, steps=min(args.steps, 10), warmup=min(args.warmup, 1))
     w = WORKLOAD
     line = {
