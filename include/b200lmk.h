@@ -94,6 +94,33 @@ int lmk_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
                  int block, float sm_scale, int dtype, int path, void* stream);
 
 /*
+ * Backward pass for callers that cannot allocate device memory.  (No counterpart in the reference.)
+ *
+ * Some hosts of this library may not call cudaMalloc at the point where they run the backward pass: a plugin that is
+ * handed finished buffers by its runtime and owns no allocator, code running inside a region where allocation is
+ * forbidden (for example while another component holds the allocator lock or a memory pool is frozen), or a
+ * real-time loop that must not touch the allocator.  lmk_attn_bwd needs lmk_attn_bwd_workspace() bytes of scratch
+ * (one float per batch*head*query row) from such a caller; this variant brings its own: a fixed array compiled into
+ * the library image, resident on every GPU that loads the library until the process exits.
+ *
+ *   - Same arguments and results as lmk_attn_bwd, without workspace / workspace_bytes.
+ *   - Limit: B*H*Lq <= lmk_attn_bwd_static_max_rows() (1,048,576 rows = 4 MiB of scratch per GPU).  Larger problems are
+ *     rejected with LMK_ERR_WORKSPACE and nothing is launched; use lmk_attn_bwd for them.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine.  The first call on each device looks up the
+ *     array's device address (a one-time host-side query with that device current); make that first call before
+ *     starting any stream capture.
+ *   - All calls on a device share the one array.  Nothing in it has to start at zero (every element that is read was
+ *     written earlier in the same call), so it is never cleared; it keeps the previous call's contents.  Two calls
+ *     whose kernels can overlap on the GPU (different streams, no ordering between them) race on it: serialise them.
+ */
+size_t lmk_attn_bwd_static_max_rows(void);
+int lmk_attn_bwd_static(const void* q, const void* k, const void* v, const void* o, const void* dO,
+                        const float* L, const float* M, void* dQ, void* dK, void* dV,
+                        int B, int H, int Lq, int Lk, int D,
+                        const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                        int block, float sm_scale, int dtype, int path, void* stream);
+
+/*
  * Stand-alone landmark grouped softmax over the last dimension of x [B,H,Lq,Lk].
  * Replaces LandmarkGroupedSoftmaxFunction.forward + landmark_grouped_softmax
  *   (llama/llama_mem.py:168-243; lm_benchmark/models/landmark.py:37-119).

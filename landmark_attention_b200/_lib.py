@@ -39,6 +39,10 @@ PROTOTYPES = {
     "lmk_attn_bwd": (c_int, [c_void_p] * 10 + [c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int,
                                                POINTER(c_int64), POINTER(c_int64), POINTER(c_int64),
                                                c_int, c_float, c_int, c_int, c_void_p]),
+    "lmk_attn_bwd_static_max_rows": (c_size_t, []),
+    "lmk_attn_bwd_static": (c_int, [c_void_p] * 10 + [c_int, c_int, c_int, c_int, c_int,
+                                                      POINTER(c_int64), POINTER(c_int64), POINTER(c_int64),
+                                                      c_int, c_float, c_int, c_int, c_void_p]),
     "lmk_grouped_softmax_fwd": (c_int, [c_void_p, POINTER(c_int64), c_void_p, POINTER(c_int64), c_void_p,
                                         POINTER(c_int64), c_void_p, POINTER(c_int64), c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),

@@ -4,6 +4,13 @@
 #include "common.cuh"
 #include "attn_params.h"
 
+#include <mutex>
+
+// Scratch for lmk_attn_bwd_static: one float per (batch, head, query row).  Lives in every GPU that loads the library
+// until the process exits.  In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+#define LMK_STATIC_SCRATCH_FLOATS (1 << 20)
+static __device__ __align__(256) float g_static_bwd_scratch[LMK_STATIC_SCRATCH_FLOATS];
+
 namespace lmk {
 
 char* error_buffer() {
@@ -127,4 +134,45 @@ extern "C" int lmk_attn_bwd(const void* q, const void* k, const void* v, const v
   if (which == LMK_PATH_TCGEN05) return attn_sm100_bwd(p, dtype, (cudaStream_t)stream);
   p.delta = reinterpret_cast<float*>(workspace);
   return attn_general_bwd(p, dtype, (cudaStream_t)stream);
+}
+
+// Device address of g_static_bwd_scratch on the current device, resolved once per device.
+static int static_scratch_address(void** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void* addr[kMaxDevices] = {nullptr};
+  int dev = 0;
+  LMK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(LMK_ERR_UNSUPPORTED, "attn_bwd_static: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_bwd_scratch);   // current device = dev
+    if (e != cudaSuccess || p == nullptr)
+      return fail(LMK_ERR_CUDA, "attn_bwd_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return LMK_OK;
+}
+
+extern "C" size_t lmk_attn_bwd_static_max_rows(void) { return (size_t)LMK_STATIC_SCRATCH_FLOATS; }
+
+extern "C" int lmk_attn_bwd_static(const void* q, const void* k, const void* v, const void* o, const void* dO,
+                                   const float* L, const float* M, void* dQ, void* dK, void* dV, int B, int H, int Lq,
+                                   int Lk, int D, const int64_t q_strides[3], const int64_t k_strides[3],
+                                   const int64_t v_strides[3], int block, float sm_scale, int dtype, int path,
+                                   void* stream) {
+  if (B >= 1 && H >= 1 && Lq >= 1) {
+    const size_t need = lmk_attn_bwd_workspace(B, H, Lq, Lk, D, block, dtype, path);
+    if (need > sizeof(float) * (size_t)LMK_STATIC_SCRATCH_FLOATS)
+      return fail(LMK_ERR_WORKSPACE,
+                  "attn_bwd_static: B*H*Lq = %lld rows exceed the built-in scratch of %d rows; use lmk_attn_bwd with a "
+                  "caller-provided workspace", (long long)B * H * Lq, LMK_STATIC_SCRATCH_FLOATS);
+  }
+  void* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc != LMK_OK) return rc;
+  return lmk_attn_bwd(q, k, v, o, dO, L, M, dQ, dK, dV, scratch, sizeof(float) * (size_t)LMK_STATIC_SCRATCH_FLOATS, B,
+                      H, Lq, Lk, D, q_strides, k_strides, v_strides, block, sm_scale, dtype, path, stream);
 }
