@@ -314,16 +314,34 @@ def bench_retrieval(P, L, dev, peaks):
     ev = lambda: torch.cuda.Event(enable_timing=True)
     flush = torch.empty(384 * 1024 * 1024, dtype=torch.uint8, device=dev)
     times = {"scores": [], "topk": [], "gather": []}
+    # each stage is captured through the public API into its own CUDA graph (the eager calls are launch-bound)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graphs = []
+    with torch.cuda.stream(side):
+        scores = P.landmark_scores(q, pk, desc, cos, sin, L.ROTARY_HALF)
+        sel = P.topk_sorted(scores, top_k)
+        P.gather_kv(pk, pv, desc, desc, sel, cos, sin, L.ROTARY_HALF)
+        torch.cuda.synchronize()
+        g1 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g1, stream=side):
+            scores = P.landmark_scores(q, pk, desc, cos, sin, L.ROTARY_HALF)
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2, pool=g1.pool(), stream=side):
+            sel = P.topk_sorted(scores, top_k)
+        g3 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g3, pool=g1.pool(), stream=side):
+            sk, sv = P.gather_kv(pk, pv, desc, desc, sel, cos, sin, L.ROTARY_HALF)
+        graphs = [g1, g2, g3]
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
     for it in range(8):
         flush.zero_()
         e = [ev() for _ in range(4)]
         e[0].record()
-        scores = P.landmark_scores(q, pk, desc, cos, sin, L.ROTARY_HALF)
-        e[1].record()
-        sel = P.topk_sorted(scores, top_k)
-        e[2].record()
-        sk, sv = P.gather_kv(pk, pv, desc, desc, sel, cos, sin, L.ROTARY_HALF)
-        e[3].record()
+        for gi, gr in enumerate(graphs):
+            gr.replay()
+            e[gi + 1].record()
         torch.cuda.synchronize()
         if it >= 3:
             for name, (a, b) in zip(times, ((e[0], e[1]), (e[1], e[2]), (e[2], e[3]))):

@@ -180,11 +180,15 @@ typedef struct {
  *   q [B,H,T,D] dense (already rotated), k_cache per desc, cos/sin tables [n_pos, D] in `dtype` (NULL with
  *   LMK_ROTARY_NONE), scores fp32 dense [B,H,T,n_blocks]; softmax != 0 applies a softmax over n in fp32
  *   (mem_cache.py:62; llama_mem.py:376 mode B) and, when dtype is 16-bit, rounds it to dtype as the reference does.
+ *   workspace (nullable): lmk_landmark_scores_workspace(...) bytes, 256-byte aligned.  When given and the shape
+ *   qualifies (bf16/fp16, D = 128, T >= 128, n_blocks >= 128) the product runs on the tensor cores (rotated landmark
+ *   keys are staged in the workspace); otherwise a CUDA-core kernel is used.
  */
+size_t lmk_landmark_scores_workspace(int B, int H, int T, int D, int n_blocks, int dtype);
 int lmk_landmark_scores(const void* q, const void* k_cache, const lmk_cache_desc* desc,
                         const void* cos_table, const void* sin_table, int n_pos, int rotary,
                         float* scores, int B, int H, int T, int D, float sm_scale, int softmax,
-                        int dtype, void* stream);
+                        int dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Per-row top-k with ascending index output.  Replaces `topk(...)[1].sort(...)[0]`

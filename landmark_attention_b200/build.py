@@ -7,7 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libb200lmk.so")
-SOURCES = ["api.cu", "attn_general.cu", "attn_sm100.cu", "grouped_softmax.cu", "retrieval.cu"]
+SOURCES = ["api.cu", "attn_general.cu", "attn_sm100.cu", "grouped_softmax.cu", "retrieval.cu", "scores_sm100.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]
 

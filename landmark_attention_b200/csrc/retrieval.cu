@@ -4,6 +4,7 @@
 // MemLMCacheStorage.retrieve_for_query (lm_benchmark/models/caches/mem_cache.py:51-98).  Both rotate cached keys at
 // "slot" positions: the newest top_k blocks occupy slots 1..top_k, every older block shares slot 0.
 #include "common.cuh"
+#include "scores_sm100.h"
 
 namespace lmk {
 namespace {
@@ -250,7 +251,8 @@ using namespace lmk;
 
 extern "C" int lmk_landmark_scores(const void* q, const void* k_cache, const lmk_cache_desc* desc,
                                    const void* cos_table, const void* sin_table, int n_pos, int rotary, float* scores,
-                                   int B, int H, int T, int D, float sm_scale, int softmax, int dtype, void* stream) {
+                                   int B, int H, int T, int D, float sm_scale, int softmax, int dtype, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
   int rc = check_desc(desc, "landmark_scores");
   if (rc != LMK_OK) return rc;
   LMK_CHECK_ARG(q && k_cache && scores, "landmark_scores: null pointer");
@@ -262,9 +264,22 @@ extern "C" int lmk_landmark_scores(const void* q, const void* k_cache, const lmk
                 "landmark_scores: rotary tables missing");
   LMK_CHECK_ARG((int64_t)B * H <= 65535 && (T + kScTile - 1) / kScTile <= 65535, "landmark_scores: grid too large");
   cudaStream_t st = (cudaStream_t)stream;
+  const int64_t rows = (int64_t)B * H * T;
+  if (workspace != nullptr && scores_sm100_supported(D, dtype, T, desc->n_blocks) &&
+      workspace_bytes >= scores_sm100_workspace(B, H, desc->n_blocks) && ((uintptr_t)workspace % 256 == 0) &&
+      ((uintptr_t)q % 16 == 0)) {
+    rc = scores_sm100(q, k_cache, *desc, cos_table, sin_table, n_pos, rotary, scores, B, H, T, sm_scale, dtype,
+                      workspace, st);
+    if (rc != LMK_OK) return rc;
+    if (softmax) {
+      if (dtype == LMK_F16) row_softmax_kernel<__half><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(scores, rows, desc->n_blocks);
+      else row_softmax_kernel<__nv_bfloat16><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(scores, rows, desc->n_blocks);
+      LMK_CUDA(cudaGetLastError());
+    }
+    return LMK_OK;
+  }
   size_t smem = sizeof(float) * ((size_t)kScTile * D + (size_t)kScTile * (D + 1));
   dim3 grid((desc->n_blocks + kScTile - 1) / kScTile, (T + kScTile - 1) / kScTile, B * H);
-  const int64_t rows = (int64_t)B * H * T;
 #define LMK_SC_LAUNCH(TT)                                                                                          \
   do {                                                                                                             \
     LMK_CUDA(cudaFuncSetAttribute(landmark_scores_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
@@ -281,6 +296,11 @@ extern "C" int lmk_landmark_scores(const void* q, const void* k_cache, const lmk
 #undef LMK_SC_LAUNCH
   LMK_CUDA(cudaGetLastError());
   return LMK_OK;
+}
+
+extern "C" size_t lmk_landmark_scores_workspace(int B, int H, int T, int D, int n_blocks, int dtype) {
+  if (B < 1 || H < 1 || n_blocks < 1 || !scores_sm100_supported(D, dtype, T, n_blocks)) return 0;
+  return scores_sm100_workspace(B, H, n_blocks);
 }
 
 extern "C" int lmk_topk_sorted(const float* scores, int32_t* idx_out, int64_t outer_count, int64_t inner_count,

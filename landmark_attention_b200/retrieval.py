@@ -53,9 +53,11 @@ def landmark_scores(q, k_cache, desc, cos=None, sin=None, rotary=L.ROTARY_NONE, 
         sm_scale = 1.0 / math.sqrt(D)
     scores = torch.empty((B, H, T, desc.n_blocks), device=q.device, dtype=torch.float32)
     n_pos = 0 if cos is None else cos.shape[0]
+    need = L.lib().lmk_landmark_scores_workspace(B, H, T, D, desc.n_blocks, L.dtype_code(q))
+    ws = torch.empty(int(need), dtype=torch.uint8, device=q.device) if need else None
     rc = L.lib().lmk_landmark_scores(L.ptr(q), L.ptr(k_cache), ctypes.byref(desc), L.ptr(cos), L.ptr(sin), n_pos,
                                      rotary, L.ptr(scores), B, H, T, D, float(sm_scale), int(softmax),
-                                     L.dtype_code(q), L.stream_ptr(q.device))
+                                     L.dtype_code(q), L.ptr(ws), int(need), L.stream_ptr(q.device))
     L.check(rc, "lmk_landmark_scores")
     return scores
 

@@ -58,7 +58,7 @@ def test_retrieval_argument_checks():
     lib = P.lib()
     one = ctypes.c_void_p(256)
     d = L.CacheDesc(1, 1, 1, 1, 4, 0, 8, 9, 0)        # top_k > n_blocks
-    rc = lib.lmk_landmark_scores(one, one, ctypes.byref(d), None, None, 0, 0, one, 1, 1, 1, 64, 1.0, 0, 0, None)
+    rc = lib.lmk_landmark_scores(one, one, ctypes.byref(d), None, None, 0, 0, one, 1, 1, 1, 64, 1.0, 0, 0, None, 0, None)
     assert rc == L.LMK_ERR_INVALID
     assert lib.lmk_topk_sorted(one, one, 1, 1, 0, 0, 1, 0, 8, 9, 0, None) == L.LMK_ERR_INVALID
     d = L.CacheDesc(8, 8, 8, 8, 4, 0, 8, 2, 0)

@@ -1,5 +1,6 @@
 """Parity of the retrieval kernels: landmark scores, top-k (bit-exact indices on identical fp32 scores), block gather
 with rotary, the LLaMA cache branch and the lm_benchmark block cache."""
+import ctypes
 import math
 
 import pytest
@@ -123,3 +124,36 @@ def test_block_cache_against_golden(golden, method):
         assert torch.equal(d["v"].cpu(), r["v_prefix"])
         assert (store.cache_iter, store.cache_size) == (r["cache_iter"], r["cache_size"])
         store.store_in_cache(r["k"].to(DEV), {"v": r["v"].to(DEV), "is_mem": r["is_mem"].to(DEV)})
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_scores_on_tensor_cores(dtype):
+    # D = 128, T >= 128 and n_blocks >= 128 take the tcgen05 scoring path (rotated landmarks staged in a workspace)
+    torch.manual_seed(3)
+    B, H, T, D, blk, nblk, top_k = 1, 3, 200, 128, 8, 160, 4
+    C = nblk * blk
+    q = torch.randn(B, H, T, D).to(dtype)
+    pk = torch.randn(B, H, C, D).to(dtype)
+    prefix_len = C - (top_k + 1) * blk
+    cos, sin = P.rotary_tables_half(C + T + 1, D, dtype, DEV)
+    pkc = pk.to(DEV)
+    st = pkc.stride()
+    desc = L.CacheDesc(st[0], st[1], st[2] * blk, st[2], nblk, 0, blk, top_k, prefix_len)
+    assert L.lib().lmk_landmark_scores_workspace(B, H, T, D, nblk, L.dtype_code(q)) == B * H * nblk * D * 2
+    scores = P.landmark_scores(q.to(DEV), pkc, desc, cos, sin, L.ROTARY_HALF)
+    assert L.device_status() == 0
+    mem_pos, _ = O.llama_slot_positions(nblk, top_k, C, blk)
+    lm = O.rotary_half_split(pk.view(B, H, nblk, blk, D)[:, :, :, blk - 1], mem_pos.view(1, 1, nblk))
+    exp = torch.matmul(q.float(), lm.float().transpose(2, 3)) / math.sqrt(D)
+    assert (scores.cpu() - exp).abs().max().item() < 6e-2
+    # same values as the CUDA-core kernel up to the rounding of the fp32 accumulation order
+    n_pos = cos.shape[0]
+    ref = torch.empty_like(scores)
+    rc = L.lib().lmk_landmark_scores(L.ptr(q.to(DEV)), L.ptr(pkc), ctypes.byref(desc), L.ptr(cos), L.ptr(sin), n_pos,
+                                     L.ROTARY_HALF, L.ptr(ref), B, H, T, D, 1.0 / math.sqrt(D), 0, L.dtype_code(q), None,
+                                     0, L.stream_ptr(ref.device))
+    L.check(rc, "lmk_landmark_scores")
+    assert (scores - ref).abs().max().item() < 4e-2
+    assert ((scores - ref).abs() > 0).float().mean().item() < 0.02
+    sel = P.topk_sorted(scores, top_k)
+    assert torch.equal(sel.long(), scores.topk(top_k, dim=-1).indices.sort(dim=-1).values)
