@@ -28,5 +28,6 @@ int attn_sm100_fwd(const AttnParams& p, int dtype, cudaStream_t st);
 int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st);
 size_t attn_sm100_bwd_workspace(int B, int H, int Lq, int Lk, int D);
 int device_status(int* out, int clear);
+int* device_status_word();
 
 }  // namespace lmk

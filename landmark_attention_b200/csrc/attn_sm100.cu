@@ -27,6 +27,7 @@
 //   Per tile pair: earlier block  dS_j = g s_j (dP_j - nD) scale,  dS_landmark = g (nD - delta) scale,  P_j = g s_j,
 //   with s = softmax inside the block, g = exp(l_n - M) / L, nD = sum_j s_j dP_j;  own block: p = exp(S - M) / L,
 //   dS = p (dP - delta) scale.                                                                      (:152-305)
+#include <stdlib.h>
 #include "common.cuh"
 #include "attn_params.h"
 #include "sm100_ptx.cuh"
@@ -657,28 +658,32 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
 // ---------------------------------------------------------------------------------------------- backward: delta
 template <bool kBf16>
-__global__ void __launch_bounds__(256) sm100_delta_kernel(const uint2* __restrict__ o, const uint2* __restrict__ dO,
+__global__ void __launch_bounds__(256) sm100_delta_kernel(const uint4* __restrict__ o, const uint4* __restrict__ dO,
                                                           float* __restrict__ delta, int64_t rows) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const uint2 a = o[row * 32 + lane], b = dO[row * 32 + lane];   // 4 elements per lane, 128 per row
-  float acc;
-  if (kBf16) {
-    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
-    float2 a0 = __bfloat1622float2(pa[0]), a1 = __bfloat1622float2(pa[1]);
-    float2 b0 = __bfloat1622float2(pb[0]), b1 = __bfloat1622float2(pb[1]);
-    acc = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
-  } else {
-    const __half2* pa = reinterpret_cast<const __half2*>(&a);
-    const __half2* pb = reinterpret_cast<const __half2*>(&b);
-    float2 a0 = __half22float2(pa[0]), a1 = __half22float2(pa[1]);
-    float2 b0 = __half22float2(pb[0]), b1 = __half22float2(pb[1]);
-    acc = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+  // 16 lanes per row (8 elements = 16 bytes per lane), two rows per warp, 16 rows per CTA
+  const int lane = threadIdx.x & 31, sub = lane & 15;
+  const int64_t row = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 5) * 2 + (lane >> 4);
+  float acc = 0.f;
+  if (row < rows) {
+    const uint4 a = o[row * 16 + sub], b = dO[row * 16 + sub];
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 fa, fb;
+      if (kBf16) {
+        fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+        fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
+      } else {
+        fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
+        fb = __half22float2(*reinterpret_cast<const __half2*>(&bw[i]));
+      }
+      acc = fmaf(fa.x, fb.x, acc);
+      acc = fmaf(fa.y, fb.y, acc);
+    }
   }
-  acc = warp_sum(acc);
-  if (lane == 0) delta[row] = acc;
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < rows && sub == 0) delta[row] = acc;
 }
 
 // One (query row, key block) pair of the backward pass, staged to keep the softmax threads below 168 registers
@@ -811,17 +816,24 @@ struct DkvSmem {
   uint64_t sdp_free[kSdpBufs];
   uint64_t pds_ready[2];
   uint64_t pds_free[2];
-  uint64_t acc_full;
+  uint64_t acc_full[2];    // one per softmax warpgroup: a parity wait is only sound for a waiter that sees every phase
+  uint64_t acc_empty;
+  uint64_t kv_empty;
   uint32_t tmem_base;
 };
 
+// Persistent: the grid is one CTA per SM; CTA c works through the units (key block n, batch*head) numbered
+// w = n * BH + bh for w = c, c + grid, c + 2 grid, ...  Low key blocks see the most query tiles, so every CTA receives
+// units of every size class, heaviest first.  Loads, S/dP products and the softmax of the next unit start while the
+// accumulators of the current unit are still being drained; only the first accumulating MMA of a unit waits for that
+// drain (acc_empty).  All barrier phases derive from counters that run across units.
 template <bool kBf16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                      const float* __restrict__ L_ptr, const float* __restrict__ M_ptr,
                      const float* __restrict__ delta_ptr, void* __restrict__ dk_ptr, void* __restrict__ dv_ptr,
-                     int H, int Lq, int Lk, float scale, float scale_log2) {
+                     int H, int BH, int Lq, int Lk, float scale, float scale_log2) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -833,15 +845,22 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   DkvSmem* sm = reinterpret_cast<DkvSmem*>(smem_raw + (base - raw) + 32768u + kDkvStages * 65536u + 65536u);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n = blockIdx.y;                              // key block; low blocks see the most query tiles
-  const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
   const int prefix_blocks = (Lk - Lq) / kBlk;
   const int n_tiles = Lq / kQTile;
-  const int tq0 = n > prefix_blocks ? (n - prefix_blocks) / 2 : 0;
-  const int n_items = n_tiles - tq0;
+  const int n_units = (Lk / kBlk) * BH;
+  // unit w -> key block, head, first query tile that sees the block, number of query tiles
+  // round r of the schedule hands units r*grid .. r*grid+grid-1 to the CTAs in alternating direction (a snake), which
+  // evens out the slowly decreasing unit sizes; an index past the end terminates the loops
+  auto unit_of = [&](int r) {
+    const int c = (r & 1) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    return r * (int)gridDim.x + c;
+  };
+  auto unit_block = [&](int w) { return w / BH; };
+  auto unit_tq0 = [&](int n) { return n > prefix_blocks ? (n - prefix_blocks) / 2 : 0; };
 
   if (tid == 0) {
     mbar_init(smem_u32(&sm->kv_full), 1);
+    mbar_init(smem_u32(&sm->kv_empty), 1);
     for (int s = 0; s < kDkvStages; ++s) {
       mbar_init(smem_u32(&sm->full[s]), 1);
       mbar_init(smem_u32(&sm->empty[s]), 1);
@@ -854,7 +873,9 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(smem_u32(&sm->pds_ready[g]), 128);
       mbar_init(smem_u32(&sm->pds_free[g]), 1);
     }
-    mbar_init(smem_u32(&sm->acc_full), 1);
+    mbar_init(smem_u32(&sm->acc_full[0]), 1);
+    mbar_init(smem_u32(&sm->acc_full[1]), 1);
+    mbar_init(smem_u32(&sm->acc_empty), 128);
     mbar_init_fence();
   }
   if (warp == kBwdGroups * 4 + 1) tmem_alloc(smem_u32(&sm->tmem_base), 512);
@@ -870,128 +891,163 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_v);
       prefetch_tensormap(&tm_do);
-      const uint32_t kvb = smem_u32(&sm->kv_full);
-      mbar_arrive_expect_tx(kvb, 2 * kTileBytes);
-      tma_load_4d(k_tile, &tm_k, kvb, 0, n * kBlk, h, b);
-      tma_load_4d(k_tile + kHalfTile, &tm_k, kvb, 64, n * kBlk, h, b);
-      tma_load_4d(v_tile, &tm_v, kvb, 0, n * kBlk, h, b);
-      tma_load_4d(v_tile + kHalfTile, &tm_v, kvb, 64, n * kBlk, h, b);
-      for (int i = 0; i < n_items; ++i) {
-        const int s = i % kDkvStages;
-        mbar_wait(smem_u32(&sm->empty[s]), ((i / kDkvStages) & 1) ^ 1, &g_lmk_status, kErrDkvProducer);
-        const uint32_t fb = smem_u32(&sm->full[s]);
-        const int r0 = (tq0 + i) * kQTile;
-        mbar_arrive_expect_tx(fb, 4 * kTileBytes);
-        tma_load_4d(q_slot(s), &tm_q, fb, 0, r0, h, b);
-        tma_load_4d(q_slot(s) + kTileBytes, &tm_q, fb, 64, r0, h, b);
-        tma_load_4d(do_slot(s), &tm_do, fb, 0, r0, h, b);
-        tma_load_4d(do_slot(s) + kTileBytes, &tm_do, fb, 64, r0, h, b);
+      int it = 0, u = 0;
+      for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
+        const int n = unit_block(w), bh = w - n * BH, b = bh / H, h = bh - b * H;
+        const int tq0 = unit_tq0(n), n_items = n_tiles - tq0;
+        const uint32_t kvb = smem_u32(&sm->kv_full);
+        mbar_wait(smem_u32(&sm->kv_empty), (u & 1) ^ 1, &g_lmk_status, kErrDkvProducer);
+        mbar_arrive_expect_tx(kvb, 2 * kTileBytes);
+        tma_load_4d(k_tile, &tm_k, kvb, 0, n * kBlk, h, b);
+        tma_load_4d(k_tile + kHalfTile, &tm_k, kvb, 64, n * kBlk, h, b);
+        tma_load_4d(v_tile, &tm_v, kvb, 0, n * kBlk, h, b);
+        tma_load_4d(v_tile + kHalfTile, &tm_v, kvb, 64, n * kBlk, h, b);
+        for (int i = 0; i < n_items; ++i, ++it) {
+          const int s = it % kDkvStages;
+          mbar_wait(smem_u32(&sm->empty[s]), ((it / kDkvStages) & 1) ^ 1, &g_lmk_status, kErrDkvProducer);
+          const uint32_t fb = smem_u32(&sm->full[s]);
+          const int r0 = (tq0 + i) * kQTile;
+          mbar_arrive_expect_tx(fb, 4 * kTileBytes);
+          tma_load_4d(q_slot(s), &tm_q, fb, 0, r0, h, b);
+          tma_load_4d(q_slot(s) + kTileBytes, &tm_q, fb, 64, r0, h, b);
+          tma_load_4d(do_slot(s), &tm_do, fb, 0, r0, h, b);
+          tma_load_4d(do_slot(s) + kTileBytes, &tm_do, fb, 64, r0, h, b);
+        }
       }
     }
     __syncwarp();
   } else if (warp == kBwdGroups * 4 + 1) {
-    // S = Q K^T and dP = dO V^T of item j into TMEM buffer j & 1
+    // S = Q K^T and dP = dO V^T of item `it` into TMEM buffer it % kSdpBufs
     if (lane == 0) {
       constexpr uint32_t fmt = kBf16 ? 1u : 0u;
       constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);
-      mbar_wait(smem_u32(&sm->kv_full), 0, &g_lmk_status, kErrDkvMma);
       const uint64_t dkt = smem_desc_sw128(k_tile, 16, 1024), dvt = smem_desc_sw128(v_tile, 16, 1024);
       const uint64_t dq0 = smem_desc_sw128(q_slot(0), 16, 1024), ddo0 = smem_desc_sw128(do_slot(0), 16, 1024);
-      for (int j = 0; j < n_items; ++j) {
-        const int s = j % kDkvStages, sb = j % kSdpBufs;
-        mbar_wait(smem_u32(&sm->full[s]), (j / kDkvStages) & 1, &g_lmk_status, kErrDkvMma);
-        if (j >= kSdpBufs)
-          mbar_wait(smem_u32(&sm->sdp_free[sb]), ((j / kSdpBufs) & 1) ^ 1, &g_lmk_status, kErrDkvMma);
-        tc_fence_after();
-        const uint64_t dq = desc_advance(dq0, (uint32_t)s * 65536u), ddo = desc_advance(ddo0, (uint32_t)s * 65536u);
+      int it = 0, u = 0;
+      for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
+        const int n_items = n_tiles - unit_tq0(unit_block(w));
+        mbar_wait(smem_u32(&sm->kv_full), u & 1, &g_lmk_status, kErrDkvMma);
+        for (int i = 0; i < n_items; ++i, ++it) {
+          const int s = it % kDkvStages, sb = it % kSdpBufs;
+          LMK_STAMP(11, it);
+          mbar_wait(smem_u32(&sm->full[s]), (it / kDkvStages) & 1, &g_lmk_status, kErrDkvMma);
+          LMK_STAMP(12, it);
+          if (it >= kSdpBufs)
+            mbar_wait(smem_u32(&sm->sdp_free[sb]), ((it / kSdpBufs) & 1) ^ 1, &g_lmk_status, kErrDkvMma);
+          tc_fence_after();
+          const uint64_t dq = desc_advance(dq0, (uint32_t)s * 65536u), ddo = desc_advance(ddo0, (uint32_t)s * 65536u);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk)
-          mma_f16_ss(tmem_s + sb * 64, desc_advance(dq, kmajor_step(kk, kTileBytes)),
-                     desc_advance(dkt, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
+          for (int kk = 0; kk < kD / 16; ++kk)
+            mma_f16_ss(tmem_s + sb * 64, desc_advance(dq, kmajor_step(kk, kTileBytes)),
+                       desc_advance(dkt, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk)
-          mma_f16_ss(tmem_dp + sb * 64, desc_advance(ddo, kmajor_step(kk, kTileBytes)),
-                     desc_advance(dvt, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
-        mma_commit(smem_u32(&sm->sdp_full[sb]));
+          for (int kk = 0; kk < kD / 16; ++kk)
+            mma_f16_ss(tmem_dp + sb * 64, desc_advance(ddo, kmajor_step(kk, kTileBytes)),
+                       desc_advance(dvt, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
+          mma_commit(smem_u32(&sm->sdp_full[sb]));
+          LMK_STAMP(13, it);
+        }
+        mma_commit(smem_u32(&sm->kv_empty));      // K / V tiles may be replaced once these products are done
       }
     }
     __syncwarp();
   } else if (warp == kBwdGroups * 4 + 2) {
+    // dV^T += dO^T P and dK^T += Q^T dS.  A = dO^T / Q^T: MN-major view of the row-major [128 q x 128 d] tile (second
+    // 64-feature half 16 KB further); B = P / dS: MN-major view of the [128 q x 64 k] tile; a K-step is 16 query rows
+    // = 2048 bytes.
     if (lane == 0) {
-      // dV^T += dO^T P and dK^T += Q^T dS.  A = dO^T / Q^T: MN-major view of the row-major [128 q x 128 d] tile
-      // (second 64-feature half 16 KB further); B = P / dS: MN-major view of the [128 q x 64 k] tile; a K-step is 16
-      // query rows = 2048 bytes.
       constexpr uint32_t fmt = kBf16 ? 1u : 0u;
       constexpr uint32_t idesc_t = instr_desc_f16(fmt, 128, 64, 1, 1);
       const uint64_t dq0t = smem_desc_sw128(q_slot(0), kTileBytes, 1024);
       const uint64_t ddo0t = smem_desc_sw128(do_slot(0), kTileBytes, 1024);
       const uint64_t dp0 = smem_desc_sw128(p_tile(0), 16, 1024), dds0 = smem_desc_sw128(ds_tile(0), 16, 1024);
-      for (int i = 0; i < n_items; ++i) {
-        const int s = i % kDkvStages, g = i & 1;
-        mbar_wait(smem_u32(&sm->pds_ready[g]), (i >> 1) & 1, &g_lmk_status, kErrDkvMma);
-        tc_fence_after();
-        const uint64_t ddot = desc_advance(ddo0t, (uint32_t)s * 65536u), dqt = desc_advance(dq0t, (uint32_t)s * 65536u);
-        const uint64_t dpt = desc_advance(dp0, (uint32_t)g * 32768u), ddst = desc_advance(dds0, (uint32_t)g * 32768u);
+      int it = 0, u = 0;
+      for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
+        const int n_items = n_tiles - unit_tq0(unit_block(w));
+        for (int i = 0; i < n_items; ++i, ++it) {
+          const int s = it % kDkvStages, g = it & 1;
+          LMK_STAMP(8, it);
+          mbar_wait(smem_u32(&sm->pds_ready[g]), (it >> 1) & 1, &g_lmk_status, kErrDkvMma);
+          LMK_STAMP(9, it);
+          if (i == 0) mbar_wait(smem_u32(&sm->acc_empty), (u & 1) ^ 1, &g_lmk_status, kErrDkvMma);
+          tc_fence_after();
+          const uint64_t ddot = desc_advance(ddo0t, (uint32_t)s * 65536u), dqt = desc_advance(dq0t, (uint32_t)s * 65536u);
+          const uint64_t dpt = desc_advance(dp0, (uint32_t)g * 32768u), ddst = desc_advance(dds0, (uint32_t)g * 32768u);
 #pragma unroll
-        for (int kk = 0; kk < kQTile / 16; ++kk)
-          mma_f16_ss(tmem_dv, desc_advance(ddot, kk * 2048), desc_advance(dpt, kk * 2048), idesc_t,
-                     (i > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kQTile / 16; ++kk)
+            mma_f16_ss(tmem_dv, desc_advance(ddot, kk * 2048), desc_advance(dpt, kk * 2048), idesc_t,
+                       (i > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < kQTile / 16; ++kk)
-          mma_f16_ss(tmem_dk, desc_advance(dqt, kk * 2048), desc_advance(ddst, kk * 2048), idesc_t,
-                     (i > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(smem_u32(&sm->pds_free[g]));
-        mma_commit(smem_u32(&sm->empty[s]));
+          for (int kk = 0; kk < kQTile / 16; ++kk)
+            mma_f16_ss(tmem_dk, desc_advance(dqt, kk * 2048), desc_advance(ddst, kk * 2048), idesc_t,
+                       (i > 0 || kk > 0) ? 1u : 0u);
+          mma_commit(smem_u32(&sm->pds_free[g]));
+          mma_commit(smem_u32(&sm->empty[s]));
+          LMK_STAMP(10, it);
+        }
+        mma_commit(smem_u32(&sm->acc_full[u & 1]));
       }
-      mma_commit(smem_u32(&sm->acc_full));
     }
     __syncwarp();
   } else {
-    const int g = warp >> 2;                       // warpgroup: handles items i with i % kBwdGroups == g
+    const int g = warp >> 2;                       // warpgroup: handles items with (running item count) % 2 == g
     const int row = tid & 127;
     const int half = row >> 6;
     const int vis = min(row & 63, kBlk - 2);
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    for (int i = g; i < n_items; i += kBwdGroups) {
-      const int tq = tq0 + i;
-      const int own = prefix_blocks + 2 * tq + half;
-      const int64_t grow = (int64_t)bh * Lq + tq * kQTile + row;
-      const float M2 = M_ptr[grow] * kLog2e, Linv = 1.f / L_ptr[grow], delta = delta_ptr[grow];
-      const int sb = i % kSdpBufs, pb = i & 1;
-      mbar_wait(smem_u32(&sm->sdp_full[sb]), (i / kSdpBufs) & 1, &g_lmk_status, kErrDkvSoftmax);
-      tc_fence_after();
-      const int kind = n > own ? 0 : (n == own ? 1 : 2);
-      bwd_item<kBf16, true>(tmem_s + sb * 64 + lane_base, tmem_dp + sb * 64 + lane_base, smem_u32(&sm->sdp_free[sb]),
-                            kind, vis, scale_log2, scale, M2, Linv, delta, p_tile(pb), ds_tile(pb), row, [&]() {
-                              if (i >= 2)
-                                mbar_wait(smem_u32(&sm->pds_free[pb]), ((i >> 1) - 1) & 1, &g_lmk_status,
-                                          kErrDkvSoftmax);
-                            });
-      fence_proxy_async_smem();
-      mbar_arrive(smem_u32(&sm->pds_ready[pb]));
-    }
-    // epilogue (warpgroup 0): thread = feature d, TMEM column = key j  ->  dV[key][d], dK[key][d]
-    if (g == 0) {
-      mbar_wait(smem_u32(&sm->acc_full), 0, &g_lmk_status, kErrDkvEpilogue);
-      tc_fence_after();
-      uint16_t* dvp = reinterpret_cast<uint16_t*>(dv_ptr) + ((int64_t)bh * Lk + (int64_t)n * kBlk) * kD + row;
-      uint16_t* dkp = reinterpret_cast<uint16_t*>(dk_ptr) + ((int64_t)bh * Lk + (int64_t)n * kBlk) * kD + row;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_dv + c * 32 + lane_base, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          dvp[(int64_t)(c * 32 + j) * kD] = (uint16_t)(pack2<kBf16>(__uint_as_float(r[j]), 0.f) & 0xffffu);
-        tmem_ld_32x32b_x32(tmem_dk + c * 32 + lane_base, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          dkp[(int64_t)(c * 32 + j) * kD] = (uint16_t)(pack2<kBf16>(__uint_as_float(r[j]), 0.f) & 0xffffu);
+    int it0 = 0, u = 0;
+    for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
+      const int n = unit_block(w), bh = w - n * BH;
+      const int tq0 = unit_tq0(n), n_items = n_tiles - tq0;
+      for (int i = (it0 + g) & 1; i < n_items; i += kBwdGroups) {
+        const int it = it0 + i;
+        const int tq = tq0 + i;
+        const int own = prefix_blocks + 2 * tq + half;
+        const int64_t grow = (int64_t)bh * Lq + tq * kQTile + row;
+        const float M2 = M_ptr[grow] * kLog2e, Linv = 1.f / L_ptr[grow], delta = delta_ptr[grow];
+        const int sb = it % kSdpBufs, pb = it & 1;
+        if (row == 0) LMK_STAMP(g * 4 + 0, it);
+        mbar_wait(smem_u32(&sm->sdp_full[sb]), (it / kSdpBufs) & 1, &g_lmk_status, kErrDkvSoftmax);
+        if (row == 0) LMK_STAMP(g * 4 + 1, it);
+        tc_fence_after();
+        const int kind = n > own ? 0 : (n == own ? 1 : 2);
+        bwd_item<kBf16, true>(tmem_s + sb * 64 + lane_base, tmem_dp + sb * 64 + lane_base,
+                              smem_u32(&sm->sdp_free[sb]), kind, vis, scale_log2, scale, M2, Linv, delta, p_tile(pb),
+                              ds_tile(pb), row, [&]() {
+                                if (it >= 2)
+                                  mbar_wait(smem_u32(&sm->pds_free[pb]), ((it >> 1) - 1) & 1, &g_lmk_status,
+                                            kErrDkvSoftmax);
+                              });
+        if (row == 0) LMK_STAMP(g * 4 + 2, it);
+        fence_proxy_async_smem();
+        mbar_arrive(smem_u32(&sm->pds_ready[pb]));
+        if (row == 0) LMK_STAMP(g * 4 + 3, it);
       }
-      tc_fence_before();
+      it0 += n_items;
+      // epilogue, alternating between the warpgroups: thread = feature d, TMEM column = key j -> dV[key][d], dK[key][d]
+      if (g == (u & 1)) {
+        mbar_wait(smem_u32(&sm->acc_full[g]), (u >> 1) & 1, &g_lmk_status, kErrDkvEpilogue);
+        tc_fence_after();
+        uint32_t rv[2][32], rk[2][32];
+        tmem_ld_32x32b_x32(tmem_dv + lane_base, rv[0]);
+        tmem_ld_32x32b_x32(tmem_dv + 32 + lane_base, rv[1]);
+        tmem_ld_32x32b_x32(tmem_dk + lane_base, rk[0]);
+        tmem_ld_32x32b_x32(tmem_dk + 32 + lane_base, rk[1]);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sm->acc_empty));     // the next unit may start accumulating
+        uint16_t* dvp = reinterpret_cast<uint16_t*>(dv_ptr) + ((int64_t)bh * Lk + (int64_t)n * kBlk) * kD + row;
+        uint16_t* dkp = reinterpret_cast<uint16_t*>(dk_ptr) + ((int64_t)bh * Lk + (int64_t)n * kBlk) * kD + row;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            dvp[(int64_t)(c * 32 + j) * kD] = (uint16_t)(pack2<kBf16>(__uint_as_float(rv[c][j]), 0.f) & 0xffffu);
+            dkp[(int64_t)(c * 32 + j) * kD] = (uint16_t)(pack2<kBf16>(__uint_as_float(rk[c][j]), 0.f) & 0xffffu);
+          }
+      }
     }
+    tc_fence_before();
   }
   __syncthreads();
   if (warp == kBwdGroups * 4 + 1) {
@@ -1308,15 +1364,24 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
   const float scale_log2 = p.scale * kLog2e;
   const size_t smem_dkv = 1024 + 32768 + kDkvStages * 65536 + 65536 + sizeof(DkvSmem);
   const size_t smem_dq = 1024 + 65536 + kDqStages * 32768 + sizeof(DqSmem);
-  dim3 grid_dkv(p.B * p.H, p.Lk / kBlk), grid_dq(p.B * p.H, p.Lq / kQTile);
+  int dev = 0, n_sm = 148;
+  LMK_CUDA(cudaGetDevice(&dev));
+  LMK_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+  if (const char* cap = getenv("LMK_MAX_CTAS")) {   // tests: force several work units per persistent CTA
+    const int v = atoi(cap);
+    if (v >= 1 && v < n_sm) n_sm = v;
+  }
+  const int dkv_units = (p.Lk / kBlk) * p.B * p.H;
+  dim3 grid_dkv(dkv_units < n_sm ? dkv_units : n_sm), grid_dq(p.B * p.H, p.Lq / kQTile);
 #define LMK_BWD_LAUNCH(BF)                                                                                          \
   do {                                                                                                              \
-    sm100_delta_kernel<BF><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(                                             \
-        reinterpret_cast<const uint2*>(p.o), reinterpret_cast<const uint2*>(p.dO), delta, rows);                    \
+    sm100_delta_kernel<BF><<<(unsigned)((rows + 15) / 16), 256, 0, st>>>(                                           \
+        reinterpret_cast<const uint4*>(p.o), reinterpret_cast<const uint4*>(p.dO), delta, rows);                    \
     LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dkv_kernel<BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
                                   (int)smem_dkv));                                                                  \
     sm100_bwd_dkv_kernel<BF><<<grid_dkv, kBwdThreads, smem_dkv, st>>>(tq, tk, tv, tdo, p.L, p.M, delta, p.dk, p.dv, \
-                                                                     p.H, p.Lq, p.Lk, p.scale, scale_log2);         \
+                                                                     p.H, p.B * p.H, p.Lq, p.Lk, p.scale,           \
+                                                                     scale_log2);                                   \
     LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dq_kernel<BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
                                   (int)smem_dq));                                                                   \
     sm100_bwd_dq_kernel<BF><<<grid_dq, kBwdThreads, smem_dq, st>>>(tq, tk, tv, tdo, p.L, p.M, delta, p.dq, p.H,     \
@@ -1336,6 +1401,13 @@ extern "C" int lmk_trace_set(long long* buf) {
   return cudaMemcpyToSymbol(g_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : -3;
 }
 #endif
+
+// Device address of the status word on the current device, for kernels compiled in other translation units.
+int* device_status_word() {
+  int* ptr = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_lmk_status) != cudaSuccess) return nullptr;
+  return ptr;
+}
 
 int device_status(int* out, int clear) {
   int v = 0;

@@ -28,6 +28,35 @@ __device__ __forceinline__ float rotary_elem(float x, float partner_signed, floa
   return to_f32(from_f32<T>(__fadd_rn(a, b)));
 }
 
+// Two rotary outputs at once with the same rounding steps; 16-bit types use the packed float2 -> x2 conversions, which
+// halves the work on the conversion pipe (the gather kernel is otherwise limited by it, not by HBM).
+template <typename T>
+__device__ __forceinline__ void rotary_pair(float x0, float x1, float p0, float p1, float c0, float c1, float s0,
+                                            float s1, T& o0, T& o1) {
+  o0 = from_f32<T>(rotary_elem<T>(x0, p0, c0, s0));
+  o1 = from_f32<T>(rotary_elem<T>(x1, p1, c1, s1));
+}
+template <>
+__device__ __forceinline__ void rotary_pair<__nv_bfloat16>(float x0, float x1, float p0, float p1, float c0, float c1,
+                                                           float s0, float s1, __nv_bfloat16& o0, __nv_bfloat16& o1) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(__fmul_rn(x0, c0), __fmul_rn(x1, c1));
+  const __nv_bfloat162 b = __floats2bfloat162_rn(__fmul_rn(p0, s0), __fmul_rn(p1, s1));
+  const __nv_bfloat162 r = __floats2bfloat162_rn(__fadd_rn(__low2float(a), __low2float(b)),
+                                                 __fadd_rn(__high2float(a), __high2float(b)));
+  o0 = __low2bfloat16(r);
+  o1 = __high2bfloat16(r);
+}
+template <>
+__device__ __forceinline__ void rotary_pair<__half>(float x0, float x1, float p0, float p1, float c0, float c1, float s0,
+                                                    float s1, __half& o0, __half& o1) {
+  const __half2 a = __floats2half2_rn(__fmul_rn(x0, c0), __fmul_rn(x1, c1));
+  const __half2 b = __floats2half2_rn(__fmul_rn(p0, s0), __fmul_rn(p1, s1));
+  const __half2 r = __floats2half2_rn(__fadd_rn(__low2float(a), __low2float(b)),
+                                      __fadd_rn(__high2float(a), __high2float(b)));
+  o0 = __low2half(r);
+  o1 = __high2half(r);
+}
+
 // ------------------------------------------------------------------------------------------- landmark scores
 constexpr int kScTile = 32;
 
@@ -216,16 +245,17 @@ __global__ void __launch_bounds__(128) gather_kv_kernel(const T* __restrict__ kc
           const bool lo = d0 < D / 2;
           Vec y = *reinterpret_cast<const Vec*>(krow + (lo ? d0 + D / 2 : d0 - D / 2));
 #pragma unroll
-          for (int u = 0; u < VEC; ++u) {
-            float partner = lo ? -to_f32(y.v[u]) : to_f32(y.v[u]);
-            o.v[u] = from_f32<T>(rotary_elem<T>(to_f32(x.v[u]), partner, to_f32(c.v[u]), to_f32(s.v[u])));
+          for (int u = 0; u < VEC; u += 2) {
+            const float p0 = lo ? -to_f32(y.v[u]) : to_f32(y.v[u]);
+            const float p1 = lo ? -to_f32(y.v[u + 1]) : to_f32(y.v[u + 1]);
+            rotary_pair<T>(to_f32(x.v[u]), to_f32(x.v[u + 1]), p0, p1, to_f32(c.v[u]), to_f32(c.v[u + 1]),
+                           to_f32(s.v[u]), to_f32(s.v[u + 1]), o.v[u], o.v[u + 1]);
           }
         } else {
 #pragma unroll
-          for (int u = 0; u < VEC; ++u) {
-            float partner = (u & 1) ? to_f32(x.v[u - 1]) : -to_f32(x.v[u + 1]);
-            o.v[u] = from_f32<T>(rotary_elem<T>(to_f32(x.v[u]), partner, to_f32(c.v[u]), to_f32(s.v[u])));
-          }
+          for (int u = 0; u < VEC; u += 2)
+            rotary_pair<T>(to_f32(x.v[u]), to_f32(x.v[u + 1]), -to_f32(x.v[u + 1]), to_f32(x.v[u]), to_f32(c.v[u]),
+                           to_f32(c.v[u + 1]), to_f32(s.v[u]), to_f32(s.v[u + 1]), o.v[u], o.v[u + 1]);
         }
       }
       *reinterpret_cast<Vec*>(k_out + out_base + (int64_t)r * D + d0) = o;

@@ -9,10 +9,9 @@
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "scores_sm100.h"
+#include "attn_params.h"
 
 namespace lmk {
-
-extern __device__ int g_lmk_status;
 
 namespace {
 
@@ -65,7 +64,8 @@ struct ScoreSmem {
 template <typename T>
 __global__ void __launch_bounds__(128) scores_gemm_kernel(const __grid_constant__ CUtensorMap tm_q,
                                                           const __grid_constant__ CUtensorMap tm_k,
-                                                          float* __restrict__ scores, int Tq, int N, float scale) {
+                                                          float* __restrict__ scores, int Tq, int N, float scale,
+                                                          int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(128) scores_gemm_kernel(const __grid_constant_
     tma_load_3d(a_tile + 16384u, &tm_q, fb, 64, t0, bh);
     tma_load_3d(b_tile, &tm_k, fb, 0, n0, bh);
     tma_load_3d(b_tile + 16384u, &tm_k, fb, 64, n0, bh);
-    mbar_wait(fb, 0, &g_lmk_status, 401);
+    mbar_wait(fb, 0, status, 401);
     tc_fence_after();
     constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
     constexpr uint32_t idesc = instr_desc_f16(fmt, 128, 128, 0, 0);
@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(128) scores_gemm_kernel(const __grid_constant_
     mma_commit(smem_u32(&sm->done));
   }
   __syncwarp();
-  mbar_wait(smem_u32(&sm->done), 0, &g_lmk_status, 402);
+  mbar_wait(smem_u32(&sm->done), 0, status, 402);
   tc_fence_after();
   // Epilogue: TMEM -> registers (thread = token row) -> shared memory (rows padded to 132 floats so that 16-byte
   // stores of 32 different rows spread over all banks) -> global memory one full 512-byte row per warp instruction.
@@ -192,7 +192,9 @@ int run(const void* q, const void* k_cache, const lmk_cache_desc& desc, const vo
   const size_t smem = 1024 + 128 * 132 * 4 + sizeof(ScoreSmem);   // operand tiles (64 KB), reused as the padded output stage
   LMK_CUDA(cudaFuncSetAttribute(scores_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 g2((N + 127) / 128, (Tq + 127) / 128, B * H);
-  scores_gemm_kernel<T><<<g2, 128, smem, st>>>(tq, tk, scores, Tq, N, scale);
+  int* status = device_status_word();
+  if (status == nullptr) return fail(LMK_ERR_CUDA, "device status word is not addressable");
+  scores_gemm_kernel<T><<<g2, 128, smem, st>>>(tq, tk, scores, Tq, N, scale, status);
   LMK_CUDA(cudaGetLastError());
   return LMK_OK;
 }

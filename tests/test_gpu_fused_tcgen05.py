@@ -99,3 +99,15 @@ def test_backward_properties():
     for x, y in zip(a, g):
         assert (x - y).abs().max().item() < 2e-2
     assert L.device_status() == 0
+
+
+def test_persistent_kernels_with_several_units_per_cta(monkeypatch):
+    # cap the persistent grid so that every CTA walks through many work units (cross-unit pipelining, phase counters)
+    q, k, v, do = make(1, 3, 512, 640, torch.bfloat16, 13)
+    ref = run_bwd(q, k, v, do, P.PATH_TCGEN05)
+    for cap in ("1", "2", "5"):
+        monkeypatch.setenv("LMK_MAX_CTAS", cap)
+        got = run_bwd(q, k, v, do, P.PATH_TCGEN05)
+        for a, b in zip(got, ref):
+            assert torch.equal(a, b)
+        assert L.device_status() == 0
