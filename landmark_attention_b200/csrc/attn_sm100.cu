@@ -810,23 +810,25 @@ constexpr int kDkvStages = 2;
 
 struct DkvSmem {
   uint64_t kv_full;
+  uint64_t kv_empty;
   uint64_t full[kDkvStages];
   uint64_t empty[kDkvStages];
-  uint64_t sdp_full[kSdpBufs];
-  uint64_t sdp_free[kSdpBufs];
-  uint64_t pds_ready[2];
-  uint64_t pds_free[2];
-  uint64_t acc_full[2];    // one per softmax warpgroup: a parity wait is only sound for a waiter that sees every phase
-  uint64_t acc_empty;
-  uint64_t kv_empty;
+  uint64_t sdp_full[2];     // per key block of the pair (= per softmax warpgroup)
+  uint64_t sdp_free[2];
+  uint64_t pds_ready;
+  uint64_t pds_free[2];     // [g]: the accumulating MMAs of warpgroup g's latest item have read the P/dS tiles
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
   uint32_t tmem_base;
 };
 
-// Persistent: the grid is one CTA per SM; CTA c works through the units (key block n, batch*head) numbered
-// w = n * BH + bh for w = c, c + grid, c + 2 grid, ...  Low key blocks see the most query tiles, so every CTA receives
-// units of every size class, heaviest first.  Loads, S/dP products and the softmax of the next unit start while the
-// accumulators of the current unit are still being drained; only the first accumulating MMA of a unit waits for that
-// drain (acc_empty).  All barrier phases derive from counters that run across units.
+// Persistent; a work unit is a PAIR of adjacent 64-key blocks (a = 2c, b = 2c+1) of one (batch, head).  Both blocks
+// stay in shared memory while the unit streams the query tiles that see them, so each 64 KB Q/dO tile is fetched from
+// L2 once per 128 keys.  Warpgroup 0 rebuilds P and dS for block a, warpgroup 1 for block b; the products of block b
+// are issued after those of block a, so warpgroup 1 runs about one MMA group behind warpgroup 0 and the two can share
+// a single P/dS tile pair (a writer waits until the accumulating MMAs of the previous item have read it).
+// CTA c takes units w = round * grid + c with the direction alternating per round (snake), heaviest pairs first.
+// Loads, S/dP products and the softmax of the next unit start while the accumulators of the current one are drained.
 template <bool kBf16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -837,26 +839,25 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  const uint32_t k_tile = base, v_tile = base + 16384u;
-  auto q_slot = [&](int s) { return base + 32768u + (uint32_t)s * 65536u; };
-  auto do_slot = [&](int s) { return base + 32768u + (uint32_t)s * 65536u + 32768u; };
-  auto p_tile = [&](int g) { return base + 32768u + kDkvStages * 65536u + (uint32_t)g * 32768u; };
-  auto ds_tile = [&](int g) { return base + 32768u + kDkvStages * 65536u + (uint32_t)g * 32768u + 16384u; };
-  DkvSmem* sm = reinterpret_cast<DkvSmem*>(smem_raw + (base - raw) + 32768u + kDkvStages * 65536u + 65536u);
+  auto k_tile = [&](int g) { return base + (uint32_t)g * 32768u; };             // block g of the pair: K then V
+  auto v_tile = [&](int g) { return base + (uint32_t)g * 32768u + 16384u; };
+  auto q_slot = [&](int s) { return base + 65536u + (uint32_t)s * 65536u; };
+  auto do_slot = [&](int s) { return base + 65536u + (uint32_t)s * 65536u + 32768u; };
+  const uint32_t p_tile = base + 65536u + kDkvStages * 65536u;
+  const uint32_t ds_tile = p_tile + 16384u;
+  DkvSmem* sm = reinterpret_cast<DkvSmem*>(smem_raw + (base - raw) + 65536u + kDkvStages * 65536u + 32768u);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int prefix_blocks = (Lk - Lq) / kBlk;
   const int n_tiles = Lq / kQTile;
-  const int n_units = (Lk / kBlk) * BH;
-  // unit w -> key block, head, first query tile that sees the block, number of query tiles
-  // round r of the schedule hands units r*grid .. r*grid+grid-1 to the CTAs in alternating direction (a snake), which
-  // evens out the slowly decreasing unit sizes; an index past the end terminates the loops
+  const int n_blocks = Lk / kBlk;
+  const int n_pairs = (n_blocks + 1) / 2;
+  const int n_units = n_pairs * BH;
   auto unit_of = [&](int r) {
     const int c = (r & 1) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
     return r * (int)gridDim.x + c;
   };
-  auto unit_block = [&](int w) { return w / BH; };
-  auto unit_tq0 = [&](int n) { return n > prefix_blocks ? (n - prefix_blocks) / 2 : 0; };
+  auto unit_tq0 = [&](int pair) { return 2 * pair > prefix_blocks ? (2 * pair - prefix_blocks) / 2 : 0; };
 
   if (tid == 0) {
     mbar_init(smem_u32(&sm->kv_full), 1);
@@ -865,17 +866,15 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(smem_u32(&sm->full[s]), 1);
       mbar_init(smem_u32(&sm->empty[s]), 1);
     }
-    for (int g = 0; g < kSdpBufs; ++g) {
+    for (int g = 0; g < 2; ++g) {
       mbar_init(smem_u32(&sm->sdp_full[g]), 1);
       mbar_init(smem_u32(&sm->sdp_free[g]), 128);
+      mbar_init(smem_u32(&sm->acc_full[g]), 1);
+      mbar_init(smem_u32(&sm->acc_empty[g]), 128);
     }
-    for (int g = 0; g < 2; ++g) {
-      mbar_init(smem_u32(&sm->pds_ready[g]), 128);
-      mbar_init(smem_u32(&sm->pds_free[g]), 1);
-    }
-    mbar_init(smem_u32(&sm->acc_full[0]), 1);
-    mbar_init(smem_u32(&sm->acc_full[1]), 1);
-    mbar_init(smem_u32(&sm->acc_empty), 128);
+    mbar_init(smem_u32(&sm->pds_ready), 128);
+    mbar_init(smem_u32(&sm->pds_free[0]), 1);
+    mbar_init(smem_u32(&sm->pds_free[1]), 1);
     mbar_init_fence();
   }
   if (warp == kBwdGroups * 4 + 1) tmem_alloc(smem_u32(&sm->tmem_base), 512);
@@ -883,7 +882,10 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
-  const uint32_t tmem_s = tmem, tmem_dp = tmem + 192, tmem_dv = tmem + 384, tmem_dk = tmem + 448;
+  auto tmem_s = [&](int g) { return tmem + (uint32_t)g * 64u; };
+  auto tmem_dp = [&](int g) { return tmem + 128u + (uint32_t)g * 64u; };
+  auto tmem_dv = [&](int g) { return tmem + 256u + (uint32_t)g * 128u; };
+  auto tmem_dk = [&](int g) { return tmem + 320u + (uint32_t)g * 128u; };
 
   if (warp == kBwdGroups * 4) {
     if (lane == 0) {
@@ -893,15 +895,18 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       prefetch_tensormap(&tm_do);
       int it = 0, u = 0;
       for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
-        const int n = unit_block(w), bh = w - n * BH, b = bh / H, h = bh - b * H;
-        const int tq0 = unit_tq0(n), n_items = n_tiles - tq0;
+        const int pair = w / BH, bh = w - pair * BH, b = bh / H, h = bh - b * H;
+        const int tq0 = unit_tq0(pair), n_items = n_tiles - tq0;
         const uint32_t kvb = smem_u32(&sm->kv_full);
         mbar_wait(smem_u32(&sm->kv_empty), (u & 1) ^ 1, &g_lmk_status, kErrDkvProducer);
-        mbar_arrive_expect_tx(kvb, 2 * kTileBytes);
-        tma_load_4d(k_tile, &tm_k, kvb, 0, n * kBlk, h, b);
-        tma_load_4d(k_tile + kHalfTile, &tm_k, kvb, 64, n * kBlk, h, b);
-        tma_load_4d(v_tile, &tm_v, kvb, 0, n * kBlk, h, b);
-        tma_load_4d(v_tile + kHalfTile, &tm_v, kvb, 64, n * kBlk, h, b);
+        mbar_arrive_expect_tx(kvb, 4 * kTileBytes);
+        for (int g = 0; g < 2; ++g) {       // a block past the end of the sequence reads as zeros
+          const int r0 = (2 * pair + g) * kBlk;
+          tma_load_4d(k_tile(g), &tm_k, kvb, 0, r0, h, b);
+          tma_load_4d(k_tile(g) + kHalfTile, &tm_k, kvb, 64, r0, h, b);
+          tma_load_4d(v_tile(g), &tm_v, kvb, 0, r0, h, b);
+          tma_load_4d(v_tile(g) + kHalfTile, &tm_v, kvb, 64, r0, h, b);
+        }
         for (int i = 0; i < n_items; ++i, ++it) {
           const int s = it % kDkvStages;
           mbar_wait(smem_u32(&sm->empty[s]), ((it / kDkvStages) & 1) ^ 1, &g_lmk_status, kErrDkvProducer);
@@ -917,42 +922,42 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     __syncwarp();
   } else if (warp == kBwdGroups * 4 + 1) {
-    // S = Q K^T and dP = dO V^T of item `it` into TMEM buffer it % kSdpBufs
+    // S_g = Q K_g^T and dP_g = dO V_g^T for both blocks of the pair, one query tile at a time
     if (lane == 0) {
       constexpr uint32_t fmt = kBf16 ? 1u : 0u;
       constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);
-      const uint64_t dkt = smem_desc_sw128(k_tile, 16, 1024), dvt = smem_desc_sw128(v_tile, 16, 1024);
+      const uint64_t dk0 = smem_desc_sw128(k_tile(0), 16, 1024), dv0 = smem_desc_sw128(v_tile(0), 16, 1024);
       const uint64_t dq0 = smem_desc_sw128(q_slot(0), 16, 1024), ddo0 = smem_desc_sw128(do_slot(0), 16, 1024);
       int it = 0, u = 0;
       for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
-        const int n_items = n_tiles - unit_tq0(unit_block(w));
+        const int n_items = n_tiles - unit_tq0(w / BH);
         mbar_wait(smem_u32(&sm->kv_full), u & 1, &g_lmk_status, kErrDkvMma);
         for (int i = 0; i < n_items; ++i, ++it) {
-          const int s = it % kDkvStages, sb = it % kSdpBufs;
-          LMK_STAMP(11, it);
+          const int s = it % kDkvStages;
           mbar_wait(smem_u32(&sm->full[s]), (it / kDkvStages) & 1, &g_lmk_status, kErrDkvMma);
-          LMK_STAMP(12, it);
-          if (it >= kSdpBufs)
-            mbar_wait(smem_u32(&sm->sdp_free[sb]), ((it / kSdpBufs) & 1) ^ 1, &g_lmk_status, kErrDkvMma);
-          tc_fence_after();
           const uint64_t dq = desc_advance(dq0, (uint32_t)s * 65536u), ddo = desc_advance(ddo0, (uint32_t)s * 65536u);
 #pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk)
-            mma_f16_ss(tmem_s + sb * 64, desc_advance(dq, kmajor_step(kk, kTileBytes)),
-                       desc_advance(dkt, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
+          for (int g = 0; g < 2; ++g) {
+            if (it >= 1) mbar_wait(smem_u32(&sm->sdp_free[g]), (it & 1) ^ 1, &g_lmk_status, kErrDkvMma);
+            tc_fence_after();
+            const uint64_t dkt = desc_advance(dk0, (uint32_t)g * 32768u), dvt = desc_advance(dv0, (uint32_t)g * 32768u);
 #pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk)
-            mma_f16_ss(tmem_dp + sb * 64, desc_advance(ddo, kmajor_step(kk, kTileBytes)),
-                       desc_advance(dvt, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
-          mma_commit(smem_u32(&sm->sdp_full[sb]));
-          LMK_STAMP(13, it);
+            for (int kk = 0; kk < kD / 16; ++kk)
+              mma_f16_ss(tmem_s(g), desc_advance(dq, kmajor_step(kk, kTileBytes)),
+                         desc_advance(dkt, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
+#pragma unroll
+            for (int kk = 0; kk < kD / 16; ++kk)
+              mma_f16_ss(tmem_dp(g), desc_advance(ddo, kmajor_step(kk, kTileBytes)),
+                         desc_advance(dvt, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
+            mma_commit(smem_u32(&sm->sdp_full[g]));
+          }
         }
         mma_commit(smem_u32(&sm->kv_empty));      // K / V tiles may be replaced once these products are done
       }
     }
     __syncwarp();
   } else if (warp == kBwdGroups * 4 + 2) {
-    // dV^T += dO^T P and dK^T += Q^T dS.  A = dO^T / Q^T: MN-major view of the row-major [128 q x 128 d] tile (second
+    // dV_g^T += dO^T P and dK_g^T += Q^T dS.  A = dO^T / Q^T: MN-major view of the row-major [128 q x 128 d] tile (second
     // 64-feature half 16 KB further); B = P / dS: MN-major view of the [128 q x 64 k] tile; a K-step is 16 query rows
     // = 2048 bytes.
     if (lane == 0) {
@@ -960,82 +965,80 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       constexpr uint32_t idesc_t = instr_desc_f16(fmt, 128, 64, 1, 1);
       const uint64_t dq0t = smem_desc_sw128(q_slot(0), kTileBytes, 1024);
       const uint64_t ddo0t = smem_desc_sw128(do_slot(0), kTileBytes, 1024);
-      const uint64_t dp0 = smem_desc_sw128(p_tile(0), 16, 1024), dds0 = smem_desc_sw128(ds_tile(0), 16, 1024);
+      const uint64_t dpt = smem_desc_sw128(p_tile, 16, 1024), ddst = smem_desc_sw128(ds_tile, 16, 1024);
       int it = 0, u = 0;
       for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
-        const int n_items = n_tiles - unit_tq0(unit_block(w));
+        const int n_items = n_tiles - unit_tq0(w / BH);
         for (int i = 0; i < n_items; ++i, ++it) {
-          const int s = it % kDkvStages, g = it & 1;
-          LMK_STAMP(8, it);
-          mbar_wait(smem_u32(&sm->pds_ready[g]), (it >> 1) & 1, &g_lmk_status, kErrDkvMma);
-          LMK_STAMP(9, it);
-          if (i == 0) mbar_wait(smem_u32(&sm->acc_empty), (u & 1) ^ 1, &g_lmk_status, kErrDkvMma);
-          tc_fence_after();
+          const int s = it % kDkvStages;
           const uint64_t ddot = desc_advance(ddo0t, (uint32_t)s * 65536u), dqt = desc_advance(dq0t, (uint32_t)s * 65536u);
-          const uint64_t dpt = desc_advance(dp0, (uint32_t)g * 32768u), ddst = desc_advance(dds0, (uint32_t)g * 32768u);
 #pragma unroll
-          for (int kk = 0; kk < kQTile / 16; ++kk)
-            mma_f16_ss(tmem_dv, desc_advance(ddot, kk * 2048), desc_advance(dpt, kk * 2048), idesc_t,
-                       (i > 0 || kk > 0) ? 1u : 0u);
+          for (int g = 0; g < 2; ++g) {
+            // item j = 2 * it + g of the single P/dS tile pair
+            mbar_wait(smem_u32(&sm->pds_ready), g, &g_lmk_status, kErrDkvMma);
+            if (i == 0) mbar_wait(smem_u32(&sm->acc_empty[g]), (u & 1) ^ 1, &g_lmk_status, kErrDkvMma);
+            tc_fence_after();
 #pragma unroll
-          for (int kk = 0; kk < kQTile / 16; ++kk)
-            mma_f16_ss(tmem_dk, desc_advance(dqt, kk * 2048), desc_advance(ddst, kk * 2048), idesc_t,
-                       (i > 0 || kk > 0) ? 1u : 0u);
-          mma_commit(smem_u32(&sm->pds_free[g]));
+            for (int kk = 0; kk < kQTile / 16; ++kk)
+              mma_f16_ss(tmem_dv(g), desc_advance(ddot, kk * 2048), desc_advance(dpt, kk * 2048), idesc_t,
+                         (i > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+            for (int kk = 0; kk < kQTile / 16; ++kk)
+              mma_f16_ss(tmem_dk(g), desc_advance(dqt, kk * 2048), desc_advance(ddst, kk * 2048), idesc_t,
+                         (i > 0 || kk > 0) ? 1u : 0u);
+            mma_commit(smem_u32(&sm->pds_free[g]));
+          }
           mma_commit(smem_u32(&sm->empty[s]));
-          LMK_STAMP(10, it);
         }
-        mma_commit(smem_u32(&sm->acc_full[u & 1]));
+        mma_commit(smem_u32(&sm->acc_full[0]));
+        mma_commit(smem_u32(&sm->acc_full[1]));
       }
     }
     __syncwarp();
   } else {
-    const int g = warp >> 2;                       // warpgroup: handles items with (running item count) % 2 == g
+    const int g = warp >> 2;                       // warpgroup g owns block g of every pair
     const int row = tid & 127;
     const int half = row >> 6;
     const int vis = min(row & 63, kBlk - 2);
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    int it0 = 0, u = 0;
+    int it = 0, u = 0;
     for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
-      const int n = unit_block(w), bh = w - n * BH;
-      const int tq0 = unit_tq0(n), n_items = n_tiles - tq0;
-      for (int i = (it0 + g) & 1; i < n_items; i += kBwdGroups) {
-        const int it = it0 + i;
+      const int pair = w / BH, bh = w - pair * BH;
+      const int n = 2 * pair + g;
+      const int tq0 = unit_tq0(pair), n_items = n_tiles - tq0;
+      for (int i = 0; i < n_items; ++i, ++it) {
         const int tq = tq0 + i;
         const int own = prefix_blocks + 2 * tq + half;
         const int64_t grow = (int64_t)bh * Lq + tq * kQTile + row;
         const float M2 = M_ptr[grow] * kLog2e, Linv = 1.f / L_ptr[grow], delta = delta_ptr[grow];
-        const int sb = it % kSdpBufs, pb = it & 1;
-        if (row == 0) LMK_STAMP(g * 4 + 0, it);
-        mbar_wait(smem_u32(&sm->sdp_full[sb]), (it / kSdpBufs) & 1, &g_lmk_status, kErrDkvSoftmax);
-        if (row == 0) LMK_STAMP(g * 4 + 1, it);
+        mbar_wait(smem_u32(&sm->sdp_full[g]), it & 1, &g_lmk_status, kErrDkvSoftmax);
         tc_fence_after();
         const int kind = n > own ? 0 : (n == own ? 1 : 2);
-        bwd_item<kBf16, true>(tmem_s + sb * 64 + lane_base, tmem_dp + sb * 64 + lane_base,
-                              smem_u32(&sm->sdp_free[sb]), kind, vis, scale_log2, scale, M2, Linv, delta, p_tile(pb),
-                              ds_tile(pb), row, [&]() {
-                                if (it >= 2)
-                                  mbar_wait(smem_u32(&sm->pds_free[pb]), ((it >> 1) - 1) & 1, &g_lmk_status,
+        bwd_item<kBf16, true>(tmem_s(g) + lane_base, tmem_dp(g) + lane_base, smem_u32(&sm->sdp_free[g]), kind, vis,
+                              scale_log2, scale, M2, Linv, delta, p_tile, ds_tile, row, [&]() {
+                                // The single P/dS tile pair is written in the order a, b, a, b, ...: before writing,
+                                // the accumulating MMAs of the OTHER warpgroup's latest item must have read it.  Each
+                                // warpgroup is the only waiter on the other one's barrier and sees every phase of it.
+                                const int prev = 2 * it + g - 1;          // item written just before this one
+                                if (prev >= 0)
+                                  mbar_wait(smem_u32(&sm->pds_free[1 - g]), (prev >> 1) & 1, &g_lmk_status,
                                             kErrDkvSoftmax);
                               });
-        if (row == 0) LMK_STAMP(g * 4 + 2, it);
         fence_proxy_async_smem();
-        mbar_arrive(smem_u32(&sm->pds_ready[pb]));
-        if (row == 0) LMK_STAMP(g * 4 + 3, it);
+        mbar_arrive(smem_u32(&sm->pds_ready));
       }
-      it0 += n_items;
-      // epilogue, alternating between the warpgroups: thread = feature d, TMEM column = key j -> dV[key][d], dK[key][d]
-      if (g == (u & 1)) {
-        mbar_wait(smem_u32(&sm->acc_full[g]), (u >> 1) & 1, &g_lmk_status, kErrDkvEpilogue);
-        tc_fence_after();
-        uint32_t rv[2][32], rk[2][32];
-        tmem_ld_32x32b_x32(tmem_dv + lane_base, rv[0]);
-        tmem_ld_32x32b_x32(tmem_dv + 32 + lane_base, rv[1]);
-        tmem_ld_32x32b_x32(tmem_dk + lane_base, rk[0]);
-        tmem_ld_32x32b_x32(tmem_dk + 32 + lane_base, rk[1]);
-        tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive(smem_u32(&sm->acc_empty));     // the next unit may start accumulating
+      // epilogue: each warpgroup drains its own block; thread = feature d, TMEM column = key j -> dV[key][d], dK[key][d]
+      mbar_wait(smem_u32(&sm->acc_full[g]), u & 1, &g_lmk_status, kErrDkvEpilogue);
+      tc_fence_after();
+      uint32_t rv[2][32], rk[2][32];
+      tmem_ld_32x32b_x32(tmem_dv(g) + lane_base, rv[0]);
+      tmem_ld_32x32b_x32(tmem_dv(g) + 32 + lane_base, rv[1]);
+      tmem_ld_32x32b_x32(tmem_dk(g) + lane_base, rk[0]);
+      tmem_ld_32x32b_x32(tmem_dk(g) + 32 + lane_base, rk[1]);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sm->acc_empty[g]));     // the next unit may start accumulating into this block's columns
+      if (n < n_blocks) {
         uint16_t* dvp = reinterpret_cast<uint16_t*>(dv_ptr) + ((int64_t)bh * Lk + (int64_t)n * kBlk) * kD + row;
         uint16_t* dkp = reinterpret_cast<uint16_t*>(dk_ptr) + ((int64_t)bh * Lk + (int64_t)n * kBlk) * kD + row;
 #pragma unroll
@@ -1362,7 +1365,7 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
   float* delta = reinterpret_cast<float*>(p.workspace);
   const int64_t rows = (int64_t)p.B * p.H * p.Lq;
   const float scale_log2 = p.scale * kLog2e;
-  const size_t smem_dkv = 1024 + 32768 + kDkvStages * 65536 + 65536 + sizeof(DkvSmem);
+  const size_t smem_dkv = 1024 + 65536 + kDkvStages * 65536 + 32768 + sizeof(DkvSmem);
   const size_t smem_dq = 1024 + 65536 + kDqStages * 32768 + sizeof(DqSmem);
   int dev = 0, n_sm = 148;
   LMK_CUDA(cudaGetDevice(&dev));
@@ -1371,7 +1374,7 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
     const int v = atoi(cap);
     if (v >= 1 && v < n_sm) n_sm = v;
   }
-  const int dkv_units = (p.Lk / kBlk) * p.B * p.H;
+  const int dkv_units = ((p.Lk / kBlk + 1) / 2) * p.B * p.H;
   dim3 grid_dkv(dkv_units < n_sm ? dkv_units : n_sm), grid_dq(p.B * p.H, p.Lq / kQTile);
 #define LMK_BWD_LAUNCH(BF)                                                                                          \
   do {                                                                                                              \
