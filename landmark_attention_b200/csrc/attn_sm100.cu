@@ -36,13 +36,6 @@ namespace lmk {
 
 __device__ int g_lmk_status = 0;   // first bounded wait that expired (0 = none); see lmk_device_status()
 
-#ifdef LMK_TRACE
-__device__ long long* g_trace = nullptr;   // development aid: per-item clock64 stamps of CTA (0,0)
-#define LMK_STAMP(slot, item) \
-  do { if (g_trace && blockIdx.x == 0 && blockIdx.y == 0 && (item) < 64) g_trace[(slot) * 64 + (item)] = clock64(); } while (0)
-#else
-#define LMK_STAMP(slot, item) do { } while (0)
-#endif
 
 namespace {
 
@@ -556,9 +549,7 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int i = 0; i < total; ++i) {
       if (!active(w, i)) continue;
       const int sb = k & 1;
-      if (row == 0) LMK_STAMP(w * 5 + 0, k);
       mbar_wait(smem_u32(&sm->s_full[w][sb]), (k / 2) & 1, &g_lmk_status, kErrFwd2Softmax);
-      if (row == 0) LMK_STAMP(w * 5 + 1, k);
       tc_fence_after();
       float sv[64];
       {
@@ -592,12 +583,6 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 32; ++j) wgt[j] = pack2<kBf16>(sv[2 * j], sv[2 * j + 1]);
         } else {
-#ifdef LMK_EXP_NOCOMPUTE
-#pragma unroll
-          for (int j = 0; j < 32; ++j) wgt[j] = __float_as_uint(sv[2 * j] + sv[2 * j + 1]);
-          l += 1.f;
-          if (false) {
-#endif
           const float nmx = -row_max<63>(sv) * scale_log2;
           const float el = ex2(fmaf(sv[63], scale_log2, -m2));
 #pragma unroll
@@ -608,20 +593,14 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           sv[63] = 0.f;
 #pragma unroll
           for (int j = 0; j < 32; ++j) wgt[j] = pack2<kBf16>(sv[2 * j] * wg, sv[2 * j + 1] * wg);
-#ifdef LMK_EXP_NOCOMPUTE
-          }
-#endif
         }
       }
-      if (row == 0) LMK_STAMP(w * 5 + 2, k);
       if (k > 0) mbar_wait(smem_u32(&sm->p_free[w]), (k - 1) & 1, &g_lmk_status, kErrFwd2Softmax);
-      if (row == 0) LMK_STAMP(w * 5 + 3, k);
       if (write_p) {
         store_row_sw128(p_tile(w), row, wgt);
         fence_proxy_async_smem();
       }
       mbar_arrive(smem_u32(&sm->p_ready[w]));
-      if (row == 0) LMK_STAMP(w * 5 + 4, k);
       ++k;
     }
     // ------------------------------------------------------------------ epilogue
@@ -1398,12 +1377,6 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
 }
 
 size_t attn_sm100_bwd_workspace(int B, int H, int Lq, int, int) { return sizeof(float) * (size_t)B * H * Lq; }
-
-#ifdef LMK_TRACE
-extern "C" int lmk_trace_set(long long* buf) {
-  return cudaMemcpyToSymbol(g_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : -3;
-}
-#endif
 
 // Device address of the status word on the current device, for kernels compiled in other translation units.
 int* device_status_word() {

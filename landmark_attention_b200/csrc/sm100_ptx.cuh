@@ -159,13 +159,9 @@ __host__ __device__ constexpr uint32_t instr_desc_f16(uint32_t fmt, uint32_t m, 
 }
 
 __device__ __forceinline__ float ex2(float x) {
-#ifdef LMK_EXP_NOEX2
-  return x * 0.001f;
-#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-#endif
 }
 
 }  // namespace ptx
