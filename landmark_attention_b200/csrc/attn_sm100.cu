@@ -683,10 +683,14 @@ __device__ __forceinline__ void store_half_row_sw128(uint32_t tile_base, int row
   }
 }
 
-template <bool kBf16, bool kNeedP, typename WaitFn>
+struct NoHook {
+  __device__ __forceinline__ void operator()() const {}
+};
+
+template <bool kBf16, bool kNeedP, typename WaitFn, typename AfterSFn = NoHook>
 __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t free_bar, int kind, int vis, float c,
                                          float scale, float M2, float Linv, float delta, uint32_t p_dst,
-                                         uint32_t ds_dst, int row, WaitFn wait_dst) {
+                                         uint32_t ds_dst, int row, WaitFn wait_dst, AfterSFn after_s = AfterSFn()) {
   float sv[64];
   {
     uint32_t ra[32], rb[32];
@@ -699,6 +703,7 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
       sv[32 + j] = __uint_as_float(rb[j]);
     }
   }
+  after_s();      // S is in registers: a caller with separate S / dP buffers releases S and waits for dP here
   float sub = delta, lm_ds = 0.f;
   if (kind == 0) {
 #pragma unroll
@@ -736,36 +741,71 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
     sub = nd;
     lm_ds = g * (nd - delta) * scale;
   }
-  wait_dst();
   if (kNeedP) {
-    uint32_t wp[32];
+    // dK/dV kernel: P is packed first and dS is formed from the packed (bf16) P, so that both result rows sit in
+    // registers before the shared tiles are claimed; the wait for the tiles then only covers the 16 stores.
+    uint32_t wp[32], wd[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) wp[j] = pack2<kBf16>(sv[2 * j], sv[2 * j + 1]);
-    store_row_sw128(p_dst, row, wp);
-  }
 #pragma unroll
-  for (int hf = 0; hf < 2; ++hf) {
-    uint32_t wd[16];
-    if (kind == 0) {
+    for (int hf = 0; hf < 2; ++hf) {
+      if (kind == 0) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) wd[j] = 0u;
-    } else {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(tdp + hf * 32, r);
-      tmem_ld_wait();
-      if (hf == 1) {
-        tc_fence_before();
-        mbar_arrive(free_bar);
-      }
+        for (int j = 0; j < 16; ++j) wd[hf * 16 + j] = 0u;
+      } else {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tdp + hf * 32, r);
+        tmem_ld_wait();
+        if (hf == 1) {
+          tc_fence_before();
+          mbar_arrive(free_bar);
+        }
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        float d0 = sv[hf * 32 + 2 * j] * (__uint_as_float(r[2 * j]) - sub) * scale;
-        float d1 = sv[hf * 32 + 2 * j + 1] * (__uint_as_float(r[2 * j + 1]) - sub) * scale;
-        if (hf == 1 && j == 15 && kind == 2) d1 = lm_ds;
-        wd[j] = pack2<kBf16>(d0, d1);
+        for (int j = 0; j < 16; ++j) {
+          float p0, p1;
+          if (kBf16) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wp[hf * 16 + j]));
+            p0 = f.x; p1 = f.y;
+          } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wp[hf * 16 + j]));
+            p0 = f.x; p1 = f.y;
+          }
+          float d0 = p0 * (__uint_as_float(r[2 * j]) - sub) * scale;
+          float d1 = p1 * (__uint_as_float(r[2 * j + 1]) - sub) * scale;
+          if (hf == 1 && j == 15 && kind == 2) d1 = lm_ds;
+          wd[hf * 16 + j] = pack2<kBf16>(d0, d1);
+        }
       }
     }
-    store_half_row_sw128(ds_dst, row, hf, wd);
+    wait_dst();
+    store_row_sw128(p_dst, row, wp);
+    store_row_sw128(ds_dst, row, wd);
+  } else {
+    wait_dst();
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      uint32_t wd[16];
+      if (kind == 0) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) wd[j] = 0u;
+      } else {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tdp + hf * 32, r);
+        tmem_ld_wait();
+        if (hf == 1) {
+          tc_fence_before();
+          mbar_arrive(free_bar);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float d0 = sv[hf * 32 + 2 * j] * (__uint_as_float(r[2 * j]) - sub) * scale;
+          float d1 = sv[hf * 32 + 2 * j + 1] * (__uint_as_float(r[2 * j + 1]) - sub) * scale;
+          if (hf == 1 && j == 15 && kind == 2) d1 = lm_ds;
+          wd[j] = pack2<kBf16>(d0, d1);
+        }
+      }
+      store_half_row_sw128(ds_dst, row, hf, wd);
+    }
   }
   if (kind == 0) {
     tc_fence_before();
@@ -784,7 +824,7 @@ enum { kErrDkvProducer = 201, kErrDkvMma = 202, kErrDkvSoftmax = 203, kErrDkvEpi
 // a time, so 9 to 12 warps all leave 168 registers per thread.)
 constexpr int kBwdGroups = 2;                       // softmax warpgroups (items are dealt round-robin)
 constexpr int kBwdThreads = (kBwdGroups * 4 + 3) * 32;
-constexpr int kSdpBufs = 3;                         // S / dP buffers in TMEM: 3 x (64 + 64) columns
+constexpr int kSdpBufs = 3;                         // S / dP buffers in TMEM of the dQ kernel: 3 x (64 + 64) columns
 constexpr int kDkvStages = 2;
 
 struct DkvSmem {

@@ -111,3 +111,22 @@ def test_persistent_kernels_with_several_units_per_cta(monkeypatch):
         for a, b in zip(got, ref):
             assert torch.equal(a, b)
         assert L.device_status() == 0
+
+
+def test_auto_path_selection():
+    lib = L.lib()
+    assert lib.lmk_attn_tcgen05_supported(1, 32, 2048, 2048, 128, 64, L.LMK_BF16) == 1
+    assert lib.lmk_attn_tcgen05_supported(1, 32, 2048, 2048, 64, 64, L.LMK_BF16) == 0      # head dim
+    assert lib.lmk_attn_tcgen05_supported(1, 32, 2048, 2048, 128, 32, L.LMK_BF16) == 0     # block size
+    assert lib.lmk_attn_tcgen05_supported(1, 32, 2048, 2048, 128, 64, L.LMK_F32) == 0      # fp32 needs the CUDA-core path
+    assert lib.lmk_attn_tcgen05_supported(1, 32, 192, 192, 128, 64, L.LMK_BF16) == 0       # not whole 128-row tiles
+    # a non-positive softmax scale is legal for the operator but not for the tcgen05 kernels: AUTO falls back
+    q, k, v, do = make(1, 2, 256, 256, torch.bfloat16, 14)
+    qc, kc, vc = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    out = P.fused_landmark_attention(qc, kc, vc, None, sm_scale=-0.05)
+    grads = torch.autograd.grad(out, [qc, kc, vc], do.to(DEV))
+    exp = O.landmark_attention_grads(q.float(), k.float(), v.float(), do.float(), 64, sm_scale=-0.05)
+    for got, e in zip((out, *grads), exp):
+        assert (got.detach().float().cpu() - e).abs().max().item() < 2e-2
+    with pytest.raises(NotImplementedError):
+        P.fused_landmark_attention(qc, kc, vc, None, sm_scale=-0.05, path=P.PATH_TCGEN05)
