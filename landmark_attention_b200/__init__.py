@@ -6,6 +6,7 @@ eager fallback: calls fail loudly when the library is missing or a tensor is not
 from ._lib import PATH_AUTO, PATH_GENERAL, PATH_TCGEN05, ROTARY_HALF, ROTARY_INTERLEAVED, ROTARY_NONE, lib  # noqa: F401
 from .fused import (FusedLandmarkAttention, attn_forward_with_stats, fused_landmark_attention,  # noqa: F401
                     landmark_sdpa)
+from .host_pipeline import HostAttentionPipeline  # noqa: F401
 from .grouped_softmax import (landmark_grouped_softmax, landmark_grouped_softmax_lm,  # noqa: F401
                               lm_landmark_attention, prepare_landmark_masks)
 from .mem_cache import MemLMCache, MemLMCacheStorage  # noqa: F401

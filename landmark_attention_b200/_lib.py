@@ -61,6 +61,7 @@ PROTOTYPES = {
 }
 
 _lib = None
+c_void_p = c_void_p          # re-exported for callers that pass raw stream handles
 
 
 def lib():
