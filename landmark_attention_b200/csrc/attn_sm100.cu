@@ -16,14 +16,16 @@
 //   3. Epilogue: O / l -> global, plus the statistics L = l, M = m the backward pass needs.
 // Reference semantics: llama/ltriton/flash_landmark_attention.py:6-122.
 //
-// Backward is recompute-based and atomic-free (bit-reproducible), in three launches:
-//   a. delta = rowsum(O * dO)                                              (:125-149, without the 1/L pre-scaling)
-//   b. dK/dV: one CTA per (key block of 64, batch*head) loops over the query tiles that see the block.  Per tile:
-//      S = Q K^T and dP = dO V^T into TMEM; the softmax threads rebuild P and dS (bf16, [128 q x 64 k] swizzled tiles);
-//      dV^T += dO^T P and dK^T += Q^T dS accumulate TRANSPOSED ([128 features x 64 keys], M = 128) so that every MMA
-//      keeps the full 128-lane shape; dO, Q, P and dS are consumed as MN-major operands from their row-major tiles.
-//   c. dQ: one CTA per (128 query rows, batch*head) loops over the key blocks like the forward pass:
-//      S, dP -> dS (written over the V tile, which dP no longer needs) -> dQ += dS K with K as an MN-major operand.
+// Backward is recompute-based and atomic-free (bit-reproducible), in two launches:
+//   a. dQ (sm100_bwd_dq_kernel): one CTA per (128 query rows, batch*head).  Its prologue computes
+//      delta = rowsum(O * dO) from the O and dO tiles (:125-149, without the 1/L pre-scaling) and stores it for (b).
+//      Then, per key block: S = Q K^T, dP = dO V^T -> dS (written over the V tile, which dP no longer needs) ->
+//      dQ += dS K with K as an MN-major operand.  Two softmax warpgroups take alternate blocks.
+//   b. dK/dV (sm100_bwd_dkv_kernel): persistent; a unit is a pair of adjacent key blocks of one head, held in shared
+//      memory while the query tiles that see them stream through.  Per tile and block: S, dP into TMEM; the softmax
+//      threads rebuild P and dS (bf16, [128 q x 64 k] swizzled tiles); dV^T += dO^T P and dK^T += Q^T dS accumulate
+//      TRANSPOSED ([128 features x 64 keys], M = 128) so that every MMA keeps the full 128-lane shape; dO, Q, P and dS
+//      are consumed as MN-major operands from their row-major tiles.
 //   Per tile pair: earlier block  dS_j = g s_j (dP_j - nD) scale,  dS_landmark = g (nD - delta) scale,  P_j = g s_j,
 //   with s = softmax inside the block, g = exp(l_n - M) / L, nD = sum_j s_j dP_j;  own block: p = exp(S - M) / L,
 //   dS = p (dP - delta) scale.                                                                      (:152-305)
@@ -635,36 +637,7 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
 }
 
-// ---------------------------------------------------------------------------------------------- backward: delta
-template <bool kBf16>
-__global__ void __launch_bounds__(256) sm100_delta_kernel(const uint4* __restrict__ o, const uint4* __restrict__ dO,
-                                                          float* __restrict__ delta, int64_t rows) {
-  // 16 lanes per row (8 elements = 16 bytes per lane), two rows per warp, 16 rows per CTA
-  const int lane = threadIdx.x & 31, sub = lane & 15;
-  const int64_t row = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 5) * 2 + (lane >> 4);
-  float acc = 0.f;
-  if (row < rows) {
-    const uint4 a = o[row * 16 + sub], b = dO[row * 16 + sub];
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 fa, fb;
-      if (kBf16) {
-        fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
-        fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
-      } else {
-        fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
-        fb = __half22float2(*reinterpret_cast<const __half2*>(&bw[i]));
-      }
-      acc = fmaf(fa.x, fb.x, acc);
-      acc = fmaf(fa.y, fb.y, acc);
-    }
-  }
-#pragma unroll
-  for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (row < rows && sub == 0) delta[row] = acc;
-}
-
+// ---------------------------------------------------------------------------------------------- backward
 // One (query row, key block) pair of the backward pass, staged to keep the softmax threads below 168 registers
 // (so that two softmax warpgroups fit): S is read once, dP twice (once to reduce nD = sum_j s_j dP_j, once to form dS),
 // and each result row is stored as soon as it is complete.
@@ -1096,16 +1069,17 @@ template <bool kBf16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                    const float* __restrict__ L_ptr, const float* __restrict__ M_ptr,
-                    const float* __restrict__ delta_ptr, void* __restrict__ dq_ptr, int H, int Lq, int Lk,
-                    float scale, float scale_log2) {
+                    const __grid_constant__ CUtensorMap tm_o, const float* __restrict__ L_ptr,
+                    const float* __restrict__ M_ptr, float* __restrict__ delta_ptr, void* __restrict__ dq_ptr, int H,
+                    int Lq, int Lk, float scale, float scale_log2) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   const uint32_t q_tile = base, do_tile = base + 32768u;
   auto k_slot = [&](int s) { return base + 65536u + (uint32_t)s * 32768u; };
   auto v_slot = [&](int s) { return base + 65536u + (uint32_t)s * 32768u + 16384u; };   // V block, later dS
-  DqSmem* sm = reinterpret_cast<DqSmem*>(smem_raw + (base - raw) + 65536u + kDqStages * 32768u);
+  const uint32_t o_tile = base + 65536u + kDqStages * 32768u;      // forward output tile, only for delta
+  DqSmem* sm = reinterpret_cast<DqSmem*>(smem_raw + (base - raw) + 65536u + kDqStages * 32768u + 32768u);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = Lq / kQTile;
@@ -1143,8 +1117,11 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_v);
       prefetch_tensormap(&tm_do);
+      prefetch_tensormap(&tm_o);
       const uint32_t qb = smem_u32(&sm->qdo_full);
-      mbar_arrive_expect_tx(qb, 4 * kTileBytes);
+      mbar_arrive_expect_tx(qb, 6 * kTileBytes);
+      tma_load_4d(o_tile, &tm_o, qb, 0, t * kQTile, h, b);
+      tma_load_4d(o_tile + kTileBytes, &tm_o, qb, 64, t * kQTile, h, b);
       tma_load_4d(q_tile, &tm_q, qb, 0, t * kQTile, h, b);
       tma_load_4d(q_tile + kTileBytes, &tm_q, qb, 64, t * kQTile, h, b);
       tma_load_4d(do_tile, &tm_do, qb, 0, t * kQTile, h, b);
@@ -1216,7 +1193,36 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int vis = min(row & 63, kBlk - 2);
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const int64_t grow = (int64_t)bh * Lq + t * kQTile + row;
-    const float M2 = M_ptr[grow] * kLog2e, Linv = 1.f / L_ptr[grow], delta = delta_ptr[grow];
+    const float M2 = M_ptr[grow] * kLog2e, Linv = 1.f / L_ptr[grow];
+    // delta = rowsum(O * dO), straight from the swizzled tiles (one row per thread, 16-byte chunks); warpgroup 0 also
+    // publishes it for the dK/dV kernel, which runs after this one
+    mbar_wait(smem_u32(&sm->qdo_full), 0, &g_lmk_status, kErrDqSoftmax);
+    float delta = 0.f;
+#pragma unroll
+    for (int sub = 0; sub < 2; ++sub)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint32_t off = (uint32_t)sub * kTileBytes + (uint32_t)row * 128u + (uint32_t)((c ^ (row & 7)) << 4);
+        uint32_t ov[4], gv[4];
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(ov[0]), "=r"(ov[1]), "=r"(ov[2]), "=r"(ov[3])
+                     : "r"(o_tile + off));
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(gv[0]), "=r"(gv[1]), "=r"(gv[2]), "=r"(gv[3])
+                     : "r"(do_tile + off));
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float2 fo, fg;
+          if (kBf16) {
+            fo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ov[e]));
+            fg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv[e]));
+          } else {
+            fo = __half22float2(*reinterpret_cast<const __half2*>(&ov[e]));
+            fg = __half22float2(*reinterpret_cast<const __half2*>(&gv[e]));
+          }
+          delta = fmaf(fo.x, fg.x, delta);
+          delta = fmaf(fo.y, fg.y, delta);
+        }
+      }
+    if (g == 0) delta_ptr[grow] = delta;
     for (int i = g; i < total; i += kBwdGroups) {
       const int s = i % kDqStages;
       const int n = n_last - i;
@@ -1369,7 +1375,8 @@ int attn_sm100_fwd(const AttnParams& p, int dtype, cudaStream_t st) {
 }
 
 int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
-  if (!tma_ok(p.q, p.qs) || !tma_ok(p.k, p.ks) || !tma_ok(p.v, p.vs) || (uintptr_t)p.dO % 16 != 0)
+  if (!tma_ok(p.q, p.qs) || !tma_ok(p.k, p.ks) || !tma_ok(p.v, p.vs) || (uintptr_t)p.dO % 16 != 0 ||
+      (uintptr_t)p.o % 16 != 0)
     return fail(LMK_ERR_UNSUPPORTED, "tcgen05 path needs 16-byte aligned tensors with strides that are multiples of 8");
   if (p.Lk % kBlk != 0 || p.Lq % kQTile != 0)
     return fail(LMK_ERR_INVALID, "Backward supported only for full blocks");
@@ -1382,10 +1389,11 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
   if ((rc = make_map_4d(&tv, p.v, dtype, p.B, p.H, p.Lk, p.vs, kBlk)) != LMK_OK) return rc;
   if ((rc = make_map_4d(&tdo, p.dO, dtype, p.B, p.H, p.Lq, dense, kQTile)) != LMK_OK) return rc;
   float* delta = reinterpret_cast<float*>(p.workspace);
-  const int64_t rows = (int64_t)p.B * p.H * p.Lq;
   const float scale_log2 = p.scale * kLog2e;
   const size_t smem_dkv = 1024 + 65536 + kDkvStages * 65536 + 32768 + sizeof(DkvSmem);
-  const size_t smem_dq = 1024 + 65536 + kDqStages * 32768 + sizeof(DqSmem);
+  const size_t smem_dq = 1024 + 65536 + kDqStages * 32768 + 32768 + sizeof(DqSmem);
+  CUtensorMap to;
+  if ((rc = make_map_4d(&to, p.o, dtype, p.B, p.H, p.Lq, dense, kQTile)) != LMK_OK) return rc;
   int dev = 0, n_sm = 148;
   LMK_CUDA(cudaGetDevice(&dev));
   LMK_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
@@ -1397,17 +1405,16 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
   dim3 grid_dkv(dkv_units < n_sm ? dkv_units : n_sm), grid_dq(p.B * p.H, p.Lq / kQTile);
 #define LMK_BWD_LAUNCH(BF)                                                                                          \
   do {                                                                                                              \
-    sm100_delta_kernel<BF><<<(unsigned)((rows + 15) / 16), 256, 0, st>>>(                                           \
-        reinterpret_cast<const uint4*>(p.o), reinterpret_cast<const uint4*>(p.dO), delta, rows);                    \
+    /* the dQ kernel also produces delta = rowsum(O * dO), which the dK/dV kernel launched after it reads */         \
+    LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dq_kernel<BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+                                  (int)smem_dq));                                                                   \
+    sm100_bwd_dq_kernel<BF><<<grid_dq, kBwdThreads, smem_dq, st>>>(tq, tk, tv, tdo, to, p.L, p.M, delta, p.dq, p.H, \
+                                                                   p.Lq, p.Lk, p.scale, scale_log2);                \
     LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dkv_kernel<BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
                                   (int)smem_dkv));                                                                  \
     sm100_bwd_dkv_kernel<BF><<<grid_dkv, kBwdThreads, smem_dkv, st>>>(tq, tk, tv, tdo, p.L, p.M, delta, p.dk, p.dv, \
                                                                      p.H, p.B * p.H, p.Lq, p.Lk, p.scale,           \
                                                                      scale_log2);                                   \
-    LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dq_kernel<BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
-                                  (int)smem_dq));                                                                   \
-    sm100_bwd_dq_kernel<BF><<<grid_dq, kBwdThreads, smem_dq, st>>>(tq, tk, tv, tdo, p.L, p.M, delta, p.dq, p.H,     \
-                                                                   p.Lq, p.Lk, p.scale, scale_log2);                \
   } while (0)
   if (dtype == LMK_BF16) LMK_BWD_LAUNCH(true);
   else LMK_BWD_LAUNCH(false);
