@@ -1056,22 +1056,29 @@ constexpr int kDqStages = 4;
 
 struct DqSmem {
   uint64_t qdo_full;
+  uint64_t qdo_empty;       // the S / dP products of the unit have read the Q and dO tiles
+  uint64_t delta_read;      // both softmax warpgroups have read the O and dO tiles for delta
   uint64_t full[kDqStages];
   uint64_t empty[kDqStages];
   uint64_t ds_ready[kDqStages];
   uint64_t sdp_full[kSdpBufs];
   uint64_t sdp_free[kSdpBufs];
-  uint64_t acc_full;
+  uint64_t acc_full[2];     // per draining warpgroup (units alternate between them)
+  uint64_t acc_empty;
   uint32_t tmem_base;
 };
 
+// Persistent: one CTA per SM walks through the units (128 query rows, batch*head), heaviest tiles first, dealt to the
+// CTAs in a snake.  The K/V stream, the S/dP products and the softmax of the next unit start while dQ of the current
+// unit is drained by one warpgroup (the two warpgroups alternate); only the unit's first accumulating MMA waits for
+// the drain.  All barrier phases derive from counters that run across units.
 template <bool kBf16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                     const __grid_constant__ CUtensorMap tm_o, const float* __restrict__ L_ptr,
                     const float* __restrict__ M_ptr, float* __restrict__ delta_ptr, void* __restrict__ dq_ptr, int H,
-                    int Lq, int Lk, float scale, float scale_log2) {
+                    int BH, int Lq, int Lk, float scale, float scale_log2) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -1083,15 +1090,20 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = Lq / kQTile;
-  const int t = n_tiles - 1 - (int)blockIdx.y;
-  const int bh = blockIdx.x, b = bh / H, h = bh - b * H;
   const int prefix_blocks = (Lk - Lq) / kBlk;
-  const int own0 = prefix_blocks + 2 * t;
-  const int n_last = own0 + 1;
-  const int total = n_last + 1;
+  const int n_units = n_tiles * BH;
+  auto unit_of = [&](int r) {
+    const int c = (r & 1) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    return r * (int)gridDim.x + c;
+  };
+  // unit w -> query tile (heaviest = last tile first) and number of key blocks it sees
+  auto unit_tile = [&](int w) { return n_tiles - 1 - w / BH; };
+  auto unit_items = [&](int t) { return prefix_blocks + 2 * t + 2; };
 
   if (tid == 0) {
     mbar_init(smem_u32(&sm->qdo_full), 1);
+    mbar_init(smem_u32(&sm->qdo_empty), 1);
+    mbar_init(smem_u32(&sm->delta_read), 256);
     for (int s = 0; s < kDqStages; ++s) {
       mbar_init(smem_u32(&sm->full[s]), 1);
       mbar_init(smem_u32(&sm->empty[s]), 1);
@@ -1101,7 +1113,9 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_init(smem_u32(&sm->sdp_full[s]), 1);
       mbar_init(smem_u32(&sm->sdp_free[s]), 128);
     }
-    mbar_init(smem_u32(&sm->acc_full), 1);
+    mbar_init(smem_u32(&sm->acc_full[0]), 1);
+    mbar_init(smem_u32(&sm->acc_full[1]), 1);
+    mbar_init(smem_u32(&sm->acc_empty), 128);
     mbar_init_fence();
   }
   if (warp == kBwdGroups * 4 + 1) tmem_alloc(smem_u32(&sm->tmem_base), 512);
@@ -1118,24 +1132,31 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       prefetch_tensormap(&tm_v);
       prefetch_tensormap(&tm_do);
       prefetch_tensormap(&tm_o);
-      const uint32_t qb = smem_u32(&sm->qdo_full);
-      mbar_arrive_expect_tx(qb, 6 * kTileBytes);
-      tma_load_4d(o_tile, &tm_o, qb, 0, t * kQTile, h, b);
-      tma_load_4d(o_tile + kTileBytes, &tm_o, qb, 64, t * kQTile, h, b);
-      tma_load_4d(q_tile, &tm_q, qb, 0, t * kQTile, h, b);
-      tma_load_4d(q_tile + kTileBytes, &tm_q, qb, 64, t * kQTile, h, b);
-      tma_load_4d(do_tile, &tm_do, qb, 0, t * kQTile, h, b);
-      tma_load_4d(do_tile + kTileBytes, &tm_do, qb, 64, t * kQTile, h, b);
-      for (int i = 0; i < total; ++i) {
-        const int s = i % kDqStages;
-        mbar_wait(smem_u32(&sm->empty[s]), ((i / kDqStages) & 1) ^ 1, &g_lmk_status, kErrDqProducer);
-        const uint32_t fb = smem_u32(&sm->full[s]);
-        const int n = n_last - i;
-        mbar_arrive_expect_tx(fb, 2 * kTileBytes);
-        tma_load_4d(k_slot(s), &tm_k, fb, 0, n * kBlk, h, b);
-        tma_load_4d(k_slot(s) + kHalfTile, &tm_k, fb, 64, n * kBlk, h, b);
-        tma_load_4d(v_slot(s), &tm_v, fb, 0, n * kBlk, h, b);
-        tma_load_4d(v_slot(s) + kHalfTile, &tm_v, fb, 64, n * kBlk, h, b);
+      int it = 0, u = 0;
+      for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
+        const int t = unit_tile(w), bh = w % BH, b = bh / H, h = bh - b * H;
+        const int total = unit_items(t), n_last = total - 1;
+        const uint32_t qb = smem_u32(&sm->qdo_full);
+        mbar_wait(smem_u32(&sm->qdo_empty), (u & 1) ^ 1, &g_lmk_status, kErrDqProducer);
+        mbar_wait(smem_u32(&sm->delta_read), (u & 1) ^ 1, &g_lmk_status, kErrDqProducer);
+        mbar_arrive_expect_tx(qb, 6 * kTileBytes);
+        tma_load_4d(o_tile, &tm_o, qb, 0, t * kQTile, h, b);
+        tma_load_4d(o_tile + kTileBytes, &tm_o, qb, 64, t * kQTile, h, b);
+        tma_load_4d(q_tile, &tm_q, qb, 0, t * kQTile, h, b);
+        tma_load_4d(q_tile + kTileBytes, &tm_q, qb, 64, t * kQTile, h, b);
+        tma_load_4d(do_tile, &tm_do, qb, 0, t * kQTile, h, b);
+        tma_load_4d(do_tile + kTileBytes, &tm_do, qb, 64, t * kQTile, h, b);
+        for (int i = 0; i < total; ++i, ++it) {
+          const int s = it % kDqStages;
+          mbar_wait(smem_u32(&sm->empty[s]), ((it / kDqStages) & 1) ^ 1, &g_lmk_status, kErrDqProducer);
+          const uint32_t fb = smem_u32(&sm->full[s]);
+          const int n = n_last - i;
+          mbar_arrive_expect_tx(fb, 2 * kTileBytes);
+          tma_load_4d(k_slot(s), &tm_k, fb, 0, n * kBlk, h, b);
+          tma_load_4d(k_slot(s) + kHalfTile, &tm_k, fb, 64, n * kBlk, h, b);
+          tma_load_4d(v_slot(s), &tm_v, fb, 0, n * kBlk, h, b);
+          tma_load_4d(v_slot(s) + kHalfTile, &tm_v, fb, 64, n * kBlk, h, b);
+        }
       }
     }
     __syncwarp();
@@ -1143,25 +1164,30 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (lane == 0) {
       constexpr uint32_t fmt = kBf16 ? 1u : 0u;
       constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);
-      mbar_wait(smem_u32(&sm->qdo_full), 0, &g_lmk_status, kErrDqMma);
       const uint64_t dqd = smem_desc_sw128(q_tile, 16, 1024), ddo = smem_desc_sw128(do_tile, 16, 1024);
       const uint64_t dk0 = smem_desc_sw128(k_slot(0), 16, 1024), dv0 = smem_desc_sw128(v_slot(0), 16, 1024);
-      for (int j = 0; j < total; ++j) {
-        const int s = j % kDqStages, sb = j % kSdpBufs;
-        mbar_wait(smem_u32(&sm->full[s]), (j / kDqStages) & 1, &g_lmk_status, kErrDqMma);
-        if (j >= kSdpBufs)
-          mbar_wait(smem_u32(&sm->sdp_free[sb]), ((j / kSdpBufs) & 1) ^ 1, &g_lmk_status, kErrDqMma);
-        tc_fence_after();
-        const uint64_t dk = desc_advance(dk0, (uint32_t)s * 32768u), dv = desc_advance(dv0, (uint32_t)s * 32768u);
+      int it = 0, u = 0;
+      for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
+        const int total = unit_items(unit_tile(w));
+        mbar_wait(smem_u32(&sm->qdo_full), u & 1, &g_lmk_status, kErrDqMma);
+        for (int i = 0; i < total; ++i, ++it) {
+          const int s = it % kDqStages, sb = it % kSdpBufs;
+          mbar_wait(smem_u32(&sm->full[s]), (it / kDqStages) & 1, &g_lmk_status, kErrDqMma);
+          if (it >= kSdpBufs)
+            mbar_wait(smem_u32(&sm->sdp_free[sb]), ((it / kSdpBufs) & 1) ^ 1, &g_lmk_status, kErrDqMma);
+          tc_fence_after();
+          const uint64_t dk = desc_advance(dk0, (uint32_t)s * 32768u), dv = desc_advance(dv0, (uint32_t)s * 32768u);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk)
-          mma_f16_ss(tmem_s + sb * 64, desc_advance(dqd, kmajor_step(kk, kTileBytes)),
-                     desc_advance(dk, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
+          for (int kk = 0; kk < kD / 16; ++kk)
+            mma_f16_ss(tmem_s + sb * 64, desc_advance(dqd, kmajor_step(kk, kTileBytes)),
+                       desc_advance(dk, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk)
-          mma_f16_ss(tmem_dp + sb * 64, desc_advance(ddo, kmajor_step(kk, kTileBytes)),
-                     desc_advance(dv, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
-        mma_commit(smem_u32(&sm->sdp_full[sb]));
+          for (int kk = 0; kk < kD / 16; ++kk)
+            mma_f16_ss(tmem_dp + sb * 64, desc_advance(ddo, kmajor_step(kk, kTileBytes)),
+                       desc_advance(dv, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
+          mma_commit(smem_u32(&sm->sdp_full[sb]));
+        }
+        mma_commit(smem_u32(&sm->qdo_empty));
       }
     }
     __syncwarp();
@@ -1171,93 +1197,109 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       constexpr uint32_t idesc_q = instr_desc_f16(fmt, 128, 128, 0, 1);   // dQ += dS K  (K is MN-major)
       const uint64_t dv0 = smem_desc_sw128(v_slot(0), 16, 1024);
       const uint64_t dk0t = smem_desc_sw128(k_slot(0), kHalfTile, 1024);
-      for (int i = 0; i < total; ++i) {
-        const int s = i % kDqStages;
-        mbar_wait(smem_u32(&sm->ds_ready[s]), (i / kDqStages) & 1, &g_lmk_status, kErrDqMma);
-        tc_fence_after();
-        const uint64_t dds = desc_advance(dv0, (uint32_t)s * 32768u), dkt = desc_advance(dk0t, (uint32_t)s * 32768u);
+      int it = 0, u = 0;
+      for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
+        const int total = unit_items(unit_tile(w));
+        for (int i = 0; i < total; ++i, ++it) {
+          const int s = it % kDqStages;
+          mbar_wait(smem_u32(&sm->ds_ready[s]), (it / kDqStages) & 1, &g_lmk_status, kErrDqMma);
+          if (i == 0) mbar_wait(smem_u32(&sm->acc_empty), (u & 1) ^ 1, &g_lmk_status, kErrDqMma);
+          tc_fence_after();
+          const uint64_t dds = desc_advance(dv0, (uint32_t)s * 32768u), dkt = desc_advance(dk0t, (uint32_t)s * 32768u);
 #pragma unroll
-        for (int kk = 0; kk < kBlk / 16; ++kk)
-          mma_f16_ss(tmem_dq, desc_advance(dds, kk * 32), desc_advance(dkt, kk * 2048), idesc_q,
-                     (i > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(smem_u32(&sm->empty[s]));
+          for (int kk = 0; kk < kBlk / 16; ++kk)
+            mma_f16_ss(tmem_dq, desc_advance(dds, kk * 32), desc_advance(dkt, kk * 2048), idesc_q,
+                       (i > 0 || kk > 0) ? 1u : 0u);
+          mma_commit(smem_u32(&sm->empty[s]));
+        }
+        mma_commit(smem_u32(&sm->acc_full[u & 1]));
       }
-      mma_commit(smem_u32(&sm->acc_full));
     }
     __syncwarp();
   } else {
-    const int g = warp >> 2;
+    const int g = warp >> 2;                       // warpgroup: items with (running item count) % 2 == g
     const int row = tid & 127;
     const int half = row >> 6;
-    const int own = own0 + half;
     const int vis = min(row & 63, kBlk - 2);
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const int64_t grow = (int64_t)bh * Lq + t * kQTile + row;
-    const float M2 = M_ptr[grow] * kLog2e, Linv = 1.f / L_ptr[grow];
-    // delta = rowsum(O * dO), straight from the swizzled tiles (one row per thread, 16-byte chunks); warpgroup 0 also
-    // publishes it for the dK/dV kernel, which runs after this one
-    mbar_wait(smem_u32(&sm->qdo_full), 0, &g_lmk_status, kErrDqSoftmax);
-    float delta = 0.f;
+    int it0 = 0, u = 0;
+    for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
+      const int t = unit_tile(w), bh = w % BH;
+      const int own = prefix_blocks + 2 * t + half;
+      const int total = unit_items(t), n_last = total - 1;
+      const int64_t grow = (int64_t)bh * Lq + t * kQTile + row;
+      const float M2 = M_ptr[grow] * kLog2e, Linv = 1.f / L_ptr[grow];
+      // delta = rowsum(O * dO), straight from the swizzled tiles (one row per thread, 16-byte chunks); warpgroup 0
+      // also publishes it for the dK/dV kernel, which runs after this one
+      mbar_wait(smem_u32(&sm->qdo_full), u & 1, &g_lmk_status, kErrDqSoftmax);
+      float delta = 0.f;
 #pragma unroll
-    for (int sub = 0; sub < 2; ++sub)
+      for (int sub = 0; sub < 2; ++sub)
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint32_t off = (uint32_t)sub * kTileBytes + (uint32_t)row * 128u + (uint32_t)((c ^ (row & 7)) << 4);
-        uint32_t ov[4], gv[4];
-        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(ov[0]), "=r"(ov[1]), "=r"(ov[2]), "=r"(ov[3])
-                     : "r"(o_tile + off));
-        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(gv[0]), "=r"(gv[1]), "=r"(gv[2]), "=r"(gv[3])
-                     : "r"(do_tile + off));
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t off = (uint32_t)sub * kTileBytes + (uint32_t)row * 128u + (uint32_t)((c ^ (row & 7)) << 4);
+          uint32_t ov[4], gv[4];
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(ov[0]), "=r"(ov[1]), "=r"(ov[2]), "=r"(ov[3]) : "r"(o_tile + off));
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(gv[0]), "=r"(gv[1]), "=r"(gv[2]), "=r"(gv[3]) : "r"(do_tile + off));
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float2 fo, fg;
-          if (kBf16) {
-            fo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ov[e]));
-            fg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv[e]));
-          } else {
-            fo = __half22float2(*reinterpret_cast<const __half2*>(&ov[e]));
-            fg = __half22float2(*reinterpret_cast<const __half2*>(&gv[e]));
+          for (int e = 0; e < 4; ++e) {
+            float2 fo, fg;
+            if (kBf16) {
+              fo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ov[e]));
+              fg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv[e]));
+            } else {
+              fo = __half22float2(*reinterpret_cast<const __half2*>(&ov[e]));
+              fg = __half22float2(*reinterpret_cast<const __half2*>(&gv[e]));
+            }
+            delta = fmaf(fo.x, fg.x, delta);
+            delta = fmaf(fo.y, fg.y, delta);
           }
-          delta = fmaf(fo.x, fg.x, delta);
-          delta = fmaf(fo.y, fg.y, delta);
+        }
+      mbar_arrive(smem_u32(&sm->delta_read));
+      if (g == 0) delta_ptr[grow] = delta;
+      for (int i = (it0 + g) & 1; i < total; i += kBwdGroups) {
+        const int it = it0 + i;
+        const int s = it % kDqStages, sb = it % kSdpBufs;
+        const int n = n_last - i;
+        mbar_wait(smem_u32(&sm->sdp_full[sb]), (it / kSdpBufs) & 1, &g_lmk_status, kErrDqSoftmax);
+        tc_fence_after();
+        const int kind = n > own ? 0 : (n == own ? 1 : 2);
+        // dS replaces the V tile of this stage, which dP = dO V^T has finished reading
+        bwd_item<kBf16, false>(tmem_s + sb * 64 + lane_base, tmem_dp + sb * 64 + lane_base,
+                               smem_u32(&sm->sdp_free[sb]), kind, vis, scale_log2, scale, M2, Linv, delta, 0u,
+                               v_slot(s), row, []() {});
+        fence_proxy_async_smem();
+        mbar_arrive(smem_u32(&sm->ds_ready[s]));
+      }
+      it0 += total;
+      if (g == (u & 1)) {      // drain dQ of this unit; the other warpgroup moves on to the next unit
+        mbar_wait(smem_u32(&sm->acc_full[g]), (u >> 1) & 1, &g_lmk_status, kErrDqEpilogue);
+        tc_fence_after();
+        uint4* orow = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dq_ptr) + grow * kD);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_dq + c * 32 + lane_base, r);
+          tmem_ld_wait();
+          if (c == 3) {
+            tc_fence_before();
+            mbar_arrive(smem_u32(&sm->acc_empty));     // the next unit may start accumulating
+          }
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint4 pk;
+            pk.x = pack2<kBf16>(__uint_as_float(r[8 * v4 + 0]), __uint_as_float(r[8 * v4 + 1]));
+            pk.y = pack2<kBf16>(__uint_as_float(r[8 * v4 + 2]), __uint_as_float(r[8 * v4 + 3]));
+            pk.z = pack2<kBf16>(__uint_as_float(r[8 * v4 + 4]), __uint_as_float(r[8 * v4 + 5]));
+            pk.w = pack2<kBf16>(__uint_as_float(r[8 * v4 + 6]), __uint_as_float(r[8 * v4 + 7]));
+            orow[c * 4 + v4] = pk;
+          }
         }
       }
-    if (g == 0) delta_ptr[grow] = delta;
-    for (int i = g; i < total; i += kBwdGroups) {
-      const int s = i % kDqStages;
-      const int n = n_last - i;
-      const int sb = i % kSdpBufs;
-      mbar_wait(smem_u32(&sm->sdp_full[sb]), (i / kSdpBufs) & 1, &g_lmk_status, kErrDqSoftmax);
-      tc_fence_after();
-      const int kind = n > own ? 0 : (n == own ? 1 : 2);
-      // dS replaces the V tile of this stage, which dP = dO V^T has finished reading
-      bwd_item<kBf16, false>(tmem_s + sb * 64 + lane_base, tmem_dp + sb * 64 + lane_base,
-                             smem_u32(&sm->sdp_free[sb]), kind, vis, scale_log2, scale, M2, Linv, delta, 0u,
-                             v_slot(s), row, []() {});
-      fence_proxy_async_smem();
-      mbar_arrive(smem_u32(&sm->ds_ready[s]));
     }
-    if (g == 0) {
-      mbar_wait(smem_u32(&sm->acc_full), 0, &g_lmk_status, kErrDqEpilogue);
-      tc_fence_after();
-      uint4* orow = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dq_ptr) + grow * kD);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_dq + c * 32 + lane_base, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int v4 = 0; v4 < 4; ++v4) {
-          uint4 pk;
-          pk.x = pack2<kBf16>(__uint_as_float(r[8 * v4 + 0]), __uint_as_float(r[8 * v4 + 1]));
-          pk.y = pack2<kBf16>(__uint_as_float(r[8 * v4 + 2]), __uint_as_float(r[8 * v4 + 3]));
-          pk.z = pack2<kBf16>(__uint_as_float(r[8 * v4 + 4]), __uint_as_float(r[8 * v4 + 5]));
-          pk.w = pack2<kBf16>(__uint_as_float(r[8 * v4 + 6]), __uint_as_float(r[8 * v4 + 7]));
-          orow[c * 4 + v4] = pk;
-        }
-      }
-      tc_fence_before();
-    }
+    tc_fence_before();
   }
   __syncthreads();
   if (warp == kBwdGroups * 4 + 1) {
@@ -1402,14 +1444,15 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
     if (v >= 1 && v < n_sm) n_sm = v;
   }
   const int dkv_units = ((p.Lk / kBlk + 1) / 2) * p.B * p.H;
-  dim3 grid_dkv(dkv_units < n_sm ? dkv_units : n_sm), grid_dq(p.B * p.H, p.Lq / kQTile);
+  const int dq_units = (p.Lq / kQTile) * p.B * p.H;
+  dim3 grid_dkv(dkv_units < n_sm ? dkv_units : n_sm), grid_dq(dq_units < n_sm ? dq_units : n_sm);
 #define LMK_BWD_LAUNCH(BF)                                                                                          \
   do {                                                                                                              \
     /* the dQ kernel also produces delta = rowsum(O * dO), which the dK/dV kernel launched after it reads */         \
     LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dq_kernel<BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
                                   (int)smem_dq));                                                                   \
     sm100_bwd_dq_kernel<BF><<<grid_dq, kBwdThreads, smem_dq, st>>>(tq, tk, tv, tdo, to, p.L, p.M, delta, p.dq, p.H, \
-                                                                   p.Lq, p.Lk, p.scale, scale_log2);                \
+                                                                   p.B * p.H, p.Lq, p.Lk, p.scale, scale_log2);     \
     LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dkv_kernel<BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
                                   (int)smem_dkv));                                                                  \
     sm100_bwd_dkv_kernel<BF><<<grid_dkv, kBwdThreads, smem_dkv, st>>>(tq, tk, tv, tdo, p.L, p.M, delta, p.dk, p.dv, \
