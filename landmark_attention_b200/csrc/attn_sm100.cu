@@ -587,14 +587,33 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         } else {
           const float nmx = -row_max<63>(sv) * scale_log2;
           const float el = ex2(fmaf(sv[63], scale_log2, -m2));
+          const uint64_t c2 = pk2(scale_log2, scale_log2), n2 = pk2(nmx, nmx);
+          uint64_t sp[32];
 #pragma unroll
-          for (int j = 0; j < 63; ++j) sv[j] = ex2(fmaf(sv[j], scale_log2, nmx));
-          const float den = row_sum<63>(sv);
+          for (int j = 0; j < 32; ++j) {
+            float a, b;
+            upk2(fma2(pk2(sv[2 * j], sv[2 * j + 1]), c2, n2), a, b);
+            sp[j] = pk2(ex2(a), j == 31 ? 0.f : ex2(b));
+          }
+          uint64_t s0 = sp[0], s1 = sp[1], s2 = sp[2], s3 = sp[3];
+#pragma unroll
+          for (int j = 4; j < 32; j += 4) {
+            s0 = add2(s0, sp[j]);
+            s1 = add2(s1, sp[j + 1]);
+            s2 = add2(s2, sp[j + 2]);
+            s3 = add2(s3, sp[j + 3]);
+          }
+          float dl, dh;
+          upk2(add2(add2(s0, s1), add2(s2, s3)), dl, dh);
           l += el;
-          const float wg = __fdividef(el, den);
-          sv[63] = 0.f;
+          const float wg = __fdividef(el, dl + dh);
+          const uint64_t w2 = pk2(wg, wg);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) wgt[j] = pack2<kBf16>(sv[2 * j] * wg, sv[2 * j + 1] * wg);
+          for (int j = 0; j < 32; ++j) {
+            float a, b;
+            upk2(mul2(sp[j], w2), a, b);
+            wgt[j] = pack2<kBf16>(a, b);
+          }
         }
       }
       if (k > 0) mbar_wait(smem_u32(&sm->p_free[w]), (k - 1) & 1, &g_lmk_status, kErrFwd2Softmax);
@@ -660,66 +679,115 @@ struct NoHook {
   __device__ __forceinline__ void operator()() const {}
 };
 
+// packed (bf16 or f16) pair -> packed fp32 pair
+template <bool kBf16>
+__device__ __forceinline__ uint64_t unpack2(uint32_t w) {
+  if (kBf16) return pk2u(w << 16, w & 0xffff0000u);
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+  return pk2(f.x, f.y);
+}
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2p(uint64_t v) {
+  float lo, hi;
+  upk2(v, lo, hi);
+  return pack2<kBf16>(lo, hi);
+}
+
+// M2L = (row max + log(row sum)) * log2(e): exp2(s * c - M2L) is the outer-softmax probability.
 template <bool kBf16, bool kNeedP, typename WaitFn, typename AfterSFn = NoHook>
 __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t free_bar, int kind, int vis, float c,
-                                         float scale, float M2, float Linv, float delta, uint32_t p_dst,
-                                         uint32_t ds_dst, int row, WaitFn wait_dst, AfterSFn after_s = AfterSFn()) {
-  float sv[64];
+                                         float scale, float M2L, float delta, uint32_t p_dst, uint32_t ds_dst, int row,
+                                         WaitFn wait_dst, AfterSFn after_s = AfterSFn()) {
+  uint64_t sp[32];      // the row as packed pairs: S, then P
+  float nmx = 0.f, lm2 = 0.f;
   {
     uint32_t ra[32], rb[32];
     tmem_ld_32x32b_x32(ts, ra);
     tmem_ld_32x32b_x32(ts + 32, rb);
     tmem_ld_wait();
+    if (kind == 2) {
+      float sv[64];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      sv[j] = __uint_as_float(ra[j]);
-      sv[32 + j] = __uint_as_float(rb[j]);
+      for (int j = 0; j < 32; ++j) {
+        sv[j] = __uint_as_float(ra[j]);
+        sv[32 + j] = __uint_as_float(rb[j]);
+      }
+      nmx = -row_max<63>(sv) * c;
+      lm2 = sv[63] * c;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      sp[j] = pk2u(ra[2 * j], ra[2 * j + 1]);
+      sp[16 + j] = pk2u(rb[2 * j], rb[2 * j + 1]);
     }
   }
   after_s();      // S is in registers: a caller with separate S / dP buffers releases S and waits for dP here
   float sub = delta, lm_ds = 0.f;
+  const uint64_t c2 = pk2(c, c);
   if (kind == 0) {
 #pragma unroll
-    for (int j = 0; j < 64; ++j) sv[j] = 0.f;
+    for (int j = 0; j < 32; ++j) sp[j] = 0ull;
   } else if (kind == 1) {
+    const uint64_t m2 = pk2(-M2L, -M2L);
 #pragma unroll
-    for (int j = 0; j < 64; ++j) sv[j] = (j <= vis) ? ex2(fmaf(sv[j], c, -M2)) * Linv : 0.f;
+    for (int j = 0; j < 32; ++j) {
+      float a, b;
+      upk2(fma2(sp[j], c2, m2), a, b);
+      sp[j] = pk2(2 * j <= vis ? ex2(a) : 0.f, 2 * j + 1 <= vis ? ex2(b) : 0.f);
+    }
   } else {
-    const float nmx = -row_max<63>(sv) * c;
-    const float lm2 = sv[63] * c;
+    const uint64_t n2 = pk2(nmx, nmx);
 #pragma unroll
-    for (int j = 0; j < 63; ++j) sv[j] = ex2(fmaf(sv[j], c, nmx));
-    sv[63] = 0.f;
-    const float den = row_sum<63>(sv);
-    float nd0 = 0.f, nd1 = 0.f, nd2 = 0.f, nd3 = 0.f;
+    for (int j = 0; j < 32; ++j) {
+      float a, b;
+      upk2(fma2(sp[j], c2, n2), a, b);
+      sp[j] = pk2(ex2(a), j == 31 ? 0.f : ex2(b));
+    }
+    uint64_t s0 = sp[0], s1 = sp[1], s2 = sp[2], s3 = sp[3];
+#pragma unroll
+    for (int j = 4; j < 32; j += 4) {
+      s0 = add2(s0, sp[j]);
+      s1 = add2(s1, sp[j + 1]);
+      s2 = add2(s2, sp[j + 2]);
+      s3 = add2(s3, sp[j + 3]);
+    }
+    uint64_t n0 = 0ull, n1 = 0ull, n2a = 0ull, n3 = 0ull;
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
       uint32_t r[32];
       tmem_ld_32x32b_x32(tdp + hf * 32, r);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        nd0 = fmaf(sv[hf * 32 + j], __uint_as_float(r[j]), nd0);
-        nd1 = fmaf(sv[hf * 32 + j + 1], __uint_as_float(r[j + 1]), nd1);
-        nd2 = fmaf(sv[hf * 32 + j + 2], __uint_as_float(r[j + 2]), nd2);
-        nd3 = fmaf(sv[hf * 32 + j + 3], __uint_as_float(r[j + 3]), nd3);
+      for (int j = 0; j < 16; j += 4) {
+        n0 = fma2(sp[hf * 16 + j], pk2u(r[2 * j], r[2 * j + 1]), n0);
+        n1 = fma2(sp[hf * 16 + j + 1], pk2u(r[2 * j + 2], r[2 * j + 3]), n1);
+        n2a = fma2(sp[hf * 16 + j + 2], pk2u(r[2 * j + 4], r[2 * j + 5]), n2a);
+        n3 = fma2(sp[hf * 16 + j + 3], pk2u(r[2 * j + 6], r[2 * j + 7]), n3);
       }
     }
-    const float rden = __fdividef(1.f, den);
-    const float nd = ((nd0 + nd1) + (nd2 + nd3)) * rden;
-    const float g = ex2(lm2 - M2) * Linv;
+    float dl, dh, ql, qh;
+    upk2(add2(add2(s0, s1), add2(s2, s3)), dl, dh);
+    upk2(add2(add2(n0, n1), add2(n2a, n3)), ql, qh);
+    const float rden = __fdividef(1.f, dl + dh);
+    const float nd = (ql + qh) * rden;
+    const float g = ex2(lm2 - M2L);
     const float w = g * rden;
+    const uint64_t w2 = pk2(w, w);
 #pragma unroll
-    for (int j = 0; j < 63; ++j) sv[j] *= w;
+    for (int j = 0; j < 32; ++j) sp[j] = mul2(sp[j], w2);
     sub = nd;
     lm_ds = g * (nd - delta) * scale;
   }
+  // dS = P * (dP - sub) * scale = P * fma(dP, scale, -sub * scale)
+  const uint64_t sc2 = pk2(scale, scale);
+  const float nss = -sub * scale;
+  const uint64_t nss2 = pk2(nss, nss);
   if (kNeedP) {
-    // dK/dV kernel: P is packed first and dS is formed from the packed (bf16) P, so that both result rows sit in
+    // dK/dV kernel: P is packed first and dS is formed from the packed (16-bit) P, so that both result rows sit in
     // registers before the shared tiles are claimed; the wait for the tiles then only covers the 16 stores.
     uint32_t wp[32], wd[32];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) wp[j] = pack2<kBf16>(sv[2 * j], sv[2 * j + 1]);
+    for (int j = 0; j < 32; ++j) wp[j] = pack2p<kBf16>(sp[j]);
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
       if (kind == 0) {
@@ -735,16 +803,9 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
         }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          float p0, p1;
-          if (kBf16) {
-            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wp[hf * 16 + j]));
-            p0 = f.x; p1 = f.y;
-          } else {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wp[hf * 16 + j]));
-            p0 = f.x; p1 = f.y;
-          }
-          float d0 = p0 * (__uint_as_float(r[2 * j]) - sub) * scale;
-          float d1 = p1 * (__uint_as_float(r[2 * j + 1]) - sub) * scale;
+          const uint64_t t = fma2(pk2u(r[2 * j], r[2 * j + 1]), sc2, nss2);
+          float d0, d1;
+          upk2(mul2(unpack2<kBf16>(wp[hf * 16 + j]), t), d0, d1);
           if (hf == 1 && j == 15 && kind == 2) d1 = lm_ds;
           wd[hf * 16 + j] = pack2<kBf16>(d0, d1);
         }
@@ -771,8 +832,9 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
         }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          float d0 = sv[hf * 32 + 2 * j] * (__uint_as_float(r[2 * j]) - sub) * scale;
-          float d1 = sv[hf * 32 + 2 * j + 1] * (__uint_as_float(r[2 * j + 1]) - sub) * scale;
+          const uint64_t t = fma2(pk2u(r[2 * j], r[2 * j + 1]), sc2, nss2);
+          float d0, d1;
+          upk2(mul2(sp[hf * 16 + j], t), d0, d1);
           if (hf == 1 && j == 15 && kind == 2) d1 = lm_ds;
           wd[j] = pack2<kBf16>(d0, d1);
         }
@@ -1002,12 +1064,12 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int tq = tq0 + i;
         const int own = prefix_blocks + 2 * tq + half;
         const int64_t grow = (int64_t)bh * Lq + tq * kQTile + row;
-        const float M2 = M_ptr[grow] * kLog2e, Linv = 1.f / L_ptr[grow], delta = delta_ptr[grow];
+        const float M2L = fmaf(M_ptr[grow], kLog2e, __log2f(L_ptr[grow])), delta = delta_ptr[grow];
         mbar_wait(smem_u32(&sm->sdp_full[g]), it & 1, &g_lmk_status, kErrDkvSoftmax);
         tc_fence_after();
         const int kind = n > own ? 0 : (n == own ? 1 : 2);
         bwd_item<kBf16, true>(tmem_s(g) + lane_base, tmem_dp(g) + lane_base, smem_u32(&sm->sdp_free[g]), kind, vis,
-                              scale_log2, scale, M2, Linv, delta, p_tile, ds_tile, row, [&]() {
+                              scale_log2, scale, M2L, delta, p_tile, ds_tile, row, [&]() {
                                 // The single P/dS tile pair is written in the order a, b, a, b, ...: before writing,
                                 // the accumulating MMAs of the OTHER warpgroup's latest item must have read it.  Each
                                 // warpgroup is the only waiter on the other one's barrier and sees every phase of it.
@@ -1228,7 +1290,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const int own = prefix_blocks + 2 * t + half;
       const int total = unit_items(t), n_last = total - 1;
       const int64_t grow = (int64_t)bh * Lq + t * kQTile + row;
-      const float M2 = M_ptr[grow] * kLog2e, Linv = 1.f / L_ptr[grow];
+      const float M2L = fmaf(M_ptr[grow], kLog2e, __log2f(L_ptr[grow]));
       // delta = rowsum(O * dO), straight from the swizzled tiles (one row per thread, 16-byte chunks); warpgroup 0
       // also publishes it for the dK/dV kernel, which runs after this one
       mbar_wait(smem_u32(&sm->qdo_full), u & 1, &g_lmk_status, kErrDqSoftmax);
@@ -1268,7 +1330,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const int kind = n > own ? 0 : (n == own ? 1 : 2);
         // dS replaces the V tile of this stage, which dP = dO V^T has finished reading
         bwd_item<kBf16, false>(tmem_s + sb * 64 + lane_base, tmem_dp + sb * 64 + lane_base,
-                               smem_u32(&sm->sdp_free[sb]), kind, vis, scale_log2, scale, M2, Linv, delta, 0u,
+                               smem_u32(&sm->sdp_free[sb]), kind, vis, scale_log2, scale, M2L, delta, 0u,
                                v_slot(s), row, []() {});
         fence_proxy_async_smem();
         mbar_arrive(smem_u32(&sm->ds_ready[s]));
