@@ -374,6 +374,11 @@ constexpr int kFwd2Stages = 4;
 constexpr int kFwd2Threads = 352;
 enum { kErrFwd2Producer = 111, kErrFwd2Mma = 112, kErrFwd2Softmax = 113, kErrFwd2Epilogue = 114 };
 
+#ifndef LMK_FWD_POLY_EVERY
+#define LMK_FWD_POLY_EVERY 4
+#endif
+constexpr int kFwdPolyEvery = LMK_FWD_POLY_EVERY;   // one in this many pairs of exponentials uses ex2_poly2
+
 struct Fwd2Smem {
   uint64_t q_full;
   uint64_t full[kFwd2Stages];
@@ -591,9 +596,14 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           uint64_t sp[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            float a, b;
-            upk2(fma2(pk2(sv[2 * j], sv[2 * j + 1]), c2, n2), a, b);
-            sp[j] = pk2(ex2(a), j == 31 ? 0.f : ex2(b));
+            const uint64_t x = fma2(pk2(sv[2 * j], sv[2 * j + 1]), c2, n2);
+            if (j % kFwdPolyEvery == 1) {
+              sp[j] = ex2_poly2(x);       // a share of the exponentials runs on the FMA pipe
+            } else {
+              float a, b;
+              upk2(x, a, b);
+              sp[j] = pk2(ex2(a), j == 31 ? 0.f : ex2(b));
+            }
           }
           uint64_t s0 = sp[0], s1 = sp[1], s2 = sp[2], s3 = sp[3];
 #pragma unroll
@@ -694,10 +704,13 @@ __device__ __forceinline__ uint32_t pack2p(uint64_t v) {
 }
 
 // M2L = (row max + log(row sum)) * log2(e): exp2(s * c - M2L) is the outer-softmax probability.
-template <bool kBf16, bool kNeedP, typename WaitFn, typename AfterSFn = NoHook>
+template <bool kBf16, bool kNeedP, typename WaitFn, typename AfterSFn = NoHook, typename BeforeDpFn = NoHook,
+          typename BetweenFn = NoHook>
 __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t free_bar, int kind, int vis, float c,
                                          float scale, float M2L, float delta, uint32_t p_dst, uint32_t ds_dst, int row,
-                                         WaitFn wait_dst, AfterSFn after_s = AfterSFn()) {
+                                         WaitFn wait_dst, AfterSFn after_s = AfterSFn(),
+                                         BeforeDpFn before_dp = BeforeDpFn(),
+                                         BetweenFn between_stores = BetweenFn()) {
   uint64_t sp[32];      // the row as packed pairs: S, then P
   float nmx = 0.f, lm2 = 0.f;
   {
@@ -721,12 +734,13 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
       sp[16 + j] = pk2u(rb[2 * j], rb[2 * j + 1]);
     }
   }
-  after_s();      // S is in registers: a caller with separate S / dP buffers releases S and waits for dP here
+  after_s();      // S is in registers: a caller with separate S / dP buffers releases the S buffer here
   float sub = delta, lm_ds = 0.f;
   const uint64_t c2 = pk2(c, c);
   if (kind == 0) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) sp[j] = 0ull;
+    before_dp();
   } else if (kind == 1) {
     const uint64_t m2 = pk2(-M2L, -M2L);
 #pragma unroll
@@ -735,6 +749,7 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
       upk2(fma2(sp[j], c2, m2), a, b);
       sp[j] = pk2(2 * j <= vis ? ex2(a) : 0.f, 2 * j + 1 <= vis ? ex2(b) : 0.f);
     }
+    before_dp();
   } else {
     const uint64_t n2 = pk2(nmx, nmx);
 #pragma unroll
@@ -752,6 +767,7 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
       s3 = add2(s3, sp[j + 3]);
     }
     uint64_t n0 = 0ull, n1 = 0ull, n2a = 0ull, n3 = 0ull;
+    before_dp();    // a caller with separate S / dP buffers waits for dP only now, after the exponentials
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
       uint32_t r[32];
@@ -813,6 +829,7 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
     }
     wait_dst();
     store_row_sw128(p_dst, row, wp);
+    between_stores();   // the P tile and the dS tile are handed over separately
     store_row_sw128(ds_dst, row, wd);
   } else {
     wait_dst();
@@ -867,10 +884,14 @@ struct DkvSmem {
   uint64_t kv_empty;
   uint64_t full[kDkvStages];
   uint64_t empty[kDkvStages];
-  uint64_t sdp_full[2];     // per key block of the pair (= per softmax warpgroup)
-  uint64_t sdp_free[2];
-  uint64_t pds_ready;
-  uint64_t pds_free[2];     // [g]: the accumulating MMAs of warpgroup g's latest item have read the P/dS tiles
+  uint64_t s_full;          // S of both blocks (one N = 128 product)
+  uint64_t s_free;          // both warpgroups hold S in registers
+  uint64_t dp_full;
+  uint64_t dp_free;         // both warpgroups have read dP for the last time
+  uint64_t p_ready;         // the P tile / the dS tile are handed over separately, so that one warpgroup's stores
+  uint64_t ds_ready;        // overlap the other one's accumulating MMAs
+  uint64_t p_free[2];       // [g]: the dV MMAs of warpgroup g's latest item have read the P tile
+  uint64_t ds_free[2];      // [g]: likewise the dK MMAs and the dS tile
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -878,9 +899,9 @@ struct DkvSmem {
 
 // Persistent; a work unit is a PAIR of adjacent 64-key blocks (a = 2c, b = 2c+1) of one (batch, head).  Both blocks
 // stay in shared memory while the unit streams the query tiles that see them, so each 64 KB Q/dO tile is fetched from
-// L2 once per 128 keys.  Warpgroup 0 rebuilds P and dS for block a, warpgroup 1 for block b; the products of block b
-// are issued after those of block a, so warpgroup 1 runs about one MMA group behind warpgroup 0 and the two can share
-// a single P/dS tile pair (a writer waits until the accumulating MMAs of the previous item have read it).
+// L2 once per 128 keys, and S / dP of the two blocks are single N = 128 products.  Warpgroup 0 rebuilds P and dS for
+// block a, warpgroup 1 for block b; they share a single P/dS tile pair (a writer waits until the accumulating MMAs of
+// the item written before have read it), which settles them half an item apart.
 // CTA c takes units w = round * grid + c with the direction alternating per round (snake), heaviest pairs first.
 // Loads, S/dP products and the softmax of the next unit start while the accumulators of the current one are drained.
 template <bool kBf16>
@@ -893,8 +914,9 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  auto k_tile = [&](int g) { return base + (uint32_t)g * 32768u; };             // block g of the pair: K then V
-  auto v_tile = [&](int g) { return base + (uint32_t)g * 32768u + 16384u; };
+  // K of the pair as one [128 keys x 128 d] K-major operand: 64-feature sub-tile c at c * 16 KB, block g's 64 rows at
+  // g * 8 KB inside it; V likewise, 32 KB further
+  const uint32_t k_pair = base, v_pair = base + 32768u;
   auto q_slot = [&](int s) { return base + 65536u + (uint32_t)s * 65536u; };
   auto do_slot = [&](int s) { return base + 65536u + (uint32_t)s * 65536u + 32768u; };
   const uint32_t p_tile = base + 65536u + kDkvStages * 65536u;
@@ -920,15 +942,20 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(smem_u32(&sm->full[s]), 1);
       mbar_init(smem_u32(&sm->empty[s]), 1);
     }
+    mbar_init(smem_u32(&sm->s_full), 1);
+    mbar_init(smem_u32(&sm->s_free), 256);
+    mbar_init(smem_u32(&sm->dp_full), 1);
+    mbar_init(smem_u32(&sm->dp_free), 256);
     for (int g = 0; g < 2; ++g) {
-      mbar_init(smem_u32(&sm->sdp_full[g]), 1);
-      mbar_init(smem_u32(&sm->sdp_free[g]), 128);
       mbar_init(smem_u32(&sm->acc_full[g]), 1);
       mbar_init(smem_u32(&sm->acc_empty[g]), 128);
     }
-    mbar_init(smem_u32(&sm->pds_ready), 128);
-    mbar_init(smem_u32(&sm->pds_free[0]), 1);
-    mbar_init(smem_u32(&sm->pds_free[1]), 1);
+    mbar_init(smem_u32(&sm->p_ready), 128);
+    mbar_init(smem_u32(&sm->ds_ready), 128);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(smem_u32(&sm->p_free[g]), 1);
+      mbar_init(smem_u32(&sm->ds_free[g]), 1);
+    }
     mbar_init_fence();
   }
   if (warp == kBwdGroups * 4 + 1) tmem_alloc(smem_u32(&sm->tmem_base), 512);
@@ -956,10 +983,10 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_arrive_expect_tx(kvb, 4 * kTileBytes);
         for (int g = 0; g < 2; ++g) {       // a block past the end of the sequence reads as zeros
           const int r0 = (2 * pair + g) * kBlk;
-          tma_load_4d(k_tile(g), &tm_k, kvb, 0, r0, h, b);
-          tma_load_4d(k_tile(g) + kHalfTile, &tm_k, kvb, 64, r0, h, b);
-          tma_load_4d(v_tile(g), &tm_v, kvb, 0, r0, h, b);
-          tma_load_4d(v_tile(g) + kHalfTile, &tm_v, kvb, 64, r0, h, b);
+          tma_load_4d(k_pair + g * kHalfTile, &tm_k, kvb, 0, r0, h, b);
+          tma_load_4d(k_pair + kTileBytes + g * kHalfTile, &tm_k, kvb, 64, r0, h, b);
+          tma_load_4d(v_pair + g * kHalfTile, &tm_v, kvb, 0, r0, h, b);
+          tma_load_4d(v_pair + kTileBytes + g * kHalfTile, &tm_v, kvb, 64, r0, h, b);
         }
         for (int i = 0; i < n_items; ++i, ++it) {
           const int s = it % kDkvStages;
@@ -976,11 +1003,13 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     __syncwarp();
   } else if (warp == kBwdGroups * 4 + 1) {
-    // S_g = Q K_g^T and dP_g = dO V_g^T for both blocks of the pair, one query tile at a time
+    // S = Q K^T and dP = dO V^T for both blocks of the pair at once (N = 128: full-rate MMAs), one query tile at a
+    // time.  S has its own full / free barriers: the warpgroups hold S in registers early in an item, so the next S
+    // product runs while they are still busy with dP.
     if (lane == 0) {
       constexpr uint32_t fmt = kBf16 ? 1u : 0u;
-      constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);
-      const uint64_t dk0 = smem_desc_sw128(k_tile(0), 16, 1024), dv0 = smem_desc_sw128(v_tile(0), 16, 1024);
+      constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 128, 0, 0);
+      const uint64_t dk0 = smem_desc_sw128(k_pair, 16, 1024), dv0 = smem_desc_sw128(v_pair, 16, 1024);
       const uint64_t dq0 = smem_desc_sw128(q_slot(0), 16, 1024), ddo0 = smem_desc_sw128(do_slot(0), 16, 1024);
       int it = 0, u = 0;
       for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
@@ -990,21 +1019,20 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           const int s = it % kDkvStages;
           mbar_wait(smem_u32(&sm->full[s]), (it / kDkvStages) & 1, &g_lmk_status, kErrDkvMma);
           const uint64_t dq = desc_advance(dq0, (uint32_t)s * 65536u), ddo = desc_advance(ddo0, (uint32_t)s * 65536u);
+          if (it >= 1) mbar_wait(smem_u32(&sm->s_free), (it & 1) ^ 1, &g_lmk_status, kErrDkvMma);
+          tc_fence_after();
 #pragma unroll
-          for (int g = 0; g < 2; ++g) {
-            if (it >= 1) mbar_wait(smem_u32(&sm->sdp_free[g]), (it & 1) ^ 1, &g_lmk_status, kErrDkvMma);
-            tc_fence_after();
-            const uint64_t dkt = desc_advance(dk0, (uint32_t)g * 32768u), dvt = desc_advance(dv0, (uint32_t)g * 32768u);
+          for (int kk = 0; kk < kD / 16; ++kk)
+            mma_f16_ss(tmem_s(0), desc_advance(dq, kmajor_step(kk, kTileBytes)),
+                       desc_advance(dk0, kmajor_step(kk, kTileBytes)), idesc_s, kk > 0);
+          mma_commit(smem_u32(&sm->s_full));
+          if (it >= 1) mbar_wait(smem_u32(&sm->dp_free), (it & 1) ^ 1, &g_lmk_status, kErrDkvMma);
+          tc_fence_after();
 #pragma unroll
-            for (int kk = 0; kk < kD / 16; ++kk)
-              mma_f16_ss(tmem_s(g), desc_advance(dq, kmajor_step(kk, kTileBytes)),
-                         desc_advance(dkt, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
-#pragma unroll
-            for (int kk = 0; kk < kD / 16; ++kk)
-              mma_f16_ss(tmem_dp(g), desc_advance(ddo, kmajor_step(kk, kTileBytes)),
-                         desc_advance(dvt, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
-            mma_commit(smem_u32(&sm->sdp_full[g]));
-          }
+          for (int kk = 0; kk < kD / 16; ++kk)
+            mma_f16_ss(tmem_dp(0), desc_advance(ddo, kmajor_step(kk, kTileBytes)),
+                       desc_advance(dv0, kmajor_step(kk, kTileBytes)), idesc_s, kk > 0);
+          mma_commit(smem_u32(&sm->dp_full));
         }
         mma_commit(smem_u32(&sm->kv_empty));      // K / V tiles may be replaced once these products are done
       }
@@ -1029,18 +1057,21 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
             // item j = 2 * it + g of the single P/dS tile pair
-            mbar_wait(smem_u32(&sm->pds_ready), g, &g_lmk_status, kErrDkvMma);
+            mbar_wait(smem_u32(&sm->p_ready), g, &g_lmk_status, kErrDkvMma);
             if (i == 0) mbar_wait(smem_u32(&sm->acc_empty[g]), (u & 1) ^ 1, &g_lmk_status, kErrDkvMma);
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < kQTile / 16; ++kk)
               mma_f16_ss(tmem_dv(g), desc_advance(ddot, kk * 2048), desc_advance(dpt, kk * 2048), idesc_t,
                          (i > 0 || kk > 0) ? 1u : 0u);
+            mma_commit(smem_u32(&sm->p_free[g]));
+            mbar_wait(smem_u32(&sm->ds_ready), g, &g_lmk_status, kErrDkvMma);
+            tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < kQTile / 16; ++kk)
               mma_f16_ss(tmem_dk(g), desc_advance(dqt, kk * 2048), desc_advance(ddst, kk * 2048), idesc_t,
                          (i > 0 || kk > 0) ? 1u : 0u);
-            mma_commit(smem_u32(&sm->pds_free[g]));
+            mma_commit(smem_u32(&sm->ds_free[g]));
           }
           mma_commit(smem_u32(&sm->empty[s]));
         }
@@ -1065,21 +1096,37 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int own = prefix_blocks + 2 * tq + half;
         const int64_t grow = (int64_t)bh * Lq + tq * kQTile + row;
         const float M2L = fmaf(M_ptr[grow], kLog2e, __log2f(L_ptr[grow])), delta = delta_ptr[grow];
-        mbar_wait(smem_u32(&sm->sdp_full[g]), it & 1, &g_lmk_status, kErrDkvSoftmax);
+        mbar_wait(smem_u32(&sm->s_full), it & 1, &g_lmk_status, kErrDkvSoftmax);
         tc_fence_after();
         const int kind = n > own ? 0 : (n == own ? 1 : 2);
-        bwd_item<kBf16, true>(tmem_s(g) + lane_base, tmem_dp(g) + lane_base, smem_u32(&sm->sdp_free[g]), kind, vis,
+        bwd_item<kBf16, true>(tmem_s(g) + lane_base, tmem_dp(g) + lane_base, smem_u32(&sm->dp_free), kind, vis,
                               scale_log2, scale, M2L, delta, p_tile, ds_tile, row, [&]() {
                                 // The single P/dS tile pair is written in the order a, b, a, b, ...: before writing,
                                 // the accumulating MMAs of the OTHER warpgroup's latest item must have read it.  Each
-                                // warpgroup is the only waiter on the other one's barrier and sees every phase of it.
+                                // warpgroup is the only waiter on the other one's barriers and sees every phase.
                                 const int prev = 2 * it + g - 1;          // item written just before this one
                                 if (prev >= 0)
-                                  mbar_wait(smem_u32(&sm->pds_free[1 - g]), (prev >> 1) & 1, &g_lmk_status,
+                                  mbar_wait(smem_u32(&sm->p_free[1 - g]), (prev >> 1) & 1, &g_lmk_status,
+                                            kErrDkvSoftmax);
+                              },
+                              [&]() {
+                                tc_fence_before();
+                                mbar_arrive(smem_u32(&sm->s_free));
+                              },
+                              [&]() {
+                                mbar_wait(smem_u32(&sm->dp_full), it & 1, &g_lmk_status, kErrDkvSoftmax);
+                                tc_fence_after();
+                              },
+                              [&]() {
+                                fence_proxy_async_smem();
+                                mbar_arrive(smem_u32(&sm->p_ready));
+                                const int prev = 2 * it + g - 1;
+                                if (prev >= 0)
+                                  mbar_wait(smem_u32(&sm->ds_free[1 - g]), (prev >> 1) & 1, &g_lmk_status,
                                             kErrDkvSoftmax);
                               });
         fence_proxy_async_smem();
-        mbar_arrive(smem_u32(&sm->pds_ready));
+        mbar_arrive(smem_u32(&sm->ds_ready));
       }
       // epilogue: each warpgroup drains its own block; thread = feature d, TMEM column = key j -> dV[key][d], dK[key][d]
       mbar_wait(smem_u32(&sm->acc_full[g]), u & 1, &g_lmk_status, kErrDkvEpilogue);

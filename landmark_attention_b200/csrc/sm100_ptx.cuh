@@ -196,5 +196,27 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// exp2 of two values on the FMA and integer pipes instead of the special-function unit: round to the nearest integer
+// n with the 1.5 * 2^23 trick, evaluate a cubic for 2^(x - n) on [-0.5, 0.5] (relative error 7.5e-5, well below one
+// bf16 / fp16 rounding step of the 16-bit weights it feeds) and add n to the exponent field.  The forward softmax
+// threads are bound by the special-function unit (16 results per clock per SM), so a share of their exponentials
+// goes this way.  Inputs are clamped to >= -126 (results below 2^-126 are not needed).
+__device__ __forceinline__ uint64_t ex2_poly2(uint64_t x) {
+  float a, b;
+  upk2(x, a, b);
+  x = pk2(fmaxf(a, -126.f), fmaxf(b, -126.f));
+  const uint64_t t = add2(x, pk2(12582912.f, 12582912.f));
+  const uint64_t n = add2(t, pk2(-12582912.f, -12582912.f));
+  const uint64_t r = fma2(n, pk2(-1.f, -1.f), x);
+  uint64_t p = fma2(pk2(0.05517083778977394f, 0.05517083778977394f), r, pk2(0.24260935187339783f, 0.24260935187339783f));
+  p = fma2(p, r, pk2(0.6932609677314758f, 0.6932609677314758f));
+  p = fma2(p, r, pk2(0.9999281764030457f, 0.9999281764030457f));
+  float tl, th, pl, ph;
+  upk2(t, tl, th);
+  upk2(p, pl, ph);
+  return pk2(__int_as_float(__float_as_int(pl) + (__float_as_int(tl) << 23)),
+             __int_as_float(__float_as_int(ph) + (__float_as_int(th) << 23)));
+}
+
 }  // namespace ptx
 }  // namespace lmk
