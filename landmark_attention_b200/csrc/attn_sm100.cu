@@ -704,6 +704,8 @@ __device__ __forceinline__ uint32_t pack2p(uint64_t v) {
 }
 
 // M2L = (row max + log(row sum)) * log2(e): exp2(s * c - M2L) is the outer-softmax probability.
+// S and dP are each read from TMEM once and held as packed pairs; dP's buffer is released (free_bar) as soon as it is
+// in registers, before the reductions, so the next dP product can start early.
 template <bool kBf16, bool kNeedP, typename WaitFn, typename AfterSFn = NoHook, typename BeforeDpFn = NoHook,
           typename BetweenFn = NoHook>
 __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t free_bar, int kind, int vis, float c,
@@ -712,6 +714,7 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
                                          BeforeDpFn before_dp = BeforeDpFn(),
                                          BetweenFn between_stores = BetweenFn()) {
   uint64_t sp[32];      // the row as packed pairs: S, then P
+  uint64_t dp[32];      // dP, then dS
   float nmx = 0.f, lm2 = 0.f;
   {
     uint32_t ra[32], rb[32];
@@ -737,10 +740,10 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
   after_s();      // S is in registers: a caller with separate S / dP buffers releases the S buffer here
   float sub = delta, lm_ds = 0.f;
   const uint64_t c2 = pk2(c, c);
+  uint64_t s0 = 0ull, s1 = 0ull, s2 = 0ull, s3 = 0ull;
   if (kind == 0) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) sp[j] = 0ull;
-    before_dp();
   } else if (kind == 1) {
     const uint64_t m2 = pk2(-M2L, -M2L);
 #pragma unroll
@@ -749,7 +752,6 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
       upk2(fma2(sp[j], c2, m2), a, b);
       sp[j] = pk2(2 * j <= vis ? ex2(a) : 0.f, 2 * j + 1 <= vis ? ex2(b) : 0.f);
     }
-    before_dp();
   } else {
     const uint64_t n2 = pk2(nmx, nmx);
 #pragma unroll
@@ -758,7 +760,7 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
       upk2(fma2(sp[j], c2, n2), a, b);
       sp[j] = pk2(ex2(a), j == 31 ? 0.f : ex2(b));
     }
-    uint64_t s0 = sp[0], s1 = sp[1], s2 = sp[2], s3 = sp[3];
+    s0 = sp[0], s1 = sp[1], s2 = sp[2], s3 = sp[3];
 #pragma unroll
     for (int j = 4; j < 32; j += 4) {
       s0 = add2(s0, sp[j]);
@@ -766,20 +768,32 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
       s2 = add2(s2, sp[j + 2]);
       s3 = add2(s3, sp[j + 3]);
     }
+  }
+  before_dp();    // a caller with separate S / dP buffers waits for dP only now, after the exponentials
+  if (kind == 0) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) dp[j] = 0ull;
+  } else {
+    uint32_t ra[32], rb[32];
+    tmem_ld_32x32b_x32(tdp, ra);
+    tmem_ld_32x32b_x32(tdp + 32, rb);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      dp[j] = pk2u(ra[2 * j], ra[2 * j + 1]);
+      dp[16 + j] = pk2u(rb[2 * j], rb[2 * j + 1]);
+    }
+  }
+  tc_fence_before();
+  mbar_arrive(free_bar);
+  if (kind == 2) {
     uint64_t n0 = 0ull, n1 = 0ull, n2a = 0ull, n3 = 0ull;
-    before_dp();    // a caller with separate S / dP buffers waits for dP only now, after the exponentials
 #pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(tdp + hf * 32, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 16; j += 4) {
-        n0 = fma2(sp[hf * 16 + j], pk2u(r[2 * j], r[2 * j + 1]), n0);
-        n1 = fma2(sp[hf * 16 + j + 1], pk2u(r[2 * j + 2], r[2 * j + 3]), n1);
-        n2a = fma2(sp[hf * 16 + j + 2], pk2u(r[2 * j + 4], r[2 * j + 5]), n2a);
-        n3 = fma2(sp[hf * 16 + j + 3], pk2u(r[2 * j + 6], r[2 * j + 7]), n3);
-      }
+    for (int j = 0; j < 32; j += 4) {
+      n0 = fma2(sp[j], dp[j], n0);
+      n1 = fma2(sp[j + 1], dp[j + 1], n1);
+      n2a = fma2(sp[j + 2], dp[j + 2], n2a);
+      n3 = fma2(sp[j + 3], dp[j + 3], n3);
     }
     float dl, dh, ql, qh;
     upk2(add2(add2(s0, s1), add2(s2, s3)), dl, dh);
@@ -798,70 +812,25 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
   const uint64_t sc2 = pk2(scale, scale);
   const float nss = -sub * scale;
   const uint64_t nss2 = pk2(nss, nss);
+  uint32_t wd[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float d0, d1;
+    upk2(mul2(sp[j], fma2(dp[j], sc2, nss2)), d0, d1);
+    if (j == 31 && kind == 2) d1 = lm_ds;
+    wd[j] = pack2<kBf16>(d0, d1);
+  }
   if (kNeedP) {
-    // dK/dV kernel: P is packed first and dS is formed from the packed (16-bit) P, so that both result rows sit in
-    // registers before the shared tiles are claimed; the wait for the tiles then only covers the 16 stores.
-    uint32_t wp[32], wd[32];
+    uint32_t wp[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) wp[j] = pack2p<kBf16>(sp[j]);
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      if (kind == 0) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) wd[hf * 16 + j] = 0u;
-      } else {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tdp + hf * 32, r);
-        tmem_ld_wait();
-        if (hf == 1) {
-          tc_fence_before();
-          mbar_arrive(free_bar);
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const uint64_t t = fma2(pk2u(r[2 * j], r[2 * j + 1]), sc2, nss2);
-          float d0, d1;
-          upk2(mul2(unpack2<kBf16>(wp[hf * 16 + j]), t), d0, d1);
-          if (hf == 1 && j == 15 && kind == 2) d1 = lm_ds;
-          wd[hf * 16 + j] = pack2<kBf16>(d0, d1);
-        }
-      }
-    }
     wait_dst();
     store_row_sw128(p_dst, row, wp);
     between_stores();   // the P tile and the dS tile are handed over separately
     store_row_sw128(ds_dst, row, wd);
   } else {
     wait_dst();
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      uint32_t wd[16];
-      if (kind == 0) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) wd[j] = 0u;
-      } else {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tdp + hf * 32, r);
-        tmem_ld_wait();
-        if (hf == 1) {
-          tc_fence_before();
-          mbar_arrive(free_bar);
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const uint64_t t = fma2(pk2u(r[2 * j], r[2 * j + 1]), sc2, nss2);
-          float d0, d1;
-          upk2(mul2(sp[hf * 16 + j], t), d0, d1);
-          if (hf == 1 && j == 15 && kind == 2) d1 = lm_ds;
-          wd[j] = pack2<kBf16>(d0, d1);
-        }
-      }
-      store_half_row_sw128(ds_dst, row, hf, wd);
-    }
-  }
-  if (kind == 0) {
-    tc_fence_before();
-    mbar_arrive(free_bar);
+    store_row_sw128(ds_dst, row, wd);
   }
 }
 
@@ -1091,11 +1060,19 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const int pair = w / BH, bh = w - pair * BH;
       const int n = 2 * pair + g;
       const int tq0 = unit_tq0(pair), n_items = n_tiles - tq0;
+      // the row statistics of the next item are fetched one item ahead, so their latency is never exposed
+      const int64_t grow0 = (int64_t)bh * Lq + tq0 * kQTile + row;
+      float nM = M_ptr[grow0], nL = L_ptr[grow0], nDelta = delta_ptr[grow0];
       for (int i = 0; i < n_items; ++i, ++it) {
         const int tq = tq0 + i;
         const int own = prefix_blocks + 2 * tq + half;
-        const int64_t grow = (int64_t)bh * Lq + tq * kQTile + row;
-        const float M2L = fmaf(M_ptr[grow], kLog2e, __log2f(L_ptr[grow])), delta = delta_ptr[grow];
+        const float M2L = fmaf(nM, kLog2e, __log2f(nL)), delta = nDelta;
+        if (i + 1 < n_items) {
+          const int64_t grow = (int64_t)bh * Lq + (tq + 1) * kQTile + row;
+          nM = M_ptr[grow];
+          nL = L_ptr[grow];
+          nDelta = delta_ptr[grow];
+        }
         mbar_wait(smem_u32(&sm->s_full), it & 1, &g_lmk_status, kErrDkvSoftmax);
         tc_fence_after();
         const int kind = n > own ? 0 : (n == own ? 1 : 2);
