@@ -11,19 +11,23 @@
 //      accumulator in TMEM is never rescaled.
 //   2. Main loop over key blocks n = own0+1 ... 0:  S = Q . K_n^T (N = 64);  the softmax threads read S from TMEM,
 //      form the block's weights  p_j = softmax_inside_block(s)_j * exp(l_n - m)  (own block: exp(s_j - m), causal),
-//      write them as bf16 into the shared-memory slot the K block just vacated (128-byte swizzled, K-major), and
-//      O += P . V_n runs with V as an MN-major operand straight from its row-major TMA tile.
+//      write them as bf16 into shared memory (128-byte swizzled, K-major), and O += P . V_n runs with V as an
+//      MN-major operand straight from its row-major TMA tile.
 //   3. Epilogue: O / l -> global, plus the statistics L = l, M = m the backward pass needs.
+// When Lq is a multiple of 256 the paired kernel (sm100_fwd2_kernel) runs instead: two query tiles per CTA share every
+// K/V tile, each with its own softmax warpgroup; P goes back into the TMEM columns its S came from and P . V takes it
+// from there as the A operand (no shared-memory round trip); the exponentials are packed fp32 pairs, a quarter of them
+// evaluated on the FMA pipe.
 // Reference semantics: llama/ltriton/flash_landmark_attention.py:6-122.
 //
 // Backward is recompute-based and atomic-free (bit-reproducible), in two launches:
-//   a. dQ (sm100_bwd_dq_kernel): one CTA per (128 query rows, batch*head).  Its prologue computes
+//   a. dQ (sm100_bwd_dq_kernel): persistent; a unit is (128 query rows, batch*head).  Its prologue computes
 //      delta = rowsum(O * dO) from the O and dO tiles (:125-149, without the 1/L pre-scaling) and stores it for (b).
 //      Then, per key block: S = Q K^T, dP = dO V^T -> dS (written over the V tile, which dP no longer needs) ->
 //      dQ += dS K with K as an MN-major operand.  Two softmax warpgroups take alternate blocks.
 //   b. dK/dV (sm100_bwd_dkv_kernel): persistent; a unit is a pair of adjacent key blocks of one head, held in shared
-//      memory while the query tiles that see them stream through.  Per tile and block: S, dP into TMEM; the softmax
-//      threads rebuild P and dS (bf16, [128 q x 64 k] swizzled tiles); dV^T += dO^T P and dK^T += Q^T dS accumulate
+//      memory while the query tiles that see them stream through.  Per tile: S, dP of both blocks into TMEM (N = 128);
+//      the softmax threads rebuild P and dS (bf16, [128 q x 64 k] swizzled tiles); dV^T += dO^T P and dK^T += Q^T dS accumulate
 //      TRANSPOSED ([128 features x 64 keys], M = 128) so that every MMA keeps the full 128-lane shape; dO, Q, P and dS
 //      are consumed as MN-major operands from their row-major tiles.
 //   Per tile pair: earlier block  dS_j = g s_j (dP_j - nD) scale,  dS_landmark = g (nD - delta) scale,  P_j = g s_j,
@@ -370,7 +374,7 @@ sm100_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 // (rows 256u .. 256u+127), warpgroup 1 owns tile B (the next 128 rows).  Both tiles consume the same K/V stream, so
 // every K/V block is fetched from L2 once per 256 query rows, and the two softmax pipelines overlap with each
 // other and with the MMAs.  Tile A skips the two newest key blocks (they lie after its own blocks).
-constexpr int kFwd2Stages = 4;
+constexpr int kFwd2Stages = 5;
 constexpr int kFwd2Threads = 352;
 enum { kErrFwd2Producer = 111, kErrFwd2Mma = 112, kErrFwd2Softmax = 113, kErrFwd2Epilogue = 114 };
 
@@ -386,7 +390,6 @@ struct Fwd2Smem {
   uint64_t s_full[2][2];    // [tile][S buffer]
   uint64_t s_free[2][2];
   uint64_t p_ready[2];
-  uint64_t p_free[2];
   uint64_t o_full;
   uint32_t tmem_base;
 };
@@ -403,8 +406,7 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   auto q_tile = [&](int w) { return base + (uint32_t)w * 32768u; };
   auto k_slot = [&](int s) { return base + 65536u + (uint32_t)s * 32768u; };
   auto v_slot = [&](int s) { return base + 65536u + (uint32_t)s * 32768u + 16384u; };
-  auto p_tile = [&](int w) { return base + 65536u + kFwd2Stages * 32768u + (uint32_t)w * 16384u; };
-  Fwd2Smem* sm = reinterpret_cast<Fwd2Smem*>(smem_raw + (base - raw) + 65536u + kFwd2Stages * 32768u + 32768u);
+  Fwd2Smem* sm = reinterpret_cast<Fwd2Smem*>(smem_raw + (base - raw) + 65536u + kFwd2Stages * 32768u);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_pairs = Lq / (2 * kQTile);
@@ -427,10 +429,9 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int w = 0; w < 2; ++w) {
       for (int s = 0; s < 2; ++s) {
         mbar_init(smem_u32(&sm->s_full[w][s]), 1);
-        mbar_init(smem_u32(&sm->s_free[w][s]), 128);
+        mbar_init(smem_u32(&sm->s_free[w][s]), 1);
       }
       mbar_init(smem_u32(&sm->p_ready[w]), 128);
-      mbar_init(smem_u32(&sm->p_free[w]), 1);
     }
     mbar_init(smem_u32(&sm->o_full), 1);
     mbar_init_fence();
@@ -514,7 +515,6 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       constexpr uint32_t fmt = kBf16 ? 1u : 0u;
       constexpr uint32_t idesc_o = instr_desc_f16(fmt, 128, 128, 0, 1);
       const uint64_t dv0 = smem_desc_sw128(v_slot(0), kHalfTile, 1024);
-      const uint64_t dp0 = smem_desc_sw128(p_tile(0), 16, 1024);
       int kp[2] = {0, 0};
       bool o_started[2] = {false, false};
       int s = 0;
@@ -527,14 +527,16 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           mbar_wait(smem_u32(&sm->p_ready[w]), k & 1, &g_lmk_status, kErrFwd2Mma);
           tc_fence_after();
           if (i >= n_lm_tiles) {
-            const uint64_t dp = desc_advance(dp0, (uint32_t)w * 16384u);
+            // A = P straight from TMEM: the softmax threads wrote it over the first 32 columns of the S buffer it was
+            // computed from (8 columns = 16 keys per K-step)
+            const uint32_t tp = tmem_s(w, k & 1);
 #pragma unroll
             for (int kk = 0; kk < kBlk / 16; ++kk)
-              mma_f16_ss(tmem_o(w), desc_advance(dp, kk * 32), desc_advance(dv, kk * 2048), idesc_o,
+              mma_f16_ts(tmem_o(w), tp + kk * 8, desc_advance(dv, kk * 2048), idesc_o,
                          (o_started[w] || kk > 0) ? 1u : 0u);
             o_started[w] = true;
           }
-          mma_commit(smem_u32(&sm->p_free[w]));
+          mma_commit(smem_u32(&sm->s_free[w][k & 1]));      // the S / P buffer may take the next S product
         }
         // the stage is free once both P V products are done; each of them waited for its S product to be read
         mma_commit(smem_u32(&sm->empty[s]));
@@ -570,8 +572,6 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           sv[32 + j] = __uint_as_float(rb[j]);
         }
       }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&sm->s_free[w][sb]));
       uint32_t wgt[32];
       bool write_p = false;
       if (i < n_lm_tiles) {
@@ -626,11 +626,11 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
       }
-      if (k > 0) mbar_wait(smem_u32(&sm->p_free[w]), (k - 1) & 1, &g_lmk_status, kErrFwd2Softmax);
       if (write_p) {
-        store_row_sw128(p_tile(w), row, wgt);
-        fence_proxy_async_smem();
+        tmem_st_32x32b_x32(tmem_s(w, sb) + lane_base, wgt);     // P replaces S in place; the P V product reads it there
+        tmem_st_wait();
       }
+      tc_fence_before();
       mbar_arrive(smem_u32(&sm->p_ready[w]));
       ++k;
     }
@@ -667,24 +667,12 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------------------------- backward
-// One (query row, key block) pair of the backward pass, staged to keep the softmax threads below 168 registers
-// (so that two softmax warpgroups fit): S is read once, dP twice (once to reduce nD = sum_j s_j dP_j, once to form dS),
-// and each result row is stored as soon as it is complete.
+// One (query row, key block) pair of the backward pass, in packed fp32 pairs and within 168 registers per thread (so
+// that two softmax warpgroups fit next to the three single-thread roles).
 //   kind 0: block after the row's own block -> zeros;  kind 1: own block (causal, landmark hidden);
 //   kind 2: earlier block (grouped).
 // Writes the P row (kNeedP) into p_dst and the dS row into ds_dst ([128 x 64] 128B-swizzled tiles), arrives on
 // `free_bar` once the TMEM buffer has been read for the last time, and calls wait_dst() before the first store.
-__device__ __forceinline__ void store_half_row_sw128(uint32_t tile_base, int row, int half, const uint32_t (&w)[16]) {
-  const uint32_t row_addr = tile_base + row * 128;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint32_t addr = row_addr + (((half * 4 + c) ^ (row & 7)) << 4);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * c]), "r"(w[4 * c + 1]),
-                 "r"(w[4 * c + 2]), "r"(w[4 * c + 3])
-                 : "memory");
-  }
-}
-
 struct NoHook {
   __device__ __forceinline__ void operator()() const {}
 };
@@ -1474,7 +1462,7 @@ int attn_sm100_fwd(const AttnParams& p, int dtype, cudaStream_t st) {
   if ((rc = make_map_landmarks(&tl, p.k, dtype, p.B, p.H, p.Lk, p.ks, lm_box)) != LMK_OK) return rc;
   const float scale_log2 = p.scale * kLog2e;
   if (p.Lq % (2 * kQTile) == 0) {
-    const size_t smem = 1024 + 65536 + kFwd2Stages * 32768 + 32768 + sizeof(Fwd2Smem);
+    const size_t smem = 1024 + 65536 + kFwd2Stages * 32768 + sizeof(Fwd2Smem);
     dim3 grid(p.B * p.H, p.Lq / (2 * kQTile));
     if (dtype == LMK_BF16) {
       LMK_CUDA(cudaFuncSetAttribute(sm100_fwd2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
