@@ -302,7 +302,8 @@ def run_ours(args, world, rank, local):
 
 def bench_retrieval(P, L, dev, peaks):
     """Attention part of one layer of long-context retrieval (LLaMA-7B head shape): landmark scores, per-(head, token)
-    top-4 of 1024 cached blocks, gather of the selected KV blocks with rotary.  tok/s = raw tokens / (layers * time)."""
+    top-4 of 1024 cached blocks, then the selected blocks either gathered with rotary into dense copies (what the
+    reference does) or read in place by the fused logits / weighted-sum kernels.  tok/s = raw tokens / (layers * time)."""
     r = RETRIEVAL
     H, D, C, blk, T, top_k = r["H"], r["D"], r["cache_len"], r["block"], r["chunk"], r["top_k"]
     g = torch.Generator().manual_seed(7)
@@ -315,49 +316,75 @@ def bench_retrieval(P, L, dev, peaks):
     desc = L.CacheDesc(st[0], st[1], st[2] * blk, st[2], nblk, 0, blk, top_k, C - (top_k + 1) * blk)
     ev = lambda: torch.cuda.Event(enable_timing=True)
     flush = torch.empty(384 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    times = {"scores": [], "topk": [], "gather": []}
+    names = ["scores", "topk", "gather", "attend_gathered", "selected_logits", "selected_pv"]
+    times = {n: [] for n in names}
+    logits = torch.empty((1, H, T, top_k * blk), dtype=torch.bfloat16, device=dev)
+    stages = [
+        lambda c: c.update(scores=P.landmark_scores(q, pk, desc, cos, sin, L.ROTARY_HALF)),
+        lambda c: c.update(sel=P.topk_sorted(c["scores"], top_k)),
+        lambda c: c.update(kv=P.gather_kv(pk, pv, desc, desc, c["sel"], cos, sin, L.ROTARY_HALF)),
+        # what the reference then does with the copies (llama/llama_mem.py:399-404, 468-474): two batched matmuls
+        lambda c: c.update(ref_out=torch.matmul(
+            (torch.matmul(q.unsqueeze(3), c["kv"][0].transpose(3, 4)) * (D ** -0.5)).softmax(-1), c["kv"][1])),
+        lambda c: P.selected_logits(q, pk, desc, c["sel"], logits, 0, cos, sin, L.ROTARY_HALF),
+        lambda c: c.update(out=P.selected_pv(c["probs"], pv, desc, c["sel"])),
+    ]
     # each stage is captured through the public API into its own CUDA graph (the eager calls are launch-bound)
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
-    graphs = []
+    graphs, ctx = [], {}
     with torch.cuda.stream(side):
-        scores = P.landmark_scores(q, pk, desc, cos, sin, L.ROTARY_HALF)
-        sel = P.topk_sorted(scores, top_k)
-        P.gather_kv(pk, pv, desc, desc, sel, cos, sin, L.ROTARY_HALF)
+        for i, fn in enumerate(stages):
+            if i == 5:
+                ctx["probs"] = torch.softmax(logits.float(), dim=-1).to(torch.bfloat16)
+            fn(ctx)
         torch.cuda.synchronize()
-        g1 = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g1, stream=side):
-            scores = P.landmark_scores(q, pk, desc, cos, sin, L.ROTARY_HALF)
-        g2 = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g2, pool=g1.pool(), stream=side):
-            sel = P.topk_sorted(scores, top_k)
-        g3 = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g3, pool=g1.pool(), stream=side):
-            sk, sv = P.gather_kv(pk, pv, desc, desc, sel, cos, sin, L.ROTARY_HALF)
-        graphs = [g1, g2, g3]
+        pool = None
+        for fn in stages:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, pool=pool, stream=side):
+                fn(ctx)
+            pool = gr.pool()
+            graphs.append(gr)
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
     for it in range(8):
-        flush.zero_()
-        e = [ev() for _ in range(4)]
-        e[0].record()
-        for gi, gr in enumerate(graphs):
+        e = []
+        for gr in graphs:        # L2 is flushed before every stage: each one starts from HBM
+            flush.zero_()
+            a, b = ev(), ev()
+            a.record()
             gr.replay()
-            e[gi + 1].record()
+            b.record()
+            e.append((a, b))
         torch.cuda.synchronize()
         if it >= 3:
-            for name, (a, b) in zip(times, ((e[0], e[1]), (e[1], e[2]), (e[2], e[3]))):
-                times[name].append(a.elapsed_time(b))
+            for n, (a, b) in zip(names, e):
+                times[n].append(a.elapsed_time(b))
     ms = {k: statistics.fmean(v) for k, v in times.items()}
-    total_ms = sum(ms.values())
+    ms_mat = ms["scores"] + ms["topk"] + ms["gather"]
+    ms_mat_attend = ms_mat + ms["attend_gathered"]
+    ms_fused = ms["scores"] + ms["topk"] + ms["selected_logits"] + ms["selected_pv"]
     gather_bytes = 2 * 2 * H * T * top_k * blk * D * 2          # K and V, read + write
     gbs = gather_bytes / (ms["gather"] * 1e-3) / 1e9
+    sel = ctx["sel"]
+    uniq = sum(int(torch.unique(sel[0, h]).numel()) for h in range(H))
+    fused_bytes = 2 * uniq * blk * D * 2                        # every selected block of K and V once
+    fused_gbs = fused_bytes / ((ms["selected_logits"] + ms["selected_pv"]) * 1e-3) / 1e9
+    tok = lambda t_ms: r["raw_tokens"] / (r["layers"] * t_ms * 1e-3)
     return {"retrieval": {
-        "metric": "retrieval attention-side tok/s (scores + top-k + gather, 32 layers)",
-        "value": r["raw_tokens"] / (r["layers"] * total_ms * 1e-3), "unit": "tok/s", "ms_per_layer": ms,
-        "config": {"workload": "H=32 D=128 cache 32768 tokens in blocks of 32, chunk 258, top-k 4 per (head, token)"},
+        "metric": "retrieval attention-side tok/s (scores + top-k + selected-block logits and value sums, 32 layers)",
+        "value": tok(ms_fused), "unit": "tok/s", "ms_per_layer": ms,
+        "value_materialized_gather": tok(ms_mat),                 # data movement only, no logits / value sums
+        "value_materialized_gather_and_attend": tok(ms_mat_attend),  # like for like with `value`
+        "config": {"workload": "H=32 D=128 cache 32768 tokens in blocks of 32, chunk 258, top-k 4 per (head, token)",
+                   "l2": "flushed before every stage"},
         "roofline": {"bound": "hbm", "kernel": "gather_kv", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]}}}
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]},
+        "roofline_fused": {"bound": "hbm", "kernel": "selected_logits + selected_pv", "achieved": fused_gbs,
+                           "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": fused_gbs / peaks["hbm_gbs"],
+                           "algorithmic_bytes": fused_bytes, "unique_blocks": uniq,
+                           "peak_source": peaks["source"]}}}
 
 
 def main():
@@ -367,12 +394,20 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-retrieval", action="store_true")
+    ap.add_argument("--retrieval-only", action="store_true",
+                    help="run only the long-context retrieval stages on one GPU and print their JSON object")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     world, rank, local = dist_setup(args.gpus, cpu_only=args.impl == "reference")
     try:
         if args.impl == "reference":
             run_reference(args, world, rank)
+        elif args.retrieval_only:
+            if rank == 0:
+                import landmark_attention_b200 as P
+                from landmark_attention_b200 import _lib as L
+                torch.cuda.set_device(local)
+                print(json.dumps(bench_retrieval(P, L, torch.device("cuda", local), measured_peaks())), flush=True)
         else:
             run_ours(args, world, rank, local)
     finally:

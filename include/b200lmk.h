@@ -218,6 +218,24 @@ int lmk_gather_kv(const void* k_cache, const void* v_cache, const lmk_cache_desc
                   const void* cos_table, const void* sin_table, int n_pos, int rotary,
                   void* k_out, void* v_out, int B, int H, int T, int D, int dtype, void* stream);
 
+/*
+ * Attention over the selected blocks without materialising the gather (the two matmuls of
+ * llama/llama_mem.py:399-404 and :468-474 fused with the gather + rotary of :386-398): the blocks are read in place.
+ *   lmk_selected_logits: logits[b,h,t, col0 + i*block + r] = sm_scale * q[b,h,t,:] . rot(K[idx[b,h,t,i], r, :]),
+ *     q dense [B,H,T,D] already rotated; keys rotated at the slot positions and with the rounding steps of
+ *     lmk_gather_kv, the dot product accumulated in fp32; D * sizeof(dtype) must be 64, 128, 256 or 512 bytes;
+ *     logits in `dtype`, row stride `ld` elements, so the caller can point it into the buffer that also holds the
+ *     local keys' logits.
+ *   lmk_selected_pv: out[b,h,t,:] = sum_{i,r} probs[b,h,t, col0 + i*block + r] * V[idx[b,h,t,i], r, :];
+ *     probs in `dtype` with row stride `ld`; out dense [B,H,T,D] in `dtype`, fp32 accumulation.
+ */
+int lmk_selected_logits(const void* q, const void* k_cache, const lmk_cache_desc* kdesc, const int32_t* idx,
+                        const void* cos_table, const void* sin_table, int n_pos, int rotary, void* logits,
+                        int64_t ld, int64_t col0, int B, int H, int T, int D, float sm_scale, int dtype,
+                        void* stream);
+int lmk_selected_pv(const void* probs, int64_t ld, int64_t col0, const void* v_cache, const lmk_cache_desc* vdesc,
+                    const int32_t* idx, void* out, int B, int H, int T, int D, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -11,4 +11,4 @@ from .grouped_softmax import (landmark_grouped_softmax, landmark_grouped_softmax
                               lm_landmark_attention, prepare_landmark_masks)
 from .mem_cache import MemLMCache, MemLMCacheStorage  # noqa: F401
 from .retrieval import (gather_kv, landmark_scores, llama_retrieval_attention, make_desc,  # noqa: F401
-                        rotary_tables_half, rotary_tables_interleaved, topk_sorted)
+                        rotary_tables_half, rotary_tables_interleaved, selected_logits, selected_pv, topk_sorted)

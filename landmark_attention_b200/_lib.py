@@ -58,6 +58,11 @@ PROTOTYPES = {
     "lmk_gather_kv": (c_int, [c_void_p, c_void_p, POINTER(CacheDesc), POINTER(CacheDesc), c_void_p, c_void_p,
                               c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                               c_void_p]),
+    "lmk_selected_logits": (c_int, [c_void_p, c_void_p, POINTER(CacheDesc), c_void_p, c_void_p, c_void_p, c_int,
+                                    c_int, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_float, c_int,
+                                    c_void_p]),
+    "lmk_selected_pv": (c_int, [c_void_p, c_int64, c_int64, c_void_p, POINTER(CacheDesc), c_void_p, c_void_p, c_int,
+                                c_int, c_int, c_int, c_int, c_void_p]),
 }
 
 _lib = None

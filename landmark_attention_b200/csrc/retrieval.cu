@@ -263,6 +263,215 @@ __global__ void __launch_bounds__(128) gather_kv_kernel(const T* __restrict__ kc
   }
 }
 
+// ------------------------------------------------------------------------------------------- selected-block attention
+// The two halves of attention over the selected blocks WITHOUT materialising the gather: logits of a query against
+// the keys of its selected blocks (rotated at their slot positions, with the rounding steps of the gather kernel), and
+// the probability-weighted sum of the selected value rows.  Blocks are read in place from the cache, so a block
+// selected by many tokens of a head is served from L2 and nothing of size [B,H,T,top_k*block,D] is ever written.
+//
+// One CTA per (token t, batch*head); warp w takes selected blocks w, w+4, ...  A row of D elements is spread over
+// LPR = D / VEC lanes (16 bytes each, so every load instruction covers whole rows, fully coalesced) and a warp handles
+// 32 / LPR rows per step; the LPR partial dot products are combined with shuffles.
+template <typename T, int VEC>
+__device__ __forceinline__ void load_vec_f32(const T* p, float (&o)[VEC]) {
+  struct __align__(16) Vec { T v[VEC]; };
+  const Vec x = *reinterpret_cast<const Vec*>(p);
+#pragma unroll
+  for (int u = 0; u < VEC; ++u) o[u] = to_f32(x.v[u]);
+}
+
+// 16-bit types: the rotation x * cos + p * sin runs on packed pairs with the rounding steps of the gather kernel
+// (each product and the sum rounded to the 16-bit type, as the reference's tensor arithmetic does), which takes a
+// third of the instructions of converting everything to fp32 first; the dot product accumulates in fp32.
+#ifndef LMK_SEL_MINB
+#define LMK_SEL_MINB 8
+#endif
+template <typename T> struct Packed;      // arithmetic on two 16-bit values held in one 32-bit register
+template <> struct Packed<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
+  static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
+  static __device__ __forceinline__ void to_f32(uint32_t w, float& lo, float& hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+  }
+};
+template <> struct Packed<__half> {
+  static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
+  static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
+  static __device__ __forceinline__ void to_f32(uint32_t w, float& lo, float& hi) {
+    asm("{\n\t.reg .f16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}"
+        : "=f"(lo), "=f"(hi) : "r"(w));
+  }
+};
+template <> struct Packed<float> {};
+__device__ __forceinline__ void ld16(const void* p, uint32_t (&w)[4]) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+}
+
+template <typename T, int LPR>
+__global__ void __launch_bounds__(128, LMK_SEL_MINB) selected_logits_kernel(const T* __restrict__ q, const T* __restrict__ kc,
+                                                              lmk_cache_desc kd, const int32_t* __restrict__ idx,
+                                                              const T* __restrict__ cos_t, const T* __restrict__ sin_t,
+                                                              int n_pos, int rotary, T* __restrict__ logits,
+                                                              int64_t ld, int64_t col0, int H, int Tq, float scale) {
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int D = LPR * VEC, HALF = D / 2, RPS = 32 / LPR;
+  const int t = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / H, h = bh - b * H;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane % LPR, rsub = lane / LPR, d0 = sub * VEC;
+  const int blk = kd.block, N = kd.n_blocks, top_k = kd.top_k;
+  float qv[VEC];
+  load_vec_f32<T, VEC>(q + ((int64_t)bh * Tq + t) * D + d0, qv);
+#pragma unroll
+  for (int u = 0; u < VEC; ++u) qv[u] *= scale;
+  const bool lo = d0 < HALF;
+  const int dpart = lo ? d0 + HALF : d0 - HALF;
+  const int32_t* idx_row = idx + ((int64_t)bh * Tq + t) * top_k;
+  const T* kbase = kc + b * kd.stride_b + h * kd.stride_h;
+  for (int i = warp; i < top_k; i += 4) {
+    const int sel = idx_row[i];
+    const bool recent = logical_age(sel, kd.ring_start, N) >= N - top_k;
+    const int pos0 = kd.pos_base + (i + (recent ? 1 : 0)) * blk;
+    const T* ksrc = kbase + (int64_t)sel * kd.stride_block;
+#pragma unroll 2
+    for (int r0 = 0; r0 < blk; r0 += RPS) {
+      const int r = r0 + rsub;
+      float acc0 = 0.f, acc1 = 0.f;
+      if (r < blk) {
+        const T* krow = ksrc + (int64_t)r * kd.stride_row;
+        const int pos = max(0, min(pos0 + r, n_pos - 1));
+        if constexpr (sizeof(T) == 2) {
+          uint32_t x[4], y[4], c[4], sn[4];
+          ld16(krow + d0, x);
+          if (rotary == LMK_ROTARY_NONE) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              float f0, f1;
+              Packed<T>::to_f32(x[u], f0, f1);
+              acc0 = fmaf(qv[2 * u], f0, acc0);
+              acc1 = fmaf(qv[2 * u + 1], f1, acc1);
+            }
+          } else {
+            ld16(cos_t + (int64_t)pos * D + d0, c);
+            ld16(sin_t + (int64_t)pos * D + d0, sn);
+            if (rotary == LMK_ROTARY_HALF) {
+              ld16(krow + dpart, y);                                   // partner half of the same row (an L1 hit)
+              const uint32_t flip = lo ? 0x80008000u : 0u;             // rotate_half: -x[d + D/2] for the low half
+#pragma unroll
+              for (int u = 0; u < 4; ++u) y[u] ^= flip;
+            } else {
+#pragma unroll
+              for (int u = 0; u < 4; ++u) y[u] = __byte_perm(x[u], x[u], 0x1032) ^ 0x00008000u;   // (-x1, x0)
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              float f0, f1;
+              Packed<T>::to_f32(Packed<T>::add(Packed<T>::mul(x[u], c[u]), Packed<T>::mul(y[u], sn[u])), f0, f1);
+              acc0 = fmaf(qv[2 * u], f0, acc0);
+              acc1 = fmaf(qv[2 * u + 1], f1, acc1);
+            }
+          }
+        } else {
+          float x[VEC];
+          load_vec_f32<T, VEC>(krow + d0, x);
+          if (rotary == LMK_ROTARY_NONE) {
+#pragma unroll
+            for (int u = 0; u < VEC; ++u) acc0 = fmaf(qv[u], x[u], acc0);
+          } else {
+            float c[VEC], sn[VEC];
+            load_vec_f32<T, VEC>(cos_t + (int64_t)pos * D + d0, c);
+            load_vec_f32<T, VEC>(sin_t + (int64_t)pos * D + d0, sn);
+            if (rotary == LMK_ROTARY_HALF) {
+              float y[VEC];
+              load_vec_f32<T, VEC>(krow + dpart, y);
+#pragma unroll
+              for (int u = 0; u < VEC; ++u)
+                acc0 = fmaf(qv[u], __fadd_rn(__fmul_rn(x[u], c[u]), __fmul_rn(lo ? -y[u] : y[u], sn[u])), acc0);
+            } else {
+#pragma unroll
+              for (int u = 0; u < VEC; u += 2) {
+                acc0 = fmaf(qv[u], __fadd_rn(__fmul_rn(x[u], c[u]), __fmul_rn(-x[u + 1], sn[u])), acc0);
+                acc1 = fmaf(qv[u + 1], __fadd_rn(__fmul_rn(x[u + 1], c[u + 1]), __fmul_rn(x[u], sn[u + 1])), acc1);
+              }
+            }
+          }
+        }
+      }
+      float acc = acc0 + acc1;
+#pragma unroll
+      for (int o = LPR / 2; o >= 1; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (sub == 0 && r < blk)
+        logits[((int64_t)bh * Tq + t) * ld + col0 + (int64_t)i * blk + r] = from_f32<T>(acc);
+    }
+  }
+}
+
+// out[b,h,t,:] = sum over the selected rows j of probs[b,h,t,col0 + j] * V[row j].  One CTA per (t, batch*head):
+// 16-byte column vectors across the threads of a row group, row groups strided over the rows, fp32 partial sums
+// combined through shared memory.
+template <typename T>
+__global__ void __launch_bounds__(128) selected_pv_kernel(const T* __restrict__ probs, int64_t ld, int64_t col0,
+                                                          const T* __restrict__ vc, lmk_cache_desc vd,
+                                                          const int32_t* __restrict__ idx, T* __restrict__ out, int H,
+                                                          int Tq, int D) {
+  constexpr int VEC = 16 / sizeof(T);
+  struct __align__(16) Vec { T v[VEC]; };
+  extern __shared__ __align__(16) float sel_smem[];
+  const int t = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / H, h = bh - b * H;
+  const int blk = vd.block, top_k = vd.top_k, rows = top_k * blk;
+  float* ps = sel_smem;                       // [rows]
+  float* red = ps + ((rows + 3) & ~3);        // [row groups][D]
+  const T* pp = probs + ((int64_t)bh * Tq + t) * ld + col0;
+  for (int j = threadIdx.x; j < rows; j += blockDim.x) ps[j] = to_f32(pp[j]);
+  __syncthreads();
+  const int vec_per_row = D / VEC, groups = blockDim.x / vec_per_row;
+  const int vcol = threadIdx.x % vec_per_row, rg = threadIdx.x / vec_per_row;
+  float acc[VEC];
+#pragma unroll
+  for (int u = 0; u < VEC; ++u) acc[u] = 0.f;
+  const T* vbase = vc + b * vd.stride_b + h * vd.stride_h;
+  if (rg < groups) {
+    for (int i = 0; i < top_k; ++i) {
+      const int sel = idx[((int64_t)bh * Tq + t) * top_k + i];
+      const T* vsrc = vbase + (int64_t)sel * vd.stride_block + vcol * VEC;
+#pragma unroll 4
+      for (int r = rg; r < blk; r += groups) {
+        const Vec v = *reinterpret_cast<const Vec*>(vsrc + (int64_t)r * vd.stride_row);
+        const float p = ps[i * blk + r];
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) acc[u] = fmaf(p, to_f32(v.v[u]), acc[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) red[rg * D + vcol * VEC + u] = acc[u];
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float sum = 0.f;
+    for (int g = 0; g < groups; ++g) sum += red[g * D + d];
+    out[((int64_t)bh * Tq + t) * D + d] = from_f32<T>(sum);
+  }
+}
+
 int check_desc(const lmk_cache_desc* d, const char* what) {
   LMK_CHECK_ARG(d != nullptr, "%s: null cache descriptor", what);
   LMK_CHECK_ARG(d->block >= 1 && d->n_blocks >= 1, "%s: block %d / n_blocks %d must be positive", what, d->block,
@@ -394,6 +603,90 @@ extern "C" int lmk_gather_kv(const void* k_cache, const void* v_cache, const lmk
   else if (dtype == LMK_F16) LMK_GA_LAUNCH(__half);
   else LMK_GA_LAUNCH(__nv_bfloat16);
 #undef LMK_GA_LAUNCH
+  LMK_CUDA(cudaGetLastError());
+  return LMK_OK;
+}
+
+extern "C" int lmk_selected_logits(const void* q, const void* k_cache, const lmk_cache_desc* kdesc, const int32_t* idx,
+                                   const void* cos_table, const void* sin_table, int n_pos, int rotary, void* logits,
+                                   int64_t ld, int64_t col0, int B, int H, int T, int D, float sm_scale, int dtype,
+                                   void* stream) {
+  int rc = check_desc(kdesc, "selected_logits");
+  if (rc != LMK_OK) return rc;
+  LMK_CHECK_ARG(q && k_cache && idx && logits, "selected_logits: null pointer");
+  LMK_CHECK_ARG((((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)cos_table | (uintptr_t)sin_table) & 15) == 0,
+                "selected_logits: q, cache and rotary tables must be 16-byte aligned");
+  LMK_CHECK_ARG(dtype == LMK_F32 || dtype == LMK_F16 || dtype == LMK_BF16, "selected_logits: unknown dtype %d", dtype);
+  LMK_CHECK_ARG(B >= 0 && H >= 1 && T >= 0 && D >= 1, "selected_logits: bad shape");
+  const int vec = dtype == LMK_F32 ? 4 : 8;
+  const int lpr = D / vec;
+  LMK_CHECK_ARG(D % vec == 0 && (lpr == 4 || lpr == 8 || lpr == 16 || lpr == 32),
+                "selected_logits: D=%d must be 4, 8, 16 or 32 vectors of 16 bytes", D);
+  LMK_CHECK_ARG(kdesc->stride_row % vec == 0 && kdesc->stride_block % vec == 0 && kdesc->stride_h % vec == 0 &&
+                    kdesc->stride_b % vec == 0,
+                "selected_logits: cache strides must be multiples of %d elements", vec);
+  LMK_CHECK_ARG(rotary == LMK_ROTARY_NONE || (cos_table && sin_table && n_pos >= 1),
+                "selected_logits: rotary needs cos/sin tables");
+  LMK_CHECK_ARG(rotary == LMK_ROTARY_NONE || rotary == LMK_ROTARY_HALF || rotary == LMK_ROTARY_INTERLEAVED,
+                "selected_logits: unknown rotary mode %d", rotary);
+  LMK_CHECK_ARG(col0 >= 0 && ld >= col0 + (int64_t)kdesc->top_k * kdesc->block,
+                "selected_logits: row stride %lld too small for %d x %d columns at offset %lld", (long long)ld,
+                kdesc->top_k, kdesc->block, (long long)col0);
+  if (B == 0 || T == 0 || kdesc->top_k == 0) return LMK_OK;
+  LMK_CHECK_ARG((int64_t)B * H <= 65535, "selected_logits: grid too large");
+  dim3 grid(T, B * H);
+  cudaStream_t st = (cudaStream_t)stream;
+#define LMK_SL_LAUNCH(TT, LPR)                                                                                     \
+  selected_logits_kernel<TT, LPR><<<grid, 128, 0, st>>>((const TT*)q, (const TT*)k_cache, *kdesc, idx,            \
+                                                        (const TT*)cos_table, (const TT*)sin_table, n_pos, rotary, \
+                                                        (TT*)logits, ld, col0, H, T, sm_scale)
+#define LMK_SL_DISPATCH(TT)                     \
+  switch (lpr) {                                \
+    case 4: LMK_SL_LAUNCH(TT, 4); break;        \
+    case 8: LMK_SL_LAUNCH(TT, 8); break;        \
+    case 16: LMK_SL_LAUNCH(TT, 16); break;      \
+    default: LMK_SL_LAUNCH(TT, 32); break;      \
+  }
+  if (dtype == LMK_F32) { LMK_SL_DISPATCH(float) }
+  else if (dtype == LMK_F16) { LMK_SL_DISPATCH(__half) }
+  else { LMK_SL_DISPATCH(__nv_bfloat16) }
+#undef LMK_SL_DISPATCH
+#undef LMK_SL_LAUNCH
+  LMK_CUDA(cudaGetLastError());
+  return LMK_OK;
+}
+
+extern "C" int lmk_selected_pv(const void* probs, int64_t ld, int64_t col0, const void* v_cache,
+                               const lmk_cache_desc* vdesc, const int32_t* idx, void* out, int B, int H, int T, int D,
+                               int dtype, void* stream) {
+  int rc = check_desc(vdesc, "selected_pv");
+  if (rc != LMK_OK) return rc;
+  LMK_CHECK_ARG(probs && v_cache && idx && out, "selected_pv: null pointer");
+  LMK_CHECK_ARG(((uintptr_t)v_cache & 15) == 0, "selected_pv: the cache must be 16-byte aligned");
+  LMK_CHECK_ARG(dtype == LMK_F32 || dtype == LMK_F16 || dtype == LMK_BF16, "selected_pv: unknown dtype %d", dtype);
+  LMK_CHECK_ARG(B >= 0 && H >= 1 && T >= 0 && D >= 1, "selected_pv: bad shape");
+  const int vec = dtype == LMK_F32 ? 4 : 8;
+  LMK_CHECK_ARG(D % vec == 0 && D / vec <= 128 && 128 % (D / vec) == 0,
+                "selected_pv: D=%d must give a power-of-two number (<= 128) of 16-byte vectors per row", D);
+  LMK_CHECK_ARG(vdesc->stride_row % vec == 0 && vdesc->stride_block % vec == 0 && vdesc->stride_h % vec == 0 &&
+                    vdesc->stride_b % vec == 0,
+                "selected_pv: cache strides must be multiples of %d elements", vec);
+  const int64_t rows = (int64_t)vdesc->top_k * vdesc->block;
+  LMK_CHECK_ARG(col0 >= 0 && ld >= col0 + rows, "selected_pv: row stride %lld too small", (long long)ld);
+  if (B == 0 || T == 0) return LMK_OK;
+  LMK_CHECK_ARG((int64_t)B * H <= 65535, "selected_pv: grid too large");
+  const size_t smem = (size_t)(((rows + 3) & ~3) + (int64_t)(128 / (D / vec)) * D) * sizeof(float);
+  LMK_CHECK_ARG(smem <= 48 * 1024, "selected_pv: top_k * block = %lld rows do not fit in shared memory",
+                (long long)rows);
+  dim3 grid(T, B * H);
+  cudaStream_t st = (cudaStream_t)stream;
+#define LMK_SP_LAUNCH(TT)                                                                                       \
+  selected_pv_kernel<TT><<<grid, 128, smem, st>>>((const TT*)probs, ld, col0, (const TT*)v_cache, *vdesc, idx,  \
+                                                  (TT*)out, H, T, D)
+  if (dtype == LMK_F32) LMK_SP_LAUNCH(float);
+  else if (dtype == LMK_F16) LMK_SP_LAUNCH(__half);
+  else LMK_SP_LAUNCH(__nv_bfloat16);
+#undef LMK_SP_LAUNCH
   LMK_CUDA(cudaGetLastError());
   return LMK_OK;
 }

@@ -101,15 +101,54 @@ def gather_kv(k_cache, v_cache, kdesc, vdesc, idx, cos=None, sin=None, rotary=L.
     return k_out, v_out
 
 
+def selected_logits(q, k_cache, kdesc, idx, out, col0=0, cos=None, sin=None, rotary=L.ROTARY_NONE, sm_scale=None):
+    """Logits of each query against the keys of ITS selected blocks, read in place from the cache (no gathered copy):
+    out[b,h,t, col0 + i*block + r] = sm_scale * q[b,h,t] . rot(K[idx[b,h,t,i], r]).  `out` is a [B,H,T,W] tensor of
+    q's dtype that may be wider than top_k*block, so the logits of local keys can live in the same buffer.
+    Fuses llama/llama_mem.py:386-404 (gather, rotary at slot positions, q k^T)."""
+    L.require_cuda(q, k_cache, idx, out)
+    q = q.contiguous()
+    B, H, T, D = q.shape
+    assert idx.dtype == torch.int32 and idx.is_contiguous() and idx.shape == (B, H, T, kdesc.top_k)
+    assert out.dtype == q.dtype and out.shape[:3] == (B, H, T) and out.is_contiguous()
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    n_pos = 0 if cos is None else cos.shape[0]
+    rc = L.lib().lmk_selected_logits(L.ptr(q), L.ptr(k_cache), ctypes.byref(kdesc), L.ptr(idx), L.ptr(cos), L.ptr(sin),
+                                     n_pos, rotary, L.ptr(out), out.shape[3], col0, B, H, T, D, float(sm_scale),
+                                     L.dtype_code(q), L.stream_ptr(q.device))
+    L.check(rc, "lmk_selected_logits")
+    return out
+
+
+def selected_pv(probs, v_cache, vdesc, idx, col0=0, dim=None):
+    """sum_j probs[b,h,t, col0 + j] * V[selected row j] -> [B,H,T,D], the value rows read in place from the cache.
+    Fuses the gather with the p_prefix @ v matmul of llama/llama_mem.py:468-474."""
+    L.require_cuda(probs, v_cache, idx)
+    assert probs.is_contiguous() and probs.dtype == v_cache.dtype
+    B, H, T, W = probs.shape
+    D = dim if dim is not None else v_cache.shape[-1]
+    out = torch.empty((B, H, T, D), device=probs.device, dtype=probs.dtype)
+    rc = L.lib().lmk_selected_pv(L.ptr(probs), W, col0, L.ptr(v_cache), ctypes.byref(vdesc), L.ptr(idx), L.ptr(out),
+                                 B, H, T, D, L.dtype_code(probs), L.stream_ptr(probs.device))
+    L.check(rc, "lmk_selected_pv")
+    return out
+
+
 def llama_retrieval_attention(q, k_new, v_new, past_k, past_v, mem_freq, cache_top_k, position_ids=None,
-                              chunk_is_mem=None, cos=None, sin=None, return_debug=False):
+                              chunk_is_mem=None, cos=None, sin=None, return_debug=False, materialize=None):
     """Attention of one chunk against a landmark block cache, as LlamaAttention.forward does with
     `mem_freq`/`cache_top_k` set and use_flash=False (llama/llama_mem.py:296-298, 318-430, 447-474).
 
     q, k_new, v_new: [B,H,T,D] projections of the chunk BEFORE rotary; past_k/past_v: [B,H,C,D] un-rotated cache
     (:424,436).  chunk_is_mem: bool [1,T] landmark flags of the chunk (default: regular in absolute position).
+    materialize: True gathers the selected blocks into [B,H,T,top_k*block,D] copies as the reference does
+    (:386-398); False (default, unless return_debug asks for the copies) reads them in place with the fused
+    selected-block kernels.
     Returns (attn_output [B,H,T,D], new (past_k, past_v)).
     """
+    if materialize is None:
+        materialize = return_debug
     B, H, T, D = q.shape
     C = past_k.shape[2]
     block = mem_freq + 1
@@ -135,8 +174,11 @@ def llama_retrieval_attention(q, k_new, v_new, past_k, past_v, mem_freq, cache_t
     vdesc = L.CacheDesc(vst[0], vst[1], vst[2] * block, vst[2], num_mems, 0, block, top_k, prefix_len)
     scores = landmark_scores(qr, past_k, kdesc, cos, sin, L.ROTARY_HALF, scale)
     sel = topk_sorted(scores, top_k)
-    sel_k, sel_v = gather_kv(past_k, past_v, kdesc, vdesc, sel, cos, sin, L.ROTARY_HALF, dim=D)
-    prefix = torch.matmul(qr.unsqueeze(3), sel_k.transpose(3, 4)).squeeze(3) * scale      # [B,H,T,top_k*block]
+    n_pre = top_k * block
+    sel_k = sel_v = None
+    if materialize:
+        sel_k, sel_v = gather_kv(past_k, past_v, kdesc, vdesc, sel, cos, sin, L.ROTARY_HALF, dim=D)
+        prefix = torch.matmul(qr.unsqueeze(3), sel_k.transpose(3, 4)).squeeze(3) * scale      # [B,H,T,top_k*block]
 
     inc_pos = torch.arange(full, full + inc, device=dev)
     k_inc = apply_rotary_half(past_k[:, :, full:], cos, sin, inc_pos)
@@ -155,10 +197,18 @@ def llama_retrieval_attention(q, k_new, v_new, past_k, past_v, mem_freq, cache_t
                              torch.zeros(1, 1, T, inc, dtype=torch.bool, device=dev), is_mem_c), dim=-1)
     last_full = torch.cat((torch.zeros(1, 1, T, top_k * block, dtype=torch.bool, device=dev),
                            torch.ones(1, 1, T, inc, dtype=torch.bool, device=dev), last_c), dim=-1)
-    logits = torch.cat((prefix, local), dim=-1)
+    if materialize:
+        logits = torch.cat((prefix, local), dim=-1)
+    else:
+        logits = torch.empty((B, H, T, n_pre + local.shape[-1]), device=dev, dtype=q.dtype)
+        logits[..., n_pre:] = local
+        selected_logits(qr, past_k, kdesc, sel, logits, 0, cos, sin, L.ROTARY_HALF, scale)
     probs = landmark_grouped_softmax(logits, -1, is_mem_full, last_full).to(q.dtype)
-    p_prefix, p_local = probs[..., : top_k * block], probs[..., top_k * block:]
-    out = torch.matmul(p_local, vals) + torch.matmul(p_prefix.unsqueeze(3), sel_v).squeeze(3)
+    p_local = probs[..., n_pre:]
+    if materialize:
+        out = torch.matmul(p_local, vals) + torch.matmul(probs[..., :n_pre].unsqueeze(3), sel_v).squeeze(3)
+    else:
+        out = torch.matmul(p_local, vals) + selected_pv(probs.contiguous(), past_v, vdesc, sel, 0, dim=D)
     new_cache = (torch.cat((past_k, k_new), dim=2), torch.cat((past_v, v_new), dim=2))
     if return_debug:
         return out, new_cache, dict(scores=scores, sel=sel, sel_k=sel_k, sel_v=sel_v, probs=probs)

@@ -65,6 +65,15 @@ def test_retrieval_argument_checks():
     rc = lib.lmk_gather_kv(one, one, ctypes.byref(d), ctypes.byref(d), one, None, None, 0, L.ROTARY_HALF, one, one,
                            1, 1, 1, 64, L.LMK_BF16, None)
     assert rc == L.LMK_ERR_INVALID and b"rotary" in lib.lmk_last_error()
+    # fused selected-block attention: row stride too small for top_k * block columns at the offset; odd head dim
+    rc = lib.lmk_selected_logits(one, one, ctypes.byref(d), one, None, None, 0, L.ROTARY_NONE, one, 16, 4, 1, 1, 1, 64,
+                                 1.0, L.LMK_BF16, None)
+    assert rc == L.LMK_ERR_INVALID and b"row stride" in lib.lmk_last_error()
+    rc = lib.lmk_selected_logits(one, one, ctypes.byref(d), one, None, None, 0, L.ROTARY_NONE, one, 16, 0, 1, 1, 1, 24,
+                                 1.0, L.LMK_BF16, None)
+    assert rc == L.LMK_ERR_INVALID
+    assert lib.lmk_selected_pv(one, 8, 0, one, ctypes.byref(d), one, one, 1, 1, 1, 64, L.LMK_BF16, None) == L.LMK_ERR_INVALID
+    assert lib.lmk_selected_pv(one, 16, 0, one, ctypes.byref(d), None, one, 1, 1, 1, 64, L.LMK_BF16, None) == L.LMK_ERR_INVALID
 
 
 def test_python_wrappers_refuse_cpu_tensors():

@@ -85,13 +85,76 @@ def test_scores_and_gather_llama_layout(dtype):
     assert (sk.cpu().float() - O.rotary_half_split(ek.float(), kpos)).abs().max().item() < (1e-5 if dtype == torch.float32 else 4e-2)
 
 
+@pytest.mark.parametrize("materialize", [False, True])
 @pytest.mark.parametrize("name", ["llama_retr_blocks", "llama_retr_tail"])
-def test_llama_cache_branch_against_golden(golden, name):
+def test_llama_cache_branch_against_golden(golden, name, materialize):
+    # materialize=True gathers the selected blocks as the reference does; False reads them in place (fused kernels)
     g = golden(name + ".pt")
     out, _ = P.llama_retrieval_attention(g["q"].to(DEV), g["k"].to(DEV), g["v"].to(DEV), g["past_k"].to(DEV),
                                          g["past_v"].to(DEV), g["blk"] - 1, g["top_k"],
-                                         chunk_is_mem=g["is_mem_row"].to(DEV))
+                                         chunk_is_mem=g["is_mem_row"].to(DEV), materialize=materialize)
     assert (out.cpu() - g["out"]).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("rotary", ["half", "interleaved", "none"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_selected_block_kernels_match_gather_then_matmul(dtype, rotary):
+    # in-place logits / weighted value sums over the selected blocks == gather + rotary + matmul, on a ring-ordered
+    # cache with ragged block size (24 rows: lanes 24..31 idle), written at a column offset into a wider buffer
+    torch.manual_seed(5)
+    B, H, T, D, blk, nblk, top_k, ring = 2, 3, 9, 64, 24, 11, 3, 4
+    C = nblk * blk
+    q = torch.randn(B, H, T, D).to(dtype).to(DEV)
+    pk = torch.randn(B, H, C, D).to(dtype).to(DEV)
+    pv = torch.randn(B, H, C, D).to(dtype).to(DEV)
+    if rotary == "half":
+        cos, sin, mode = *P.rotary_tables_half(C + T + 1, D, dtype, DEV), L.ROTARY_HALF
+    elif rotary == "interleaved":
+        cos, sin, mode = *P.rotary_tables_interleaved(C + T + 1, D, dtype, DEV), L.ROTARY_INTERLEAVED
+    else:
+        cos, sin, mode = None, None, L.ROTARY_NONE
+    st = pk.stride()
+    desc = L.CacheDesc(st[0], st[1], st[2] * blk, st[2], nblk, ring, blk, top_k, C - (top_k + 1) * blk)
+    scores = torch.randn(B, H, T, nblk, device=DEV)
+    sel = P.topk_sorted(scores, top_k, ring_start=ring)
+    sk, sv = P.gather_kv(pk, pv, desc, desc, sel, cos, sin, mode)
+    scale = 0.3
+    exp_logits = torch.matmul(q.float().unsqueeze(3), sk.float().transpose(3, 4)).squeeze(3) * scale
+    col0, width = 5, top_k * blk + 12
+    buf = torch.full((B, H, T, width), 7.0, dtype=dtype, device=DEV)
+    P.selected_logits(q, pk, desc, sel, buf, col0, cos, sin, mode, scale)
+    got = buf[..., col0:col0 + top_k * blk].float()
+    tol = 1e-5 if dtype == torch.float32 else (6e-2 if dtype == torch.bfloat16 else 8e-3)
+    assert (got - exp_logits).abs().max().item() < tol
+    assert (buf[..., :col0] == 7).all() and (buf[..., col0 + top_k * blk:] == 7).all()       # nothing else touched
+    probs = torch.softmax(torch.randn(B, H, T, width, device=DEV), dim=-1).to(dtype)
+    out = P.selected_pv(probs, pv, desc, sel, col0)
+    exp_out = torch.matmul(probs[..., col0:col0 + top_k * blk].float().unsqueeze(3), sv.float()).squeeze(3)
+    assert (out.float() - exp_out).abs().max().item() < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+def test_selected_block_kernels_config4_shape():
+    # the long-context shape: D = 128, blocks of 32 rows, top-4 of 1024 blocks, one head group
+    torch.manual_seed(6)
+    B, H, T, D, blk, nblk, top_k = 1, 2, 64, 128, 32, 1024, 4
+    C = nblk * blk
+    dtype = torch.bfloat16
+    q = torch.randn(B, H, T, D).to(dtype).to(DEV)
+    pk = torch.randn(B, H, C, D).to(dtype).to(DEV)
+    pv = torch.randn(B, H, C, D).to(dtype).to(DEV)
+    cos, sin = P.rotary_tables_half(C + T + 1, D, dtype, DEV)
+    st = pk.stride()
+    desc = L.CacheDesc(st[0], st[1], st[2] * blk, st[2], nblk, 0, blk, top_k, C - (top_k + 1) * blk)
+    sel = P.topk_sorted(P.landmark_scores(q, pk, desc, cos, sin, L.ROTARY_HALF), top_k)
+    sk, sv = P.gather_kv(pk, pv, desc, desc, sel, cos, sin, L.ROTARY_HALF)
+    buf = torch.empty((B, H, T, top_k * blk), dtype=dtype, device=DEV)
+    P.selected_logits(q, pk, desc, sel, buf, 0, cos, sin, L.ROTARY_HALF)
+    exp = torch.matmul(q.float().unsqueeze(3), sk.float().transpose(3, 4)).squeeze(3) / math.sqrt(D)
+    assert (buf.float() - exp).abs().max().item() < 6e-2
+    probs = torch.softmax(buf.float(), dim=-1).to(dtype)
+    out = P.selected_pv(probs, pv, desc, sel)
+    exp_out = torch.matmul(probs.float().unsqueeze(3), sv.float()).squeeze(3)
+    assert (out.float() - exp_out).abs().max().item() < 2e-2
 
 
 def test_llama_cache_branch_selected_blocks_match_oracle():
