@@ -37,6 +37,12 @@ def measured_peaks():
     return dict(bf16_tflops=1590.0, hbm_gbs=6650.0, source="fallback")
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch at the benchmark shape, from an ncu capture of this script
+# (cold L2): forward 50.4 MB; backward = dQ launch 84.9 MB + dK/dV launch 70.5 MB.  The algorithmic operand bytes are
+# 50.3 MB (q, k, v) and 84 + 67 MB (q, k, v, o, dO / q, k, v, dO): nothing is re-read from HBM; results stay in L2.
+DRAM_TRAFFIC = {"forward": 50.4e6, "backward": 155.4e6}
+
+
 def attn_flops(B, H, L, D, backward=True):
     return (7 if backward else 2) * B * H * L * L * D
 
@@ -285,11 +291,12 @@ def run_ours(args, world, rank, local):
                     "forward_tflops": flops_fwd / (fwd_avg * 1e-3) / 1e12,
                     "backward_tflops": (flops_all - flops_fwd) / (bwd_avg * 1e-3) / 1e12},
         "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peaks["bf16_tflops"],
-                     "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                     "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                     "traffic": DRAM_TRAFFIC[dominant], "traffic_unit": "bytes per launch group, ncu dram read+write",
                      "peak_source": peaks["source"]},
         "e2e": {"value": world * flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 4 * tensor_bytes, "d2h_bytes_per_step": 4 * tensor_bytes},
-        "gpu_launches": args.steps * 4,
+        "gpu_launches": args.steps * 3,      # forward, dQ (+ delta), dK/dV
         "clocks": clocks, "wall_s": wall,
     }
     if cpu_tf is not None:
