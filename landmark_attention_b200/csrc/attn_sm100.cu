@@ -673,6 +673,11 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 //   kind 2: earlier block (grouped).
 // Writes the P row (kNeedP) into p_dst and the dS row into ds_dst ([128 x 64] 128B-swizzled tiles), arrives on
 // `free_bar` once the TMEM buffer has been read for the last time, and calls wait_dst() before the first store.
+#ifndef LMK_BWD_POLY_EVERY
+#define LMK_BWD_POLY_EVERY 4
+#endif
+constexpr int kBwdPolyEvery = LMK_BWD_POLY_EVERY;   // one in this many pairs of exponentials uses ex2_poly2
+
 struct NoHook {
   __device__ __forceinline__ void operator()() const {}
 };
@@ -744,9 +749,14 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
     const uint64_t n2 = pk2(nmx, nmx);
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-      float a, b;
-      upk2(fma2(sp[j], c2, n2), a, b);
-      sp[j] = pk2(ex2(a), j == 31 ? 0.f : ex2(b));
+      const uint64_t x = fma2(sp[j], c2, n2);
+      if (j % kBwdPolyEvery == 1) {
+        sp[j] = ex2_poly2(x);         // a share of the exponentials runs on the FMA pipe
+      } else {
+        float a, b;
+        upk2(x, a, b);
+        sp[j] = pk2(ex2(a), j == 31 ? 0.f : ex2(b));
+      }
     }
     s0 = sp[0], s1 = sp[1], s2 = sp[2], s3 = sp[3];
 #pragma unroll
@@ -1137,7 +1147,7 @@ struct DqSmem {
   uint64_t ds_ready[kDqStages];
   uint64_t sdp_full[kSdpBufs];
   uint64_t sdp_free[kSdpBufs];
-  uint64_t acc_full[2];     // per draining warpgroup (units alternate between them)
+  uint64_t acc_full[2];     // per draining warpgroup (the one that took the unit's last item)
   uint64_t acc_empty;
   uint32_t tmem_base;
 };
@@ -1286,7 +1296,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                        (i > 0 || kk > 0) ? 1u : 0u);
           mma_commit(smem_u32(&sm->empty[s]));
         }
-        mma_commit(smem_u32(&sm->acc_full[u & 1]));
+        mma_commit(smem_u32(&sm->acc_full[(it - 1) & 1]));     // drained by the warpgroup that took the last item
       }
     }
     __syncwarp();
@@ -1296,13 +1306,61 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int half = row >> 6;
     const int vis = min(row & 63, kBlk - 2);
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    int it0 = 0, u = 0;
+    int it0 = 0, u = 0, drains = 0;
+    // dQ of a unit is drained by the warpgroup that took its last item, but only after that warpgroup has done the
+    // prologue of the NEXT unit: the last dQ product queues behind the next unit's first S / dP products, so an
+    // immediate drain would just wait for it.  (The next unit's first dQ product needs its first dS, far later.)
+    int64_t drain_row = -1;
+    auto drain = [&]() {
+      mbar_wait(smem_u32(&sm->acc_full[g]), drains & 1, &g_lmk_status, kErrDqEpilogue);
+      ++drains;
+      tc_fence_after();
+      uint4* orow = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dq_ptr) + drain_row * kD);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_dq + c * 32 + lane_base, r);
+        tmem_ld_wait();
+        if (c == 3) {
+          tc_fence_before();
+          mbar_arrive(smem_u32(&sm->acc_empty));     // the next unit may start accumulating
+        }
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          uint4 pk;
+          pk.x = pack2<kBf16>(__uint_as_float(r[8 * v4 + 0]), __uint_as_float(r[8 * v4 + 1]));
+          pk.y = pack2<kBf16>(__uint_as_float(r[8 * v4 + 2]), __uint_as_float(r[8 * v4 + 3]));
+          pk.z = pack2<kBf16>(__uint_as_float(r[8 * v4 + 4]), __uint_as_float(r[8 * v4 + 5]));
+          pk.w = pack2<kBf16>(__uint_as_float(r[8 * v4 + 6]), __uint_as_float(r[8 * v4 + 7]));
+          orow[c * 4 + v4] = pk;
+        }
+      }
+      drain_row = -1;
+    };
+    // the row statistics of the next unit are fetched while the current one runs, so their latency is never exposed
+    float nM = 0.f, nL = 1.f;
+    {
+      const int w0 = unit_of(0);
+      if (w0 < n_units) {
+        const int64_t g0 = (int64_t)(w0 % BH) * Lq + unit_tile(w0) * kQTile + row;
+        nM = M_ptr[g0];
+        nL = L_ptr[g0];
+      }
+    }
     for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
       const int t = unit_tile(w), bh = w % BH;
       const int own = prefix_blocks + 2 * t + half;
       const int total = unit_items(t), n_last = total - 1;
       const int64_t grow = (int64_t)bh * Lq + t * kQTile + row;
-      const float M2L = fmaf(M_ptr[grow], kLog2e, __log2f(L_ptr[grow]));
+      const float M2L = fmaf(nM, kLog2e, __log2f(nL));
+      {
+        const int wn = unit_of(u + 1);
+        if (wn < n_units) {
+          const int64_t gn = (int64_t)(wn % BH) * Lq + unit_tile(wn) * kQTile + row;
+          nM = M_ptr[gn];
+          nL = L_ptr[gn];
+        }
+      }
       // delta = rowsum(O * dO), straight from the swizzled tiles (one row per thread, 16-byte chunks); warpgroup 0
       // also publishes it for the dK/dV kernel, which runs after this one
       mbar_wait(smem_u32(&sm->qdo_full), u & 1, &g_lmk_status, kErrDqSoftmax);
@@ -1333,6 +1391,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
       mbar_arrive(smem_u32(&sm->delta_read));
       if (g == 0) delta_ptr[grow] = delta;
+      if (drain_row >= 0) drain();
       for (int i = (it0 + g) & 1; i < total; i += kBwdGroups) {
         const int it = it0 + i;
         const int s = it % kDqStages, sb = it % kSdpBufs;
@@ -1348,31 +1407,9 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         mbar_arrive(smem_u32(&sm->ds_ready[s]));
       }
       it0 += total;
-      if (g == (u & 1)) {      // drain dQ of this unit; the other warpgroup moves on to the next unit
-        mbar_wait(smem_u32(&sm->acc_full[g]), (u >> 1) & 1, &g_lmk_status, kErrDqEpilogue);
-        tc_fence_after();
-        uint4* orow = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dq_ptr) + grow * kD);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_dq + c * 32 + lane_base, r);
-          tmem_ld_wait();
-          if (c == 3) {
-            tc_fence_before();
-            mbar_arrive(smem_u32(&sm->acc_empty));     // the next unit may start accumulating
-          }
-#pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            uint4 pk;
-            pk.x = pack2<kBf16>(__uint_as_float(r[8 * v4 + 0]), __uint_as_float(r[8 * v4 + 1]));
-            pk.y = pack2<kBf16>(__uint_as_float(r[8 * v4 + 2]), __uint_as_float(r[8 * v4 + 3]));
-            pk.z = pack2<kBf16>(__uint_as_float(r[8 * v4 + 4]), __uint_as_float(r[8 * v4 + 5]));
-            pk.w = pack2<kBf16>(__uint_as_float(r[8 * v4 + 6]), __uint_as_float(r[8 * v4 + 7]));
-            orow[c * 4 + v4] = pk;
-          }
-        }
-      }
+      if (g == ((it0 - 1) & 1)) drain_row = grow;
     }
+    if (drain_row >= 0) drain();
     tc_fence_before();
   }
   __syncthreads();
