@@ -269,9 +269,8 @@ __global__ void __launch_bounds__(128) gather_kv_kernel(const T* __restrict__ kc
 // the probability-weighted sum of the selected value rows.  Blocks are read in place from the cache, so a block
 // selected by many tokens of a head is served from L2 and nothing of size [B,H,T,top_k*block,D] is ever written.
 //
-// One CTA per (token t, batch*head); warp w takes selected blocks w, w+4, ...  A row of D elements is spread over
-// LPR = D / VEC lanes (16 bytes each, so every load instruction covers whole rows, fully coalesced) and a warp handles
-// 32 / LPR rows per step; the LPR partial dot products are combined with shuffles.
+// One CTA per (token t, batch*head); warp w takes selected blocks w, w+4, ...; every load instruction covers whole
+// rows (coalesced) and the partial dot products of a row are combined with shuffles.
 template <typename T, int VEC>
 __device__ __forceinline__ void load_vec_f32(const T* p, float (&o)[VEC]) {
   struct __align__(16) Vec { T v[VEC]; };
@@ -286,6 +285,14 @@ __device__ __forceinline__ void load_vec_f32(const T* p, float (&o)[VEC]) {
 #ifndef LMK_SEL_MINB
 #define LMK_SEL_MINB 8
 #endif
+#ifndef LMK_SEL_UNROLL
+#define LMK_SEL_UNROLL 1
+#endif
+constexpr int kSelUnroll = LMK_SEL_UNROLL;
+#ifndef LMK_PV_UNROLL
+#define LMK_PV_UNROLL 4
+#endif
+constexpr int kPvUnroll = LMK_PV_UNROLL;
 template <typename T> struct Packed;      // arithmetic on two 16-bit values held in one 32-bit register
 template <> struct Packed<__nv_bfloat16> {
   static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
@@ -331,95 +338,122 @@ __global__ void __launch_bounds__(128, LMK_SEL_MINB) selected_logits_kernel(cons
                                                               const T* __restrict__ cos_t, const T* __restrict__ sin_t,
                                                               int n_pos, int rotary, T* __restrict__ logits,
                                                               int64_t ld, int64_t col0, int H, int Tq, float scale) {
+  // A row of LPR 16-byte vectors is spread over LP = LPR / 2 lanes: lane `sub` holds vector `sub` of the low half of
+  // the features and the same vector of the high half, which are exactly the two operands of one rotate_half pair, so
+  // no lane needs another lane's data; a warp handles 32 / LP rows per step.
   constexpr int VEC = 16 / sizeof(T);
-  constexpr int D = LPR * VEC, HALF = D / 2, RPS = 32 / LPR;
+  constexpr int D = LPR * VEC, HALF = D / 2, LP = LPR / 2, RPS = 32 / LP;
   const int t = blockIdx.x, bh = blockIdx.y;
   const int b = bh / H, h = bh - b * H;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int sub = lane % LPR, rsub = lane / LPR, d0 = sub * VEC;
+  const int sub = lane % LP, rsub = lane / LP, d0 = sub * VEC;
   const int blk = kd.block, N = kd.n_blocks, top_k = kd.top_k;
-  float qv[VEC];
-  load_vec_f32<T, VEC>(q + ((int64_t)bh * Tq + t) * D + d0, qv);
+  float q0[VEC], q1[VEC];
+  load_vec_f32<T, VEC>(q + ((int64_t)bh * Tq + t) * D + d0, q0);
+  load_vec_f32<T, VEC>(q + ((int64_t)bh * Tq + t) * D + HALF + d0, q1);
 #pragma unroll
-  for (int u = 0; u < VEC; ++u) qv[u] *= scale;
-  const bool lo = d0 < HALF;
-  const int dpart = lo ? d0 + HALF : d0 - HALF;
+  for (int u = 0; u < VEC; ++u) {
+    q0[u] *= scale;
+    q1[u] *= scale;
+  }
   const int32_t* idx_row = idx + ((int64_t)bh * Tq + t) * top_k;
   const T* kbase = kc + b * kd.stride_b + h * kd.stride_h;
+  T* out_row = logits + ((int64_t)bh * Tq + t) * ld + col0;
   for (int i = warp; i < top_k; i += 4) {
     const int sel = idx_row[i];
     const bool recent = logical_age(sel, kd.ring_start, N) >= N - top_k;
     const int pos0 = kd.pos_base + (i + (recent ? 1 : 0)) * blk;
-    const T* ksrc = kbase + (int64_t)sel * kd.stride_block;
-#pragma unroll 2
+    const T* ksrc = kbase + (int64_t)sel * kd.stride_block + d0;
+#pragma unroll kSelUnroll
     for (int r0 = 0; r0 < blk; r0 += RPS) {
       const int r = r0 + rsub;
       float acc0 = 0.f, acc1 = 0.f;
       if (r < blk) {
         const T* krow = ksrc + (int64_t)r * kd.stride_row;
         const int pos = max(0, min(pos0 + r, n_pos - 1));
+        const T* cr = cos_t + (int64_t)pos * D + d0;
+        const T* sr = sin_t + (int64_t)pos * D + d0;
         if constexpr (sizeof(T) == 2) {
-          uint32_t x[4], y[4], c[4], sn[4];
-          ld16(krow + d0, x);
-          if (rotary == LMK_ROTARY_NONE) {
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              float f0, f1;
-              Packed<T>::to_f32(x[u], f0, f1);
-              acc0 = fmaf(qv[2 * u], f0, acc0);
-              acc1 = fmaf(qv[2 * u + 1], f1, acc1);
-            }
-          } else {
-            ld16(cos_t + (int64_t)pos * D + d0, c);
-            ld16(sin_t + (int64_t)pos * D + d0, sn);
+          uint32_t xl[4], xh[4];
+          ld16(krow, xl);
+          ld16(krow + HALF, xh);
+          if (rotary != LMK_ROTARY_NONE) {
+            uint32_t cl[4], ch[4], sl[4], sh[4], pl[4], ph[4];
+            ld16(cr, cl);
+            ld16(cr + HALF, ch);
+            ld16(sr, sl);
+            ld16(sr + HALF, sh);
             if (rotary == LMK_ROTARY_HALF) {
-              ld16(krow + dpart, y);                                   // partner half of the same row (an L1 hit)
-              const uint32_t flip = lo ? 0x80008000u : 0u;             // rotate_half: -x[d + D/2] for the low half
 #pragma unroll
-              for (int u = 0; u < 4; ++u) y[u] ^= flip;
+              for (int u = 0; u < 4; ++u) {        // rotate_half: (-x[d + D/2], x[d])
+                pl[u] = xh[u] ^ 0x80008000u;
+                ph[u] = xl[u];
+              }
             } else {
 #pragma unroll
-              for (int u = 0; u < 4; ++u) y[u] = __byte_perm(x[u], x[u], 0x1032) ^ 0x00008000u;   // (-x1, x0)
+              for (int u = 0; u < 4; ++u) {        // interleaved pairs: (x0, x1) -> (-x1, x0)
+                pl[u] = __byte_perm(xl[u], xl[u], 0x1032) ^ 0x00008000u;
+                ph[u] = __byte_perm(xh[u], xh[u], 0x1032) ^ 0x00008000u;
+              }
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              float f0, f1;
-              Packed<T>::to_f32(Packed<T>::add(Packed<T>::mul(x[u], c[u]), Packed<T>::mul(y[u], sn[u])), f0, f1);
-              acc0 = fmaf(qv[2 * u], f0, acc0);
-              acc1 = fmaf(qv[2 * u + 1], f1, acc1);
+              xl[u] = Packed<T>::add(Packed<T>::mul(xl[u], cl[u]), Packed<T>::mul(pl[u], sl[u]));
+              xh[u] = Packed<T>::add(Packed<T>::mul(xh[u], ch[u]), Packed<T>::mul(ph[u], sh[u]));
             }
           }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float f0, f1, g0, g1;
+            Packed<T>::to_f32(xl[u], f0, f1);
+            Packed<T>::to_f32(xh[u], g0, g1);
+            acc0 = fmaf(q0[2 * u], f0, acc0);
+            acc1 = fmaf(q0[2 * u + 1], f1, acc1);
+            acc0 = fmaf(q1[2 * u], g0, acc0);
+            acc1 = fmaf(q1[2 * u + 1], g1, acc1);
+          }
         } else {
-          float x[VEC];
-          load_vec_f32<T, VEC>(krow + d0, x);
-          if (rotary == LMK_ROTARY_NONE) {
-#pragma unroll
-            for (int u = 0; u < VEC; ++u) acc0 = fmaf(qv[u], x[u], acc0);
-          } else {
-            float c[VEC], sn[VEC];
-            load_vec_f32<T, VEC>(cos_t + (int64_t)pos * D + d0, c);
-            load_vec_f32<T, VEC>(sin_t + (int64_t)pos * D + d0, sn);
+          float xl[VEC], xh[VEC];
+          load_vec_f32<T, VEC>(krow, xl);
+          load_vec_f32<T, VEC>(krow + HALF, xh);
+          if (rotary != LMK_ROTARY_NONE) {
+            float cl[VEC], ch[VEC], sl[VEC], sh[VEC], ol[VEC], oh[VEC];
+            load_vec_f32<T, VEC>(cr, cl);
+            load_vec_f32<T, VEC>(cr + HALF, ch);
+            load_vec_f32<T, VEC>(sr, sl);
+            load_vec_f32<T, VEC>(sr + HALF, sh);
             if (rotary == LMK_ROTARY_HALF) {
-              float y[VEC];
-              load_vec_f32<T, VEC>(krow + dpart, y);
 #pragma unroll
-              for (int u = 0; u < VEC; ++u)
-                acc0 = fmaf(qv[u], __fadd_rn(__fmul_rn(x[u], c[u]), __fmul_rn(lo ? -y[u] : y[u], sn[u])), acc0);
+              for (int u = 0; u < VEC; ++u) {
+                ol[u] = __fadd_rn(__fmul_rn(xl[u], cl[u]), __fmul_rn(-xh[u], sl[u]));
+                oh[u] = __fadd_rn(__fmul_rn(xh[u], ch[u]), __fmul_rn(xl[u], sh[u]));
+              }
             } else {
 #pragma unroll
               for (int u = 0; u < VEC; u += 2) {
-                acc0 = fmaf(qv[u], __fadd_rn(__fmul_rn(x[u], c[u]), __fmul_rn(-x[u + 1], sn[u])), acc0);
-                acc1 = fmaf(qv[u + 1], __fadd_rn(__fmul_rn(x[u + 1], c[u + 1]), __fmul_rn(x[u], sn[u + 1])), acc1);
+                ol[u] = __fadd_rn(__fmul_rn(xl[u], cl[u]), __fmul_rn(-xl[u + 1], sl[u]));
+                ol[u + 1] = __fadd_rn(__fmul_rn(xl[u + 1], cl[u + 1]), __fmul_rn(xl[u], sl[u + 1]));
+                oh[u] = __fadd_rn(__fmul_rn(xh[u], ch[u]), __fmul_rn(-xh[u + 1], sh[u]));
+                oh[u + 1] = __fadd_rn(__fmul_rn(xh[u + 1], ch[u + 1]), __fmul_rn(xh[u], sh[u + 1]));
               }
             }
+#pragma unroll
+            for (int u = 0; u < VEC; ++u) {
+              xl[u] = ol[u];
+              xh[u] = oh[u];
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < VEC; ++u) {
+            acc0 = fmaf(q0[u], xl[u], acc0);
+            acc1 = fmaf(q1[u], xh[u], acc1);
           }
         }
       }
       float acc = acc0 + acc1;
 #pragma unroll
-      for (int o = LPR / 2; o >= 1; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (sub == 0 && r < blk)
-        logits[((int64_t)bh * Tq + t) * ld + col0 + (int64_t)i * blk + r] = from_f32<T>(acc);
+      for (int o = LP / 2; o >= 1; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (sub == 0 && r < blk) out_row[(int64_t)i * blk + r] = from_f32<T>(acc);
     }
   }
 }
@@ -453,7 +487,7 @@ __global__ void __launch_bounds__(128) selected_pv_kernel(const T* __restrict__ 
     for (int i = 0; i < top_k; ++i) {
       const int sel = idx[((int64_t)bh * Tq + t) * top_k + i];
       const T* vsrc = vbase + (int64_t)sel * vd.stride_block + vcol * VEC;
-#pragma unroll 4
+#pragma unroll kPvUnroll
       for (int r = rg; r < blk; r += groups) {
         const Vec v = *reinterpret_cast<const Vec*>(vsrc + (int64_t)r * vd.stride_row);
         const float p = ps[i * blk + r];
