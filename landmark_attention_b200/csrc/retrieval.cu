@@ -158,29 +158,57 @@ __global__ void __launch_bounds__(128) topk_sorted_kernel(const float* __restric
                                                           int64_t rows, int64_t inner_count, int64_t outer_stride,
                                                           int64_t inner_stride, int reduce, int64_t reduce_stride,
                                                           int n, int k, int ring_start, int warps_per_cta) {
-  extern __shared__ float tk_smem[];
+  extern __shared__ __align__(16) float tk_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t row = (int64_t)blockIdx.x * warps_per_cta + warp;
   if (warp >= warps_per_cta || row >= rows) return;
   float* vals = tk_smem + (size_t)warp * n;
   const int64_t outer = row / inner_count, inner = row - outer * inner_count;
   const float* src = scores + outer * outer_stride + inner * inner_stride;
-  for (int j = lane; j < n; j += 32) {
-    float v = src[j];
-    for (int r = 1; r < reduce; ++r) v = fmaxf(v, src[(int64_t)r * reduce_stride + j]);
-    vals[j] = (v != v) ? -INFINITY : v;   // NaN scores rank lowest
+  // rows of whole, 16-byte aligned float4 groups are moved and scanned four values at a time (several loads in flight
+  // per lane; the scalar loop is latency-bound on a cold row)
+  const bool vec4 = reduce == 1 && (n & 3) == 0 && ((reinterpret_cast<uintptr_t>(src) | (uintptr_t)(n * sizeof(float))) & 15) == 0;
+  if (vec4) {
+    const float4* src4 = reinterpret_cast<const float4*>(src);
+    float4* vals4 = reinterpret_cast<float4*>(vals);
+#pragma unroll 8
+    for (int j = lane; j < n / 4; j += 32) {
+      float4 v = src4[j];
+      v.x = (v.x != v.x) ? -INFINITY : v.x;   // NaN scores rank lowest
+      v.y = (v.y != v.y) ? -INFINITY : v.y;
+      v.z = (v.z != v.z) ? -INFINITY : v.z;
+      v.w = (v.w != v.w) ? -INFINITY : v.w;
+      vals4[j] = v;
+    }
+  } else {
+    for (int j = lane; j < n; j += 32) {
+      float v = src[j];
+      for (int r = 1; r < reduce; ++r) v = fmaxf(v, src[(int64_t)r * reduce_stride + j]);
+      vals[j] = (v != v) ? -INFINITY : v;
+    }
   }
   __syncwarp();
   int mine = -1;   // lane i keeps the i-th pick
   for (int it = 0; it < k; ++it) {
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int j = lane; j < n; j += 32) {
-      float v = vals[j];
+    auto consider = [&](float v, int j) {
       if (v > best || (v == best && j < bi)) {
         best = v;
         bi = j;
       }
+    };
+    if (vec4) {
+      const float4* vals4 = reinterpret_cast<const float4*>(vals);
+      for (int j = lane; j < n / 4; j += 32) {
+        const float4 v = vals4[j];
+        consider(v.x, 4 * j);
+        consider(v.y, 4 * j + 1);
+        consider(v.z, 4 * j + 2);
+        consider(v.w, 4 * j + 3);
+      }
+    } else {
+      for (int j = lane; j < n; j += 32) consider(vals[j], j);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
