@@ -323,7 +323,8 @@ def bench_retrieval(P, L, dev, peaks):
     desc = L.CacheDesc(st[0], st[1], st[2] * blk, st[2], nblk, 0, blk, top_k, C - (top_k + 1) * blk)
     ev = lambda: torch.cuda.Event(enable_timing=True)
     flush = torch.empty(384 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    names = ["scores", "topk", "gather", "attend_gathered", "selected_logits", "selected_pv"]
+    names = ["scores", "topk", "gather", "attend_gathered", "selected_logits", "selected_pv",
+             "topk_per_head", "selected_logits_per_head", "selected_pv_per_head"]
     times = {n: [] for n in names}
     logits = torch.empty((1, H, T, top_k * blk), dtype=torch.bfloat16, device=dev)
     stages = [
@@ -335,6 +336,11 @@ def bench_retrieval(P, L, dev, peaks):
             (torch.matmul(q.unsqueeze(3), c["kv"][0].transpose(3, 4)) * (D ** -0.5)).softmax(-1), c["kv"][1])),
         lambda c: P.selected_logits(q, pk, desc, c["sel"], logits, 0, cos, sin, L.ROTARY_HALF),
         lambda c: c.update(out=P.selected_pv(c["probs"], pv, desc, c["sel"])),
+        # the other selection mode: one set of blocks per head, the best over all tokens of the chunk
+        lambda c: c.update(sel_h=P.topk_sorted(c["scores"], top_k, mode="max_over_tokens")
+                           .expand(1, H, T, top_k).contiguous()),
+        lambda c: P.selected_logits(q, pk, desc, c["sel_h"], logits, 0, cos, sin, L.ROTARY_HALF),
+        lambda c: c.update(out_h=P.selected_pv(c["probs"], pv, desc, c["sel_h"])),
     ]
     # each stage is captured through the public API into its own CUDA graph (the eager calls are launch-bound)
     side = torch.cuda.Stream()
@@ -372,6 +378,7 @@ def bench_retrieval(P, L, dev, peaks):
     ms_mat = ms["scores"] + ms["topk"] + ms["gather"]
     ms_mat_attend = ms_mat + ms["attend_gathered"]
     ms_fused = ms["scores"] + ms["topk"] + ms["selected_logits"] + ms["selected_pv"]
+    ms_per_head = ms["scores"] + ms["topk_per_head"] + ms["selected_logits_per_head"] + ms["selected_pv_per_head"]
     gather_bytes = 2 * 2 * H * T * top_k * blk * D * 2          # K and V, read + write
     gbs = gather_bytes / (ms["gather"] * 1e-3) / 1e9
     sel = ctx["sel"]
@@ -382,6 +389,7 @@ def bench_retrieval(P, L, dev, peaks):
     return {"retrieval": {
         "metric": "retrieval attention-side tok/s (scores + top-k + selected-block logits and value sums, 32 layers)",
         "value": tok(ms_fused), "unit": "tok/s", "ms_per_layer": ms,
+        "value_per_head_selection": tok(ms_per_head),             # max_over_tokens mode, fused kernels
         "value_materialized_gather": tok(ms_mat),                 # data movement only, no logits / value sums
         "value_materialized_gather_and_attend": tok(ms_mat_attend),  # like for like with `value`
         "config": {"workload": "H=32 D=128 cache 32768 tokens in blocks of 32, chunk 258, top-k 4 per (head, token)",

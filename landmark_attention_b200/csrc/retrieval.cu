@@ -154,40 +154,11 @@ __global__ void __launch_bounds__(128) row_softmax_kernel(float* __restrict__ s,
 // ------------------------------------------------------------------------------------------- top-k
 constexpr int kTopkMaxK = 32;
 
-__global__ void __launch_bounds__(128) topk_sorted_kernel(const float* __restrict__ scores, int32_t* __restrict__ idx,
-                                                          int64_t rows, int64_t inner_count, int64_t outer_stride,
-                                                          int64_t inner_stride, int reduce, int64_t reduce_stride,
-                                                          int n, int k, int ring_start, int warps_per_cta) {
-  extern __shared__ __align__(16) float tk_smem[];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t row = (int64_t)blockIdx.x * warps_per_cta + warp;
-  if (warp >= warps_per_cta || row >= rows) return;
-  float* vals = tk_smem + (size_t)warp * n;
-  const int64_t outer = row / inner_count, inner = row - outer * inner_count;
-  const float* src = scores + outer * outer_stride + inner * inner_stride;
-  // rows of whole, 16-byte aligned float4 groups are moved and scanned four values at a time (several loads in flight
-  // per lane; the scalar loop is latency-bound on a cold row)
-  const bool vec4 = reduce == 1 && (n & 3) == 0 && ((reinterpret_cast<uintptr_t>(src) | (uintptr_t)(n * sizeof(float))) & 15) == 0;
-  if (vec4) {
-    const float4* src4 = reinterpret_cast<const float4*>(src);
-    float4* vals4 = reinterpret_cast<float4*>(vals);
-#pragma unroll 8
-    for (int j = lane; j < n / 4; j += 32) {
-      float4 v = src4[j];
-      v.x = (v.x != v.x) ? -INFINITY : v.x;   // NaN scores rank lowest
-      v.y = (v.y != v.y) ? -INFINITY : v.y;
-      v.z = (v.z != v.z) ? -INFINITY : v.z;
-      v.w = (v.w != v.w) ? -INFINITY : v.w;
-      vals4[j] = v;
-    }
-  } else {
-    for (int j = lane; j < n; j += 32) {
-      float v = src[j];
-      for (int r = 1; r < reduce; ++r) v = fmaxf(v, src[(int64_t)r * reduce_stride + j]);
-      vals[j] = (v != v) ? -INFINITY : v;
-    }
-  }
-  __syncwarp();
+// k rounds of warp arg-max over vals[0..n) in shared memory (ties: lower index), then the picks are written in
+// ascending order of logical age.  Called by one full warp.
+__device__ __forceinline__ void select_topk_sorted(float* vals, int n, int k, int ring_start, bool vec4,
+                                                   int32_t* __restrict__ out_row) {
+  const int lane = threadIdx.x & 31;
   int mine = -1;   // lane i keeps the i-th pick
   for (int it = 0; it < k; ++it) {
     float best = -INFINITY;
@@ -230,7 +201,110 @@ __global__ void __launch_bounds__(128) topk_sorted_kernel(const float* __restric
     int a = __shfl_sync(0xffffffffu, age, u);
     rank += (a < age) ? 1 : 0;
   }
-  if (lane < k) idx[row * k + rank] = mine;
+  if (lane < k) out_row[rank] = mine;
+}
+
+__global__ void __launch_bounds__(128) topk_sorted_kernel(const float* __restrict__ scores, int32_t* __restrict__ idx,
+                                                          int64_t rows, int64_t inner_count, int64_t outer_stride,
+                                                          int64_t inner_stride, int reduce, int64_t reduce_stride,
+                                                          int n, int k, int ring_start, int warps_per_cta) {
+  extern __shared__ __align__(16) float tk_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row = (int64_t)blockIdx.x * warps_per_cta + warp;
+  if (warp >= warps_per_cta || row >= rows) return;
+  float* vals = tk_smem + (size_t)warp * n;
+  const int64_t outer = row / inner_count, inner = row - outer * inner_count;
+  const float* src = scores + outer * outer_stride + inner * inner_stride;
+  // rows of whole, 16-byte aligned float4 groups are moved and scanned four values at a time (several loads in flight
+  // per lane; the scalar loop is latency-bound on a cold row)
+  const bool vec4 = reduce == 1 && (n & 3) == 0 && ((reinterpret_cast<uintptr_t>(src) | (uintptr_t)(n * sizeof(float))) & 15) == 0;
+  if (vec4) {
+    const float4* src4 = reinterpret_cast<const float4*>(src);
+    float4* vals4 = reinterpret_cast<float4*>(vals);
+#pragma unroll 8
+    for (int j = lane; j < n / 4; j += 32) {
+      float4 v = src4[j];
+      v.x = (v.x != v.x) ? -INFINITY : v.x;   // NaN scores rank lowest
+      v.y = (v.y != v.y) ? -INFINITY : v.y;
+      v.z = (v.z != v.z) ? -INFINITY : v.z;
+      v.w = (v.w != v.w) ? -INFINITY : v.w;
+      vals4[j] = v;
+    }
+  } else {
+    for (int j = lane; j < n; j += 32) {
+      float v = src[j];
+      for (int r = 1; r < reduce; ++r) v = fmaxf(v, src[(int64_t)r * reduce_stride + j]);
+      vals[j] = (v != v) ? -INFINITY : v;
+    }
+  }
+  __syncwarp();
+  select_topk_sorted(vals, n, k, ring_start, vec4, idx + row * k);
+}
+
+// The aggregated selection modes (maximum over `reduce` score rows first): one CTA of 1024 threads per output row.
+// Few rows exist in these modes (batch * heads, or batch * tokens), so each CTA must pull its share of the scores at
+// several hundred GB/s on its own: 16-byte loads, the reduce range split over `parts` thread groups with four
+// independent chains each, partial maxima combined through shared memory, then the first warp selects.
+__global__ void __launch_bounds__(1024) topk_reduce_sorted_kernel(const float* __restrict__ scores,
+                                                                  int32_t* __restrict__ idx, int64_t inner_count,
+                                                                  int64_t outer_stride, int64_t inner_stride,
+                                                                  int reduce, int64_t reduce_stride, int n, int k,
+                                                                  int ring_start, int vec4, int parts) {
+  extern __shared__ __align__(16) float tk_smem[];      // [parts][n] partial maxima; row 0 becomes the result
+  const int64_t row = blockIdx.x;
+  const int64_t outer = row / inner_count, inner = row - outer * inner_count;
+  const float* src = scores + outer * outer_stride + inner * inner_stride;
+  const float ninf = -INFINITY;
+  if (vec4) {
+    const int cgs = n / 4;                               // column groups of four
+    const int per = (int)blockDim.x / parts;             // threads per part
+    const int part = threadIdx.x / per, t0 = threadIdx.x - part * per;
+    if (part < parts) {
+      for (int cg = t0; cg < cgs; cg += per) {
+        float4 m[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) m[c] = make_float4(ninf, ninf, ninf, ninf);
+        int r = part;
+        for (; r + 3 * parts < reduce; r += 4 * parts) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)(r + c * parts) * reduce_stride + 4 * cg);
+            m[c].x = fmaxf(m[c].x, v.x);
+            m[c].y = fmaxf(m[c].y, v.y);
+            m[c].z = fmaxf(m[c].z, v.z);
+            m[c].w = fmaxf(m[c].w, v.w);
+          }
+        }
+        for (; r < reduce; r += parts) {
+          const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)r * reduce_stride + 4 * cg);
+          m[0].x = fmaxf(m[0].x, v.x);
+          m[0].y = fmaxf(m[0].y, v.y);
+          m[0].z = fmaxf(m[0].z, v.z);
+          m[0].w = fmaxf(m[0].w, v.w);
+        }
+        float4 o;                                        // fmaxf drops NaNs: a NaN score ranks lowest
+        o.x = fmaxf(fmaxf(m[0].x, m[1].x), fmaxf(m[2].x, m[3].x));
+        o.y = fmaxf(fmaxf(m[0].y, m[1].y), fmaxf(m[2].y, m[3].y));
+        o.z = fmaxf(fmaxf(m[0].z, m[1].z), fmaxf(m[2].z, m[3].z));
+        o.w = fmaxf(fmaxf(m[0].w, m[1].w), fmaxf(m[2].w, m[3].w));
+        reinterpret_cast<float4*>(tk_smem + (size_t)part * n)[cg] = o;
+      }
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+      float v = tk_smem[j];
+      for (int p = 1; p < parts; ++p) v = fmaxf(v, tk_smem[(size_t)p * n + j]);
+      tk_smem[j] = v;
+    }
+  } else {
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+      float v = ninf;
+      for (int r = 0; r < reduce; ++r) v = fmaxf(v, src[(int64_t)r * reduce_stride + j]);
+      tk_smem[j] = v;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) select_topk_sorted(tk_smem, n, k, ring_start, false, idx + row * k);
 }
 
 // ------------------------------------------------------------------------------------------- gather
@@ -613,6 +687,24 @@ extern "C" int lmk_topk_sorted(const float* scores, int32_t* idx_out, int64_t ou
   LMK_CHECK_ARG(k >= 1 && k <= kTopkMaxK && k <= n, "topk_sorted: k %d outside [1, min(n, %d)]", k, kTopkMaxK);
   LMK_CHECK_ARG(ring_start >= 0 && ring_start < n, "topk_sorted: ring_start %d outside [0, n)", ring_start);
   const int64_t rows = outer_count * inner_count;
+  if (reduce > 1) {
+    const bool vec4 = (n & 3) == 0 && (((uintptr_t)scores | (uintptr_t)(outer_stride * 4) | (uintptr_t)(inner_stride * 4) |
+                                       (uintptr_t)(reduce_stride * 4)) & 15) == 0;
+    int parts = 1;
+    if (vec4) {
+      parts = 1024 / (n / 4);                          // thread groups that split the reduce range
+      parts = parts < 1 ? 1 : (parts > 8 ? 8 : parts);
+      if (parts > reduce) parts = reduce;
+      while ((size_t)parts * n * sizeof(float) > 200 * 1024) --parts;
+    }
+    const size_t rsmem = sizeof(float) * (size_t)n * parts;
+    LMK_CUDA(cudaFuncSetAttribute(topk_reduce_sorted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rsmem));
+    topk_reduce_sorted_kernel<<<(unsigned)rows, 1024, rsmem, (cudaStream_t)stream>>>(
+        scores, idx_out, inner_count, outer_stride, inner_stride, reduce, reduce_stride, n, k, ring_start, vec4 ? 1 : 0,
+        parts);
+    LMK_CUDA(cudaGetLastError());
+    return LMK_OK;
+  }
   int wpc = n <= 2048 ? 4 : (n <= 8192 ? 2 : 1);
   size_t smem = sizeof(float) * (size_t)n * wpc;
   LMK_CUDA(cudaFuncSetAttribute(topk_sorted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

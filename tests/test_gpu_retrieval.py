@@ -133,6 +133,31 @@ def test_selected_block_kernels_match_gather_then_matmul(dtype, rotary):
     assert (out.float() - exp_out).abs().max().item() < (1e-5 if dtype == torch.float32 else 1e-2)
 
 
+def test_selected_block_kernels_per_head_selection():
+    # max_over_tokens: one set of blocks per head, shared by every token of the chunk (indices expanded over tokens)
+    torch.manual_seed(8)
+    B, H, T, D, blk, nblk, top_k = 1, 3, 20, 64, 16, 24, 3
+    C = nblk * blk
+    dtype = torch.float32
+    q = torch.randn(B, H, T, D, device=DEV)
+    pk, pv = torch.randn(B, H, C, D, device=DEV), torch.randn(B, H, C, D, device=DEV)
+    cos, sin = P.rotary_tables_half(C + T + 1, D, dtype, DEV)
+    st = pk.stride()
+    desc = L.CacheDesc(st[0], st[1], st[2] * blk, st[2], nblk, 0, blk, top_k, C - (top_k + 1) * blk)
+    scores = P.landmark_scores(q, pk, desc, cos, sin, L.ROTARY_HALF)
+    sel1 = P.topk_sorted(scores, top_k, mode="max_over_tokens")                       # [B,H,1,k]
+    assert torch.equal(sel1[:, :, 0].long(), scores.amax(dim=2).topk(top_k, dim=-1).indices.sort(dim=-1).values)
+    sel = sel1.expand(B, H, T, top_k).contiguous()
+    sk, sv = P.gather_kv(pk, pv, desc, desc, sel1, cos, sin, L.ROTARY_HALF)          # [B,H,1,k*blk,D]
+    buf = torch.empty((B, H, T, top_k * blk), dtype=dtype, device=DEV)
+    P.selected_logits(q, pk, desc, sel, buf, 0, cos, sin, L.ROTARY_HALF)
+    exp = torch.matmul(q, sk[:, :, 0].transpose(2, 3)) / math.sqrt(D)
+    assert (buf - exp).abs().max().item() < 1e-4
+    probs = torch.softmax(buf, dim=-1)
+    out = P.selected_pv(probs, pv, desc, sel)
+    assert (out - torch.matmul(probs, sv[:, :, 0])).abs().max().item() < 1e-5
+
+
 def test_selected_block_kernels_config4_shape():
     # the long-context shape: D = 128, blocks of 32 rows, top-4 of 1024 blocks, one head group
     torch.manual_seed(6)
