@@ -731,7 +731,7 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
     }
   }
   after_s();      // S is in registers: a caller with separate S / dP buffers releases the S buffer here
-  float sub = delta, lm_ds = 0.f;
+  float sub = delta, lm_ds = 0.f, pscale = 1.f;
   const uint64_t c2 = pk2(c, c);
   uint64_t s0 = 0ull, s1 = 0ull, s2 = 0ull, s3 = 0ull;
   if (kind == 0) {
@@ -800,15 +800,20 @@ __device__ __forceinline__ void bwd_item(uint32_t ts, uint32_t tdp, uint32_t fre
     const float nd = (ql + qh) * rden;
     const float g = ex2(lm2 - M2L);
     const float w = g * rden;
-    const uint64_t w2 = pk2(w, w);
+    if (kNeedP) {
+      const uint64_t w2 = pk2(w, w);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) sp[j] = mul2(sp[j], w2);
+      for (int j = 0; j < 32; ++j) sp[j] = mul2(sp[j], w2);
+    } else {
+      pscale = w;       // P itself is not stored: its row factor is folded into the dS coefficients below
+    }
     sub = nd;
     lm_ds = g * (nd - delta) * scale;
   }
   // dS = P * (dP - sub) * scale = P * fma(dP, scale, -sub * scale)
-  const uint64_t sc2 = pk2(scale, scale);
-  const float nss = -sub * scale;
+  const float sc = scale * pscale;
+  const uint64_t sc2 = pk2(sc, sc);
+  const float nss = -sub * sc;
   const uint64_t nss2 = pk2(nss, nss);
   uint32_t wd[32];
 #pragma unroll
