@@ -848,7 +848,7 @@ enum { kErrDkvProducer = 201, kErrDkvMma = 202, kErrDkvSoftmax = 203, kErrDkvEpi
 // a time, so 9 to 12 warps all leave 168 registers per thread.)
 constexpr int kBwdGroups = 2;                       // softmax warpgroups (items are dealt round-robin)
 constexpr int kBwdThreads = (kBwdGroups * 4 + 3) * 32;
-constexpr int kSdpBufs = 3;                         // S / dP buffers in TMEM of the dQ kernel: 3 x (64 + 64) columns
+constexpr int kSdpBufs = 2;                         // S / dP buffers in TMEM of the dQ kernel: 2 x (64 + 64) columns
 constexpr int kDkvStages = 2;
 
 struct DkvSmem {
@@ -1145,8 +1145,9 @@ constexpr int kDqStages = 4;
 
 struct DqSmem {
   uint64_t qdo_full;
-  uint64_t qdo_empty;       // the S / dP products of the unit have read the Q and dO tiles
-  uint64_t delta_read;      // both softmax warpgroups have read the O and dO tiles for delta
+  uint64_t ops_ready;       // the unit's Q and dO rows sit in TMEM (written by the softmax warpgroups)
+  uint64_t ops_free;        // the S / dP products of the unit have read them
+  uint64_t delta_read;      // both softmax warpgroups are done with the Q, dO and O tiles in shared memory
   uint64_t full[kDqStages];
   uint64_t empty[kDqStages];
   uint64_t ds_ready[kDqStages];
@@ -1191,7 +1192,8 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
   if (tid == 0) {
     mbar_init(smem_u32(&sm->qdo_full), 1);
-    mbar_init(smem_u32(&sm->qdo_empty), 1);
+    mbar_init(smem_u32(&sm->ops_ready), 256);
+    mbar_init(smem_u32(&sm->ops_free), 1);
     mbar_init(smem_u32(&sm->delta_read), 256);
     for (int s = 0; s < kDqStages; ++s) {
       mbar_init(smem_u32(&sm->full[s]), 1);
@@ -1212,7 +1214,11 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
-  const uint32_t tmem_s = tmem, tmem_dp = tmem + 192, tmem_dq = tmem + 384;
+  // TMEM: S buffers [0,128), dP buffers [128,256), dQ [256,384), Q rows [384,448), dO rows [448,512).  Q and dO are the
+  // A operands of S = Q K^T and dP = dO V^T for every key block of the unit: held in TMEM they are not re-read from
+  // shared memory 2 x 32 KB per block (half of the kernel's shared-memory operand traffic), and their shared-memory
+  // tiles are free for the next unit's loads as soon as the prologue has copied them.
+  const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dq = tmem + 256, tmem_q = tmem + 384, tmem_do = tmem + 448;
 
   if (warp == kBwdGroups * 4) {
     if (lane == 0) {
@@ -1226,7 +1232,6 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const int t = unit_tile(w), bh = w % BH, b = bh / H, h = bh - b * H;
         const int total = unit_items(t), n_last = total - 1;
         const uint32_t qb = smem_u32(&sm->qdo_full);
-        mbar_wait(smem_u32(&sm->qdo_empty), (u & 1) ^ 1, &g_lmk_status, kErrDqProducer);
         mbar_wait(smem_u32(&sm->delta_read), (u & 1) ^ 1, &g_lmk_status, kErrDqProducer);
         mbar_arrive_expect_tx(qb, 6 * kTileBytes);
         tma_load_4d(o_tile, &tm_o, qb, 0, t * kQTile, h, b);
@@ -1253,12 +1258,11 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (lane == 0) {
       constexpr uint32_t fmt = kBf16 ? 1u : 0u;
       constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);
-      const uint64_t dqd = smem_desc_sw128(q_tile, 16, 1024), ddo = smem_desc_sw128(do_tile, 16, 1024);
       const uint64_t dk0 = smem_desc_sw128(k_slot(0), 16, 1024), dv0 = smem_desc_sw128(v_slot(0), 16, 1024);
       int it = 0, u = 0;
       for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
         const int total = unit_items(unit_tile(w));
-        mbar_wait(smem_u32(&sm->qdo_full), u & 1, &g_lmk_status, kErrDqMma);
+        mbar_wait(smem_u32(&sm->ops_ready), u & 1, &g_lmk_status, kErrDqMma);
         for (int i = 0; i < total; ++i, ++it) {
           const int s = it % kDqStages, sb = it % kSdpBufs;
           mbar_wait(smem_u32(&sm->full[s]), (it / kDqStages) & 1, &g_lmk_status, kErrDqMma);
@@ -1267,16 +1271,15 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           tc_fence_after();
           const uint64_t dk = desc_advance(dk0, (uint32_t)s * 32768u), dv = desc_advance(dv0, (uint32_t)s * 32768u);
 #pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk)
-            mma_f16_ss(tmem_s + sb * 64, desc_advance(dqd, kmajor_step(kk, kTileBytes)),
-                       desc_advance(dk, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
+          for (int kk = 0; kk < kD / 16; ++kk)      // A from TMEM: 8 columns = 16 features per K-step
+            mma_f16_ts(tmem_s + sb * 64, tmem_q + kk * 8, desc_advance(dk, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
 #pragma unroll
           for (int kk = 0; kk < kD / 16; ++kk)
-            mma_f16_ss(tmem_dp + sb * 64, desc_advance(ddo, kmajor_step(kk, kTileBytes)),
-                       desc_advance(dv, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
+            mma_f16_ts(tmem_dp + sb * 64, tmem_do + kk * 8, desc_advance(dv, kmajor_step(kk, kHalfTile)), idesc_s,
+                       kk > 0);
           mma_commit(smem_u32(&sm->sdp_full[sb]));
         }
-        mma_commit(smem_u32(&sm->qdo_empty));
+        mma_commit(smem_u32(&sm->ops_free));        // the next unit's Q / dO rows may be written
       }
     }
     __syncwarp();
@@ -1370,6 +1373,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       // also publishes it for the dK/dV kernel, which runs after this one
       mbar_wait(smem_u32(&sm->qdo_full), u & 1, &g_lmk_status, kErrDqSoftmax);
       float delta = 0.f;
+      uint32_t opw[2][32];      // this thread's row of the operand its warpgroup moves to TMEM (0: Q, 1: dO)
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub)
 #pragma unroll
@@ -1380,6 +1384,14 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                        : "=r"(ov[0]), "=r"(ov[1]), "=r"(ov[2]), "=r"(ov[3]) : "r"(o_tile + off));
           asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                        : "=r"(gv[0]), "=r"(gv[1]), "=r"(gv[2]), "=r"(gv[3]) : "r"(do_tile + off));
+          if (g == 1) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) opw[sub][4 * c + e] = gv[e];
+          } else {
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(opw[sub][4 * c]), "=r"(opw[sub][4 * c + 1]), "=r"(opw[sub][4 * c + 2]),
+                           "=r"(opw[sub][4 * c + 3]) : "r"(q_tile + off));
+          }
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             float2 fo, fg;
@@ -1394,7 +1406,18 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             delta = fmaf(fo.y, fg.y, delta);
           }
         }
-      mbar_arrive(smem_u32(&sm->delta_read));
+      mbar_arrive(smem_u32(&sm->delta_read));       // the shared-memory tiles may take the next unit's rows
+      // row -> TMEM lane, 32-bit word j (two features) -> column j: the layout of a K-major A operand
+      mbar_wait(smem_u32(&sm->ops_free), (u & 1) ^ 1, &g_lmk_status, kErrDqSoftmax);
+      tc_fence_after();
+      {
+        const uint32_t dst = (g == 0 ? tmem_q : tmem_do) + lane_base;
+        tmem_st_32x32b_x32(dst, opw[0]);
+        tmem_st_32x32b_x32(dst + 32, opw[1]);
+        tmem_st_wait();
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sm->ops_ready));
       if (g == 0) delta_ptr[grow] = delta;
       if (drain_row >= 0) drain();
       for (int i = (it0 + g) & 1; i < total; i += kBwdGroups) {
