@@ -25,9 +25,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--only", default="both", choices=["both", "fwd", "bwd"])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
+    ap.add_argument("--grouped-softmax", action="store_true",
+                    help="time the stand-alone grouped softmax (forward and backward) on [B,H,L,L] fp32 logits instead")
     a = ap.parse_args()
     dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[a.dtype]
     dev = torch.device("cuda")
+    if a.grouped_softmax:
+        return grouped_softmax_bench(a, dev)
     g = torch.Generator().manual_seed(0)
     B, H, Lq, D = a.B, a.H, a.L, a.D
     q, k, v = [(torch.randn(B, H, Lq, D, generator=g) * 0.5).to(dt).to(dev) for _ in range(3)]
@@ -75,6 +79,51 @@ def main():
         parts.append(f"bwd {t:.1f} us ({5 * fl / t / 1e6:.0f} TFLOP/s)")
     parts.append(f"status {L.device_status()}")
     print("  ".join(parts))
+
+
+def grouped_softmax_bench(a, dev):
+    """Training-shaped call of the lm_benchmark flavour through the C ABI: causal mask, a landmark after every
+    `block - 1` tokens, fp32 logits [B,H,L,L]; reports achieved GB/s of algorithmic bytes (forward: read x, write probs;
+    backward: read x and grad, write grad; masks are broadcast views of [1,1,L,L] bytes)."""
+    from .grouped_softmax import _prep, prepare_landmark_masks
+    B, H, Lq = a.B, a.H, a.L
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(B, H, Lq, Lq, generator=g).to(dev)
+    is_mem_row = (torch.arange(Lq, device=dev) % a.block == a.block - 1).view(1, Lq)
+    hidden = torch.ones(Lq, Lq, dtype=torch.bool, device=dev).triu(1)
+    mask, is_mem, last = prepare_landmark_masks(is_mem_row, hidden)
+    grad = torch.randn(B, H, Lq, Lq, generator=g).to(dev)
+    probs, gx = torch.empty_like(x), torch.empty_like(x)
+    max_groups = Lq // a.block + 2
+    x, ((m8, ms), (l8, ls), (h8, hs)) = _prep(x, is_mem, last, mask)
+    lib, st = L.lib(), L.stream_ptr(dev)
+
+    def fwd():
+        L.check(lib.lmk_grouped_softmax_fwd(L.ptr(x), L.strides3(x), L.ptr(m8), ms, L.ptr(l8), ls, L.ptr(h8), hs,
+                                            L.ptr(probs), None, 0, B, H, Lq, Lq, L.dtype_code(x), 1, max_groups, st),
+                "lmk_grouped_softmax_fwd")
+
+    def bwd():
+        L.check(lib.lmk_grouped_softmax_bwd(L.ptr(x), L.strides3(x), L.ptr(m8), ms, L.ptr(l8), ls, L.ptr(h8), hs,
+                                            L.ptr(grad), L.ptr(gx), B, H, Lq, Lq, L.dtype_code(x), 1, max_groups, st),
+                "lmk_grouped_softmax_bwd")
+
+    def timeit(f):
+        for _ in range(a.warmup):
+            f()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.iters):
+            f()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / a.iters * 1e3
+
+    t_f, t_b = timeit(fwd), timeit(bwd)
+    nbytes = x.numel() * 4
+    print(f"grouped softmax B={B} H={H} L={Lq} block={a.block} fp32  fwd {t_f:.1f} us ({2 * nbytes / t_f / 1e3:.0f} GB/s)  "
+          f"bwd {t_b:.1f} us ({3 * nbytes / t_b / 1e3:.0f} GB/s)")
 
 
 if __name__ == "__main__":
