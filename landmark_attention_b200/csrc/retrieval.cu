@@ -384,17 +384,12 @@ __device__ __forceinline__ void load_vec_f32(const T* p, float (&o)[VEC]) {
 // 16-bit types: the rotation x * cos + p * sin runs on packed pairs with the rounding steps of the gather kernel
 // (each product and the sum rounded to the 16-bit type, as the reference's tensor arithmetic does), which takes a
 // third of the instructions of converting everything to fp32 first; the dot product accumulates in fp32.
-#ifndef LMK_SEL_MINB
-#define LMK_SEL_MINB 8
-#endif
-#ifndef LMK_SEL_UNROLL
-#define LMK_SEL_UNROLL 1
-#endif
-constexpr int kSelUnroll = LMK_SEL_UNROLL;
-#ifndef LMK_PV_UNROLL
-#define LMK_PV_UNROLL 4
-#endif
-constexpr int kPvUnroll = LMK_PV_UNROLL;
+// Tuning of the selected-block kernels, from sweeps on a B200 at the long-context retrieval shape: the logits kernel
+// wants occupancy (8 CTAs per SM, i.e. <= 64 registers, even at the price of a small spill) rather than unrolling, and
+// the value-sum kernel is insensitive to its unroll factor.
+constexpr int kSelMinBlocks = 8;
+constexpr int kSelUnroll = 1;
+constexpr int kPvUnroll = 4;
 template <typename T> struct Packed;      // arithmetic on two 16-bit values held in one 32-bit register
 template <> struct Packed<__nv_bfloat16> {
   static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
@@ -435,7 +430,7 @@ __device__ __forceinline__ void ld16(const void* p, uint32_t (&w)[4]) {
 }
 
 template <typename T, int LPR>
-__global__ void __launch_bounds__(128, LMK_SEL_MINB) selected_logits_kernel(const T* __restrict__ q, const T* __restrict__ kc,
+__global__ void __launch_bounds__(128, kSelMinBlocks) selected_logits_kernel(const T* __restrict__ q, const T* __restrict__ kc,
                                                               lmk_cache_desc kd, const int32_t* __restrict__ idx,
                                                               const T* __restrict__ cos_t, const T* __restrict__ sin_t,
                                                               int n_pos, int rotary, T* __restrict__ logits,
