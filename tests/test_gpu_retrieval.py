@@ -41,13 +41,19 @@ def test_topk_aggregations_and_ring_order():
     assert torch.equal(got, exp)
 
 
-def test_topk_with_ties_and_infinities():
-    s = torch.full((1, 1, 2, 16), float("-inf"), device=DEV)
+@pytest.mark.parametrize("k", [3, 6])
+def test_topk_with_ties_and_infinities(k):
+    s = torch.full((1, 1, 4, 80), float("-inf"), device=DEV)
     s[0, 0, 0, 5] = 1.0
     s[0, 0, 1, :] = 0.5
-    got = P.topk_sorted(s, 3)
-    assert got[0, 0, 0].tolist() == [0, 1, 5]      # one finite value, then lowest indices among the -inf ties
-    assert got[0, 0, 1].tolist() == [0, 1, 2]      # all equal: lowest indices
+    s[0, 0, 2, :] = torch.arange(80, device=DEV).float() % 7      # many exact ties spread over all lanes
+    s[0, 0, 3, 40:] = float("nan")                                # NaN ranks lowest
+    s[0, 0, 3, 77] = 2.0
+    got = P.topk_sorted(s, k)
+    assert got[0, 0, 0].tolist() == sorted([5] + list(range(k))[: k - 1] if 5 >= k - 1 else list(range(k)))
+    assert got[0, 0, 1].tolist() == list(range(k))                # all equal: lowest indices
+    assert got[0, 0, 2].tolist() == [6 + 7 * i for i in range(k)]
+    assert got[0, 0, 3].tolist() == list(range(k - 1)) + [77]     # one finite value, then lowest indices among the rest
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
