@@ -3,8 +3,10 @@
  *
  * Conventions
  *   - Every pointer is a DEVICE pointer owned by the caller unless stated otherwise; the library
- *     never allocates or frees device memory and keeps no state between calls (except a per-thread
- *     error string).
+ *     never allocates or frees device memory.  What it keeps between calls: a per-thread error string,
+ *     a per-device status word (lmk_device_status), a host-side table of encoded TMA descriptors keyed
+ *     by (pointer, shape, strides), and the fixed scratch array of lmk_attn_bwd_static.
+ *   - Calls are asynchronous: they return once the kernels are queued on `stream`.
  *   - Tensors are row-major with a contiguous last dimension.  q/k/v take explicit element strides
  *     {batch, head, row}; all other tensors are dense in the documented shape.
  *   - dtype: LMK_F32, LMK_F16 or LMK_BF16 (all of q, k, v, o, dO, dQ, dK, dV share it).
@@ -35,12 +37,12 @@ enum {
   LMK_ERR_UNSUPPORTED = -2, /* valid request that no kernel in this build covers */
   LMK_ERR_CUDA = -3,        /* a CUDA runtime or driver call failed */
   LMK_ERR_WORKSPACE = -4,   /* workspace missing or too small */
-  LMK_ERR_DEVICE = -5       /* a kernel reported a device-side error (bounded wait expired) */
+  LMK_ERR_DEVICE = -5       /* returned by lmk_device_status only: a bounded wait expired inside an earlier kernel */
 };
 
 /* Kernel family selection for the fused attention entry points. */
 enum {
-  LMK_PATH_AUTO = 0,    /* tcgen05 path when the shape qualifies, otherwise the general path */
+  LMK_PATH_AUTO = 0,    /* tcgen05 path when shape, alignment and strides qualify, otherwise the general path */
   LMK_PATH_GENERAL = 1, /* CUDA-core fp32-accumulate kernels: any dtype, D <= 128, block <= 128 */
   LMK_PATH_TCGEN05 = 2  /* TMA + tcgen05/TMEM kernels: bf16/fp16, D == 128, block == 64, full 128-row tiles */
 };
@@ -50,10 +52,18 @@ const char* lmk_last_error(void);
 
 /*
  * Device-side status word of the current device.  Every wait inside the tcgen05 kernels is bounded; a wait that
- * expires records a site code (> 0) here instead of hanging.  Synchronises the device, writes the code (0 = healthy)
- * to *status and clears it when `clear` != 0.  No counterpart in the reference.
+ * expires records a site code (> 0) here instead of hanging, and the kernel runs to its end with undefined results.
+ * The compute entry points cannot see this (they return before their kernels run), so a caller that wants to know
+ * polls this function after the work: it synchronises the device, writes the code (0 = healthy) to *status (nullable),
+ * clears it when `clear` != 0, and returns LMK_ERR_DEVICE when the code is non-zero.  No counterpart in the reference.
  */
 int lmk_device_status(int* status, int clear);
+
+/*
+ * Test hook: upper bound on the CTAs of the persistent backward kernels (0 = one per SM, the default), so that small
+ * test problems still make every CTA walk through several work units.  No counterpart in the reference.
+ */
+void lmk_debug_set_max_ctas(int n);
 
 /* 1 if the (shape, dtype) is handled by the tcgen05 kernels, else 0. */
 int lmk_attn_tcgen05_supported(int B, int H, int Lq, int Lk, int D, int block, int dtype);

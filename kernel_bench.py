@@ -1,16 +1,19 @@
 """Kernel-level timing of the fused attention entry points through the C ABI (no autograd, no allocation in the loop).
 
-    python -m landmark_attention_b200.kernel_bench --L 2048 --B 1 --H 32 [--path 2] [--iters 30] [--only fwd|bwd]
+    python kernel_bench.py --L 2048 --B 1 --H 32 [--path 2] [--iters 30] [--only fwd|bwd]
 
 Prints one line with the average device time of lmk_attn_fwd and lmk_attn_bwd (CUDA events around back-to-back
 calls) and the algorithmic TFLOP/s (2*B*H*L^2*D forward, 5*B*H*L^2*D backward).  This is the command the ncu
 summaries under profiles/ were captured with.
 """
 import argparse
+import os
+import sys
 
 import torch
 
-from . import _lib as L
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from landmark_attention_b200 import _lib as L  # noqa: E402
 
 
 def main():
@@ -85,7 +88,7 @@ def grouped_softmax_bench(a, dev):
     """Training-shaped call of the lm_benchmark flavour through the C ABI: causal mask, a landmark after every
     `block - 1` tokens, fp32 logits [B,H,L,L]; reports achieved GB/s of algorithmic bytes (forward: read x, write probs;
     backward: read x and grad, write grad; masks are broadcast views of [1,1,L,L] bytes)."""
-    from .grouped_softmax import _prep, prepare_landmark_masks
+    from landmark_attention_b200.grouped_softmax import _prep, prepare_landmark_masks
     B, H, Lq = a.B, a.H, a.L
     g = torch.Generator().manual_seed(0)
     x = torch.randn(B, H, Lq, Lq, generator=g).to(dev)

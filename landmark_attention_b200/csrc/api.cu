@@ -55,18 +55,26 @@ void fill(AttnParams& p, const void* q, const void* k, const void* v, int B, int
   }
 }
 
-// 1 = general, 2 = tcgen05, <0 = error
-int pick_path(int path, int B, int H, int Lq, int Lk, int D, int block, int dtype, float scale) {
+// 1 = general, 2 = tcgen05, <0 = error.  LMK_PATH_AUTO takes the tcgen05 kernels only when the shape AND the operands
+// (alignment, strides) qualify, and the general kernels otherwise; an explicit LMK_PATH_TCGEN05 request that cannot be
+// met is an error.
+int pick_path(int path, const AttnParams& p, int dtype, bool backward) {
   // the tcgen05 kernels take maxima on raw dot products, which needs a positive softmax scale
-  const bool fast = attn_sm100_supported(B, H, Lq, Lk, D, block, dtype) && scale > 0.f;
+  const bool shape_ok = attn_sm100_supported(p.B, p.H, p.Lq, p.Lk, p.D, p.block, dtype) && p.scale > 0.f;
+  const bool fast = shape_ok && attn_sm100_operands_ok(p, backward);
   if (path == LMK_PATH_TCGEN05) {
-    if (!fast)
+    if (!shape_ok)
       return fail(LMK_ERR_UNSUPPORTED,
                   "tcgen05 path needs bf16/fp16, D=128, block=64, Lq a multiple of 128 and a positive scale (got "
-                  "dtype=%d D=%d block=%d Lq=%d Lk=%d scale=%g)", dtype, D, block, Lq, Lk, (double)scale);
+                  "dtype=%d D=%d block=%d Lq=%d Lk=%d scale=%g)", dtype, p.D, p.block, p.Lq, p.Lk, (double)p.scale);
+    if (!fast)
+      return fail(LMK_ERR_UNSUPPORTED,
+                  "tcgen05 path needs 16-byte aligned tensors with positive batch/head strides and strides that are "
+                  "multiples of 8 elements");
     return LMK_PATH_TCGEN05;
   }
   if (path == LMK_PATH_AUTO && fast) return LMK_PATH_TCGEN05;
+  const int block = p.block;
   if (block > 128) return fail(LMK_ERR_UNSUPPORTED, "general path supports block sizes up to 128 (got %d)", block);
   return LMK_PATH_GENERAL;
 }
@@ -80,7 +88,16 @@ extern "C" int lmk_version(void) { return LMK_VERSION; }
 
 extern "C" const char* lmk_last_error(void) { return error_buffer(); }
 
-extern "C" int lmk_device_status(int* status, int clear) { return device_status(status, clear); }
+extern "C" int lmk_device_status(int* status, int clear) {
+  int v = 0;
+  const int rc = device_status(&v, clear);
+  if (status) *status = v;
+  if (rc != LMK_OK) return rc;
+  if (v != 0) return fail(LMK_ERR_DEVICE, "a bounded wait expired inside a kernel (site %d)", v);
+  return LMK_OK;
+}
+
+extern "C" void lmk_debug_set_max_ctas(int n) { attn_sm100_set_max_ctas(n); }
 
 extern "C" int lmk_attn_tcgen05_supported(int B, int H, int Lq, int Lk, int D, int block, int dtype) {
   return attn_sm100_supported(B, H, Lq, Lk, D, block, dtype) ? 1 : 0;
@@ -93,20 +110,23 @@ extern "C" int lmk_attn_fwd(const void* q, const void* k, const void* v, void* o
   int rc = check_common(q, k, v, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, block, dtype, path);
   if (rc != LMK_OK) return rc;
   LMK_CHECK_ARG(o && L && M, "attn_fwd: o, L or M is null");
-  int which = pick_path(path, B, H, Lq, Lk, D, block, dtype, sm_scale);
-  if (which < 0) return which;
   AttnParams p{};
   fill(p, q, k, v, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, block, sm_scale);
   p.o = o; p.L = L; p.M = M;
+  int which = pick_path(path, p, dtype, false);
+  if (which < 0) return which;
   if (which == LMK_PATH_TCGEN05) return attn_sm100_fwd(p, dtype, (cudaStream_t)stream);
   return attn_general_fwd(p, dtype, (cudaStream_t)stream);
 }
 
 extern "C" size_t lmk_attn_bwd_workspace(int B, int H, int Lq, int Lk, int D, int block, int dtype, int path) {
   if (B < 1 || H < 1 || Lq < 1 || Lk < 1) return 0;
-  const bool fast = attn_sm100_supported(B, H, Lq, Lk, D, block, dtype);
-  if (path == LMK_PATH_TCGEN05 || (path == LMK_PATH_AUTO && fast)) return attn_sm100_bwd_workspace(B, H, Lq, Lk, D);
-  return attn_general_bwd_workspace(B, H, Lq);
+  // with LMK_PATH_AUTO the kernel family also depends on the operands' alignment, which is not known here: both
+  // families need one float per (batch, head, query row), the larger figure is returned
+  const size_t a = attn_sm100_bwd_workspace(B, H, Lq, Lk, D), b = attn_general_bwd_workspace(B, H, Lq);
+  if (path == LMK_PATH_TCGEN05) return a;
+  if (path == LMK_PATH_GENERAL) return b;
+  return a > b ? a : b;
 }
 
 extern "C" int lmk_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO,
@@ -119,15 +139,15 @@ extern "C" int lmk_attn_bwd(const void* q, const void* k, const void* v, const v
   LMK_CHECK_ARG(o && dO && L && M && dQ && dK && dV, "attn_bwd: null tensor pointer");
   LMK_CHECK_ARG(Lq % block == 0 && Lk % block == 0, "Backward supported only for full blocks (Lq=%d Lk=%d block=%d)",
                 Lq, Lk, block);
-  int which = pick_path(path, B, H, Lq, Lk, D, block, dtype, sm_scale);
+  AttnParams p{};
+  fill(p, q, k, v, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, block, sm_scale);
+  p.o = const_cast<void*>(o); p.dO = dO;
+  int which = pick_path(path, p, dtype, true);
   if (which < 0) return which;
   const size_t need = lmk_attn_bwd_workspace(B, H, Lq, Lk, D, block, dtype, which);
   if (need > 0 && (workspace == nullptr || workspace_bytes < need))
     return fail(LMK_ERR_WORKSPACE, "attn_bwd: workspace of %zu bytes required, %zu given", need, workspace_bytes);
   LMK_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "attn_bwd: workspace must be 256-byte aligned");
-  AttnParams p{};
-  fill(p, q, k, v, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, block, sm_scale);
-  p.o = const_cast<void*>(o); p.dO = dO;
   p.L = const_cast<float*>(L); p.M = const_cast<float*>(M);
   p.dq = dQ; p.dk = dK; p.dv = dV;
   p.workspace = workspace; p.workspace_bytes = workspace_bytes;

@@ -24,6 +24,9 @@ int attn_general_bwd(const AttnParams& p, int dtype, cudaStream_t st);
 size_t attn_general_bwd_workspace(int B, int H, int Lq);
 
 bool attn_sm100_supported(int B, int H, int Lq, int Lk, int D, int block, int dtype);
+// pointers and strides of q, k, v (and o, dO for the backward pass) are addressable by TMA
+bool attn_sm100_operands_ok(const AttnParams& p, bool backward);
+void attn_sm100_set_max_ctas(int n);
 int attn_sm100_fwd(const AttnParams& p, int dtype, cudaStream_t st);
 int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st);
 size_t attn_sm100_bwd_workspace(int B, int H, int Lq, int Lk, int D);

@@ -33,7 +33,8 @@
 //   Per tile pair: earlier block  dS_j = g s_j (dP_j - nD) scale,  dS_landmark = g (nD - delta) scale,  P_j = g s_j,
 //   with s = softmax inside the block, g = exp(l_n - M) / L, nD = sum_j s_j dP_j;  own block: p = exp(S - M) / L,
 //   dS = p (dP - delta) scale.                                                                      (:152-305)
-#include <stdlib.h>
+#include <atomic>
+#include <mutex>
 #include "common.cuh"
 #include "attn_params.h"
 #include "sm100_ptx.cuh"
@@ -1467,40 +1468,135 @@ EncodeTiledFn get_encode() {
   return fn;
 }
 
+// Tensor maps are cached: a training loop calls with the same few (pointer, shape, strides) again and again, and
+// encoding five or six maps per call is a noticeable part of the host time of a 50 us kernel.  The key holds
+// everything the encoding depends on, so a hit is always valid (a map describes addresses, not contents); the table
+// is small, shared by all threads and replaced round-robin.
+struct MapKey {
+  const void* ptr;
+  int kind, dtype, B, H, L, box;
+  int64_t st[3];
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && kind == o.kind && dtype == o.dtype && B == o.B && H == o.H && L == o.L && box == o.box &&
+           st[0] == o.st[0] && st[1] == o.st[1] && st[2] == o.st[2];
+  }
+};
+constexpr int kMapCacheSize = 64;
+struct MapCache {
+  std::mutex mu;
+  MapKey keys[kMapCacheSize];
+  CUtensorMap maps[kMapCacheSize];
+  int used = 0, next = 0;
+};
+MapCache& map_cache() {
+  static MapCache c;
+  return c;
+}
+
+template <typename EncodeFn>
+int cached_map(CUtensorMap* m, const MapKey& key, EncodeFn encode) {
+  MapCache& c = map_cache();
+  {
+    std::lock_guard<std::mutex> lock(c.mu);
+    for (int i = 0; i < c.used; ++i)
+      if (c.keys[i] == key) {
+        *m = c.maps[i];
+        return LMK_OK;
+      }
+  }
+  const int rc = encode(m);
+  if (rc != LMK_OK) return rc;
+  std::lock_guard<std::mutex> lock(c.mu);
+  const int slot = c.used < kMapCacheSize ? c.used++ : (c.next++ % kMapCacheSize);
+  c.keys[slot] = key;
+  c.maps[slot] = *m;
+  return LMK_OK;
+}
+
 // [B, H, L, 128] tensor with element strides {b, h, row}; box = 64 features x `box_rows` rows, 128-byte swizzle
 int make_map_4d(CUtensorMap* m, const void* ptr, int dtype, int B, int H, int L, const int64_t st[3], int box_rows) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return fail(LMK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
-  cuuint64_t strides[3] = {(cuuint64_t)st[2] * 2, (cuuint64_t)st[1] * 2, (cuuint64_t)st[0] * 2};
-  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(m, dtype == LMK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(LMK_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed with %d", (int)r);
-  return LMK_OK;
+  const MapKey key{ptr, 4, dtype, B, H, L, box_rows, {st[0], st[1], st[2]}};
+  return cached_map(m, key, [&](CUtensorMap* out) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return fail(LMK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)st[2] * 2, (cuuint64_t)st[1] * 2, (cuuint64_t)st[0] * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(out, dtype == LMK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                     const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LMK_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed with %d", (int)r);
+    return (int)LMK_OK;
+  });
 }
 
 // landmark keys: k viewed as [B, H, L/64, 64, 128]; box = 64 features x 1 row-in-block x 64 blocks
 int make_map_landmarks(CUtensorMap* m, const void* ptr, int dtype, int B, int H, int L, const int64_t st[3],
                        int lm_box) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return fail(LMK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t dims[5] = {(cuuint64_t)kD, (cuuint64_t)kBlk, (cuuint64_t)(L / kBlk), (cuuint64_t)H, (cuuint64_t)B};
-  cuuint64_t strides[4] = {(cuuint64_t)st[2] * 2, (cuuint64_t)st[2] * 2 * kBlk, (cuuint64_t)st[1] * 2,
-                           (cuuint64_t)st[0] * 2};
-  cuuint32_t box[5] = {64, 1, (cuuint32_t)lm_box, 1, 1};
-  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-  CUresult r = enc(m, dtype == LMK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
-                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(LMK_ERR_CUDA, "cuTensorMapEncodeTiled (landmarks) failed with %d", (int)r);
+  const MapKey key{ptr, 5, dtype, B, H, L, lm_box, {st[0], st[1], st[2]}};
+  return cached_map(m, key, [&](CUtensorMap* out) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return fail(LMK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[5] = {(cuuint64_t)kD, (cuuint64_t)kBlk, (cuuint64_t)(L / kBlk), (cuuint64_t)H, (cuuint64_t)B};
+    cuuint64_t strides[4] = {(cuuint64_t)st[2] * 2, (cuuint64_t)st[2] * 2 * kBlk, (cuuint64_t)st[1] * 2,
+                             (cuuint64_t)st[0] * 2};
+    cuuint32_t box[5] = {64, 1, (cuuint32_t)lm_box, 1, 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = enc(out, dtype == LMK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
+                     const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LMK_ERR_CUDA, "cuTensorMapEncodeTiled (landmarks) failed with %d", (int)r);
+    return (int)LMK_OK;
+  });
+}
+
+// Per-device launch facts, looked up once: the SM count and the opt-in to large dynamic shared memory for every kernel
+// of this file (the attribute is a property of the function on a device, not of a launch).
+constexpr int kMaxDevices = 64;
+struct DeviceFacts {
+  bool ready = false;
+  int n_sm = 0;
+};
+constexpr size_t kSmemFwd2 = 1024 + 65536 + kFwd2Stages * 32768 + sizeof(Fwd2Smem);
+constexpr size_t kSmemFwd = 1024 + 32768 + kFwdStages * 32768 + sizeof(FwdSmem);
+constexpr size_t kSmemDkv = 1024 + 65536 + kDkvStages * 65536 + 32768 + sizeof(DkvSmem);
+constexpr size_t kSmemDq = 1024 + 65536 + kDqStages * 32768 + 32768 + sizeof(DqSmem);
+
+int device_facts(const DeviceFacts** out) {
+  static std::mutex mu;
+  static DeviceFacts facts[kMaxDevices];
+  int dev = 0;
+  LMK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(LMK_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  DeviceFacts& f = facts[dev];
+  if (!f.ready) {
+    LMK_CUDA(cudaDeviceGetAttribute(&f.n_sm, cudaDevAttrMultiProcessorCount, dev));
+    const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+    LMK_CUDA(cudaFuncSetAttribute(sm100_fwd2_kernel<true>, attr, (int)kSmemFwd2));
+    LMK_CUDA(cudaFuncSetAttribute(sm100_fwd2_kernel<false>, attr, (int)kSmemFwd2));
+    LMK_CUDA(cudaFuncSetAttribute(sm100_fwd_kernel<true>, attr, (int)kSmemFwd));
+    LMK_CUDA(cudaFuncSetAttribute(sm100_fwd_kernel<false>, attr, (int)kSmemFwd));
+    LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dq_kernel<true>, attr, (int)kSmemDq));
+    LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dq_kernel<false>, attr, (int)kSmemDq));
+    LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dkv_kernel<true>, attr, (int)kSmemDkv));
+    LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dkv_kernel<false>, attr, (int)kSmemDkv));
+    f.ready = true;
+  }
+  *out = &f;
   return LMK_OK;
 }
 
+// Upper bound on the CTAs of the persistent backward kernels; 0 = one per SM.  Only the tests lower it (to make every
+// CTA walk through several work units at small sizes).
+std::atomic<int> g_max_ctas{0};
+
+// A tensor the TMA unit can address: 16-byte aligned base, positive strides that are multiples of 16 bytes
+// (an expanded view has stride 0), rows at least one head apart.
 bool tma_ok(const void* p, const int64_t st[3]) {
-  return ((uintptr_t)p % 16 == 0) && st[0] % 8 == 0 && st[1] % 8 == 0 && st[2] % 8 == 0 && st[2] >= kD;
+  return ((uintptr_t)p % 16 == 0) && st[0] > 0 && st[1] > 0 && st[0] % 8 == 0 && st[1] % 8 == 0 && st[2] % 8 == 0 &&
+         st[2] >= kD;
 }
 
 }  // namespace
@@ -1509,6 +1605,14 @@ bool attn_sm100_supported(int B, int H, int Lq, int Lk, int D, int block, int dt
   return (dtype == LMK_BF16 || dtype == LMK_F16) && D == kD && block == kBlk && Lq >= kQTile && Lq % kQTile == 0 &&
          Lk % kBlk == 0 && Lk >= Lq && B >= 1 && H >= 1;
 }
+
+bool attn_sm100_operands_ok(const AttnParams& p, bool backward) {
+  if (!tma_ok(p.q, p.qs) || !tma_ok(p.k, p.ks) || !tma_ok(p.v, p.vs)) return false;
+  if (backward && ((uintptr_t)p.dO % 16 != 0 || (uintptr_t)p.o % 16 != 0)) return false;
+  return true;
+}
+
+void attn_sm100_set_max_ctas(int n) { g_max_ctas.store(n > 0 ? n : 0); }
 
 int attn_sm100_fwd(const AttnParams& p, int dtype, cudaStream_t st) {
   if (!tma_ok(p.q, p.qs) || !tma_ok(p.k, p.ks) || !tma_ok(p.v, p.vs))
@@ -1522,30 +1626,24 @@ int attn_sm100_fwd(const AttnParams& p, int dtype, cudaStream_t st) {
   const int lm_box = (p.Lk / kBlk) < 64 ? (p.Lk / kBlk) : 64;
   if ((rc = make_map_landmarks(&tl, p.k, dtype, p.B, p.H, p.Lk, p.ks, lm_box)) != LMK_OK) return rc;
   const float scale_log2 = p.scale * kLog2e;
+  const DeviceFacts* facts = nullptr;
+  if ((rc = device_facts(&facts)) != LMK_OK) return rc;
   if (p.Lq % (2 * kQTile) == 0) {
-    const size_t smem = 1024 + 65536 + kFwd2Stages * 32768 + sizeof(Fwd2Smem);
     dim3 grid(p.B * p.H, p.Lq / (2 * kQTile));
-    if (dtype == LMK_BF16) {
-      LMK_CUDA(cudaFuncSetAttribute(sm100_fwd2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      sm100_fwd2_kernel<true><<<grid, kFwd2Threads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk,
-                                                                lm_box, scale_log2);
-    } else {
-      LMK_CUDA(cudaFuncSetAttribute(sm100_fwd2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      sm100_fwd2_kernel<false><<<grid, kFwd2Threads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk,
-                                                                 lm_box, scale_log2);
-    }
+    if (dtype == LMK_BF16)
+      sm100_fwd2_kernel<true><<<grid, kFwd2Threads, kSmemFwd2, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk,
+                                                                     lm_box, scale_log2);
+    else
+      sm100_fwd2_kernel<false><<<grid, kFwd2Threads, kSmemFwd2, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk,
+                                                                      lm_box, scale_log2);
   } else {
-    const size_t smem = 1024 + 32768 + kFwdStages * 32768 + sizeof(FwdSmem);
     dim3 grid(p.B * p.H, p.Lq / kQTile);
-    if (dtype == LMK_BF16) {
-      LMK_CUDA(cudaFuncSetAttribute(sm100_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      sm100_fwd_kernel<true><<<grid, kFwdThreads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk, lm_box,
-                                                              scale_log2);
-    } else {
-      LMK_CUDA(cudaFuncSetAttribute(sm100_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      sm100_fwd_kernel<false><<<grid, kFwdThreads, smem, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk, lm_box,
-                                                               scale_log2);
-    }
+    if (dtype == LMK_BF16)
+      sm100_fwd_kernel<true><<<grid, kFwdThreads, kSmemFwd, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk,
+                                                                  lm_box, scale_log2);
+    else
+      sm100_fwd_kernel<false><<<grid, kFwdThreads, kSmemFwd, st>>>(tq, tk, tv, tl, p.o, p.L, p.M, p.H, p.Lq, p.Lk,
+                                                                   lm_box, scale_log2);
   }
   LMK_CUDA(cudaGetLastError());
   return LMK_OK;
@@ -1567,29 +1665,22 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
   if ((rc = make_map_4d(&tdo, p.dO, dtype, p.B, p.H, p.Lq, dense, kQTile)) != LMK_OK) return rc;
   float* delta = reinterpret_cast<float*>(p.workspace);
   const float scale_log2 = p.scale * kLog2e;
-  const size_t smem_dkv = 1024 + 65536 + kDkvStages * 65536 + 32768 + sizeof(DkvSmem);
-  const size_t smem_dq = 1024 + 65536 + kDqStages * 32768 + 32768 + sizeof(DqSmem);
+  const size_t smem_dkv = kSmemDkv, smem_dq = kSmemDq;
   CUtensorMap to;
   if ((rc = make_map_4d(&to, p.o, dtype, p.B, p.H, p.Lq, dense, kQTile)) != LMK_OK) return rc;
-  int dev = 0, n_sm = 148;
-  LMK_CUDA(cudaGetDevice(&dev));
-  LMK_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-  if (const char* cap = getenv("LMK_MAX_CTAS")) {   // tests: force several work units per persistent CTA
-    const int v = atoi(cap);
-    if (v >= 1 && v < n_sm) n_sm = v;
-  }
+  const DeviceFacts* facts = nullptr;
+  if ((rc = device_facts(&facts)) != LMK_OK) return rc;
+  int n_sm = facts->n_sm;
+  const int cap = g_max_ctas.load();
+  if (cap >= 1 && cap < n_sm) n_sm = cap;
   const int dkv_units = ((p.Lk / kBlk + 1) / 2) * p.B * p.H;
   const int dq_units = (p.Lq / kQTile) * p.B * p.H;
   dim3 grid_dkv(dkv_units < n_sm ? dkv_units : n_sm), grid_dq(dq_units < n_sm ? dq_units : n_sm);
 #define LMK_BWD_LAUNCH(BF)                                                                                          \
   do {                                                                                                              \
     /* the dQ kernel also produces delta = rowsum(O * dO), which the dK/dV kernel launched after it reads */         \
-    LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dq_kernel<BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
-                                  (int)smem_dq));                                                                   \
     sm100_bwd_dq_kernel<BF><<<grid_dq, kBwdThreads, smem_dq, st>>>(tq, tk, tv, tdo, to, p.L, p.M, delta, p.dq, p.H, \
                                                                    p.B * p.H, p.Lq, p.Lk, p.scale, scale_log2);     \
-    LMK_CUDA(cudaFuncSetAttribute(sm100_bwd_dkv_kernel<BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
-                                  (int)smem_dkv));                                                                  \
     sm100_bwd_dkv_kernel<BF><<<grid_dkv, kBwdThreads, smem_dkv, st>>>(tq, tk, tv, tdo, p.L, p.M, delta, p.dk, p.dv, \
                                                                      p.H, p.B * p.H, p.Lq, p.Lk, p.scale,           \
                                                                      scale_log2);                                   \

@@ -22,6 +22,22 @@ def _rotate_interleaved(x, cos, sin, positions):
     return x * c + rot * s
 
 
+def _require_plain_rotary(closure, hs):
+    """Accept None or a closure whose encoder is lm_benchmark's RotaryPositionalEncoder: same class name, the
+    interleaved-pair frequencies 10^(-4 i / hs), and no attention-matrix adaptation."""
+    if closure is None:
+        return
+    enc = getattr(closure, "encoder", None)
+    freqs = getattr(enc, "freqs", None)
+    ok = type(closure).__name__ == "RotaryPositionalEncoderClosure" and freqs is not None and freqs.numel() == hs // 2
+    if ok:
+        want = 10 ** (-4 * torch.arange(0, hs, 2, device=freqs.device)[: hs // 2].float() / hs)
+        ok = torch.allclose(freqs.float(), want, rtol=1e-6, atol=0)
+    if not ok:
+        raise NotImplementedError("MemLMCacheStorage applies lm_benchmark's plain rotary encoding inside its kernels; "
+                                  f"the positional encoder closure {type(closure).__name__} is not supported")
+
+
 class MemLMCacheStorage(nn.Module):
     """Per-layer storage (mem_cache.py:21-158).  `config` needs batch_size, mem_cache_size, mem_cache_freq, n_head,
     n_embd, cache_topk, cache_selection_method."""
@@ -53,8 +69,11 @@ class MemLMCacheStorage(nn.Module):
         return self._tables
 
     def retrieve_for_query(self, q, cache_context, pos_emb_closure, start_index):
-        """mem_cache.py:41-109.  `pos_emb_closure` is accepted for interface parity; positions are applied with
-        lm_benchmark's rotary tables inside the kernels."""
+        """mem_cache.py:41-109.  Positions are applied inside the kernels with lm_benchmark's plain rotary tables
+        (positional_encoders/rotary.py), so `pos_emb_closure` must be None or the closure of that encoder; any other
+        encoder (rotary_mem_jump, or one that adapts the attention matrix) is refused instead of silently giving other
+        key rotations than the model expects."""
+        _require_plain_rotary(pos_emb_closure, q.shape[-1])
         B, nh, T, hs = q.shape
         blk = self.cache_mem_k.shape[2]
         cap = self.cache_mem_k.shape[1]

@@ -121,16 +121,52 @@ def test_extreme_logits_stay_finite_and_match(std):
         assert rel_l2(got, e) < 2e-2, name
 
 
-def test_persistent_kernels_with_several_units_per_cta(monkeypatch):
+def test_persistent_kernels_with_several_units_per_cta():
     # cap the persistent grid so that every CTA walks through many work units (cross-unit pipelining, phase counters)
     q, k, v, do = make(1, 3, 512, 640, torch.bfloat16, 13)
     ref = run_bwd(q, k, v, do, P.PATH_TCGEN05)
-    for cap in ("1", "2", "5"):
-        monkeypatch.setenv("LMK_MAX_CTAS", cap)
-        got = run_bwd(q, k, v, do, P.PATH_TCGEN05)
-        for a, b in zip(got, ref):
-            assert torch.equal(a, b)
-        assert L.device_status() == 0
+    try:
+        for cap in (1, 2, 5):
+            L.lib().lmk_debug_set_max_ctas(cap)
+            got = run_bwd(q, k, v, do, P.PATH_TCGEN05)
+            for a, b in zip(got, ref):
+                assert torch.equal(a, b)
+            assert L.device_status() == 0
+    finally:
+        L.lib().lmk_debug_set_max_ctas(0)
+
+
+def test_auto_path_falls_back_for_operands_tma_cannot_address():
+    # Shapes the tcgen05 kernels take, but operands they cannot: a view that starts 8 bytes into its storage, and a key
+    # tensor whose heads are an expanded (stride 0) view.  AUTO must run the general kernels and give the same
+    # result; an explicit tcgen05 request must be refused.
+    q, k, v, do = make(1, 2, 256, 256, torch.bfloat16, 21)
+    exp = O.landmark_attention_grads(q.float(), k.float(), v.float(), do.float(), 64)
+
+    def shifted(t):      # same values, storage offset of 4 elements = 8 bytes
+        buf = torch.empty(t.numel() + 4, dtype=t.dtype, device=DEV)
+        view = buf[4:].view(t.shape)
+        view.copy_(t)
+        return view
+
+    qs = shifted(q).requires_grad_(True)
+    kc, vc = [t.to(DEV).requires_grad_(True) for t in (k, v)]
+    assert qs.data_ptr() % 16 == 8
+    out = P.fused_landmark_attention(qs, kc, vc, None)
+    grads = torch.autograd.grad(out, [qs, kc, vc], do.to(DEV))
+    for got, e in zip((out, *grads), exp):
+        assert (got.detach().float().cpu() - e).abs().max().item() < 2e-2
+    with pytest.raises(NotImplementedError):
+        P.fused_landmark_attention(qs, kc, vc, None, path=P.PATH_TCGEN05)
+
+    k1 = k[:, :1].to(DEV)
+    kexp = k1.expand(1, 2, 256, 128)
+    assert kexp.stride(1) == 0
+    qc = q.to(DEV)
+    out2 = P.fused_landmark_attention(qc, kexp, v.to(DEV), None)
+    ref2 = P.fused_landmark_attention(qc, kexp.contiguous(), v.to(DEV), None, path=P.PATH_GENERAL)
+    assert (out2.float() - ref2.float()).abs().max().item() < 2e-2
+    assert L.device_status() == 0
 
 
 def test_auto_path_selection():
