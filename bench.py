@@ -2,12 +2,16 @@
 """Benchmark of the landmark-attention hot path on B200.
 
     python bench.py --gpus N --steps K --warmup W          # this repo's CUDA kernels
-    python bench.py --impl reference ...                   # the CPU restatement of the reference, host cores only
+    python bench.py --impl reference ...                   # the reference's own high-level path on the host cores
+                                                           # (oracle/_ref, staged by oracle/make_ref.py; the CPU
+                                                           # restatement in oracle/ only where that is absent)
 
 One step = one forward + backward pass of fused landmark attention at the configuration the headline metric is
 quoted on (B=1, H=32, L=2048, D=128, bf16, block 64, causal, no mask) on every GPU; with N GPUs each rank owns its own
 (batch, head) shard of the same size and there is no collective on the data path (weak scaling).  Rank 0 prints ONE
-JSON line.  FLOPs follow the flash-attention convention for causal attention: 2*B*H*L^2*D forward, 7*B*H*L^2*D forward
+JSON line.  Beside the headline it carries: `strong` (the same 32 heads split over the N ranks), `sweep` (B*H = 256,
+L = 2048 ... 32768, heads split over the ranks), `eager` (the public API without CUDA graphs), `sustained` (a replay
+loop of at least one second with the clocks sampled during it), `grouped_softmax` and `retrieval`.  FLOPs follow the flash-attention convention for causal attention: 2*B*H*L^2*D forward, 7*B*H*L^2*D forward
 plus backward (matmuls only, causal-halved).
 """
 import argparse
@@ -123,9 +127,20 @@ def shard_heads(total_bh, world, rank):
 
 
 # ----------------------------------------------------------------------------------------------------------------
-def cpu_oracle_attn(heads, threads, steps=1, warmup=0):
-    """fwd+bwd of the CPU restatement on `heads` heads of the workload (fp32); returns (TFLOP/s, seconds per step)."""
+def _cpu_fwd_bwd():
+    """(callable, kind): the reference's own high-level path from oracle/_ref when staged, else the restatement."""
+    from oracle import ref_runner as R
+    if R.available():
+        R.llama_mem()           # import cost (transformers) outside any timed region
+        return R.highlevel_fwd_bwd, "reference"
     from oracle import landmark_oracle as O
+    return O.landmark_attention_grads, "port"
+
+
+def cpu_headline_sample(heads, threads, steps=1, warmup=0):
+    """fwd+bwd of the reference's high-level path on `heads` heads of the headline workload (fp32) on the host cores;
+    returns (TFLOP/s, seconds per step, kind)."""
+    fn, kind = _cpu_fwd_bwd()
     torch.set_num_threads(threads)
     w = WORKLOAD
     g = torch.Generator().manual_seed(0)
@@ -134,11 +149,36 @@ def cpu_oracle_attn(heads, threads, steps=1, warmup=0):
     ts = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        O.landmark_attention_grads(q, k, v, do, w["block"])
+        fn(q, k, v, do, w["block"])
         if i >= warmup:
             ts.append(time.perf_counter() - t0)
     sec = sum(ts) / len(ts)
-    return attn_flops(1, heads, w["L"], w["D"]) / sec / 1e12, sec
+    return attn_flops(1, heads, w["L"], w["D"]) / sec / 1e12, sec, kind
+
+
+def cpu_config1(threads, runs=7):
+    """The reference's CPU-runnable case: B=2 H=8 L=512 D=64 fp32, block 64, mask supplied, fwd+bwd; min and median of
+    `runs` runs after one warm-up."""
+    fn, kind = _cpu_fwd_bwd()
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    q, k, v, do = [torch.randn(2, 8, 512, 64, generator=g) for _ in range(4)]
+    fn(q, k, v, do, 64)
+    ts = []
+    for _ in range(runs):
+        t0 = time.perf_counter()
+        fn(q, k, v, do, 64)
+        ts.append(time.perf_counter() - t0)
+    ts.sort()
+    fl = attn_flops(2, 8, 512, 64)
+    return {"workload": "B=2 H=8 L=512 D=64 fp32 block 64 fwd+bwd", "runs": runs, "ms_min": ts[0] * 1e3,
+            "ms_median": ts[len(ts) // 2] * 1e3, "tflops_at_median": fl / ts[len(ts) // 2] / 1e12, "kind": kind,
+            "cores": threads}
+
+
+def cpu_kind_text(kind):
+    return ("the reference's high-level path (llama_mem.landmark_grouped_softmax driven by its test recipe), staged "
+            "in oracle/_ref" if kind == "reference" else "CPU restatement of the reference's high-level path")
 
 
 def run_reference(args, world, rank):
@@ -146,22 +186,196 @@ def run_reference(args, world, rank):
         return
     threads = os.cpu_count() or 1
     heads = int(os.environ.get("LMK_BENCH_CPU_HEADS", "8"))       # bounded sample of the 32-head workload
-    tf, sec = cpu_oracle_attn(heads, threads, steps=min(args.steps, 10), warmup=min(args.warmup, 1))
+    tf, sec, kind = cpu_headline_sample(heads, threads, steps=min(args.steps, 10), warmup=min(args.warmup, 1))
     w = WORKLOAD
+    sample = f"{cpu_kind_text(kind)}, {heads} of {w['H']} heads per step, fp32, {threads} threads"
     line = {
         "impl": "reference", "metric": "landmark attn fwd+bwd TFLOP/s at L=2048 D=128", "value": tf, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "fused landmark attention fwd+bwd B=1 H=32 L=2048 D=128 block=64 causal",
                    "sample": f"{heads} of {w['H']} heads per step"},
-        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                         "sample": f"CPU restatement of the reference's high-level path, {heads} of {w['H']} heads, fp32"},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    if not os.environ.get("LMK_BENCH_SKIP_CONFIG1"):
+        line["cpu_baseline"]["config1"] = cpu_config1(threads)
     print(json.dumps(line), flush=True)
 
 
 # ----------------------------------------------------------------------------------------------------------------
+def _stats(xs):
+    xs = sorted(xs)
+    return {"min": xs[0], "median": xs[len(xs) // 2], "max": xs[-1]}
+
+
+def _make_problem(B, H, Lq, D, dev, seed, pinned_host=False):
+    """Seeded q, k, v ~ N(0,1)*0.5 and dO ~ N(0,1) in bf16.  Device-side generation for the large sweep shapes."""
+    if pinned_host:
+        g = torch.Generator().manual_seed(seed)
+        host = [(torch.randn(B, H, Lq, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory() for _ in range(3)]
+        host.append(torch.randn(B, H, Lq, D, generator=g).to(torch.bfloat16).pin_memory())
+        return host, [t.to(dev) for t in host]
+    g = torch.Generator(device=dev).manual_seed(seed)
+    dv = [(torch.randn(B, H, Lq, D, generator=g, device=dev) * 0.5).to(torch.bfloat16) for _ in range(3)]
+    dv.append(torch.randn(B, H, Lq, D, generator=g, device=dev).to(torch.bfloat16))
+    return None, dv
+
+
+def _capture_step(P, q, k, v, do, blk):
+    """Forward and backward captured separately through the public API; returns (g_fwd, g_bwd, out, grads)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        out = P.fused_landmark_attention(q, k, v, None, block_size=blk)
+        torch.autograd.grad(out, [q, k, v], do)
+        g_fwd, g_bwd = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_fwd, stream=side):
+            out_static = P.fused_landmark_attention(q, k, v, None, block_size=blk)
+        with torch.cuda.graph(g_bwd, pool=g_fwd.pool(), stream=side):
+            grads_static = torch.autograd.grad(out_static, [q, k, v], do)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    return g_fwd, g_bwd, out_static, grads_static
+
+
+def _time_graph_steps(g_fwd, g_bwd, flush, steps, world):
+    """`steps` replays with the L2 flushed before each one (outside its events); per-step (fwd, bwd, total) ms."""
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    marks = []
+    for _ in range(3):
+        g_fwd.replay(); g_bwd.replay()
+    barrier(world); torch.cuda.synchronize()
+    wall0 = time.perf_counter()
+    for _ in range(steps):
+        flush.zero_()
+        e0, e1, e2 = ev(), ev(), ev()
+        e0.record()
+        g_fwd.replay()
+        e1.record()
+        g_bwd.replay()
+        e2.record()
+        marks.append((e0, e1, e2))
+    torch.cuda.synchronize(); barrier(world)
+    wall = time.perf_counter() - wall0
+    return ([a.elapsed_time(b) for a, b, _ in marks], [b.elapsed_time(c) for _, b, c in marks],
+            [a.elapsed_time(c) for a, _, c in marks], wall)
+
+
+def bench_strong(P, world, rank, dev, flush, steps, peaks):
+    """The headline job itself (32 heads) split over the ranks with shard_heads: device-timed and end to end."""
+    w = WORKLOAD
+    lo, hi = shard_heads(w["B"] * w["H"], world, rank)
+    Hs = hi - lo
+    host, (q, k, v, do) = _make_problem(1, Hs, w["L"], w["D"], dev, 4321 + rank, pinned_host=True)
+    for t in (q, k, v):
+        t.requires_grad_(True)
+    g_fwd, g_bwd, _, _ = _capture_step(P, q, k, v, do, w["block"])
+    _, _, tot, _ = _time_graph_steps(g_fwd, g_bwd, flush, steps, world)
+    ms = max_over_ranks(statistics.fmean(tot), world, dev)
+    chunks = 4 if Hs % 4 == 0 else (2 if Hs % 2 == 0 else 1)
+    pipe = P.HostAttentionPipeline(1, Hs, w["L"], w["L"], w["D"], torch.bfloat16, w["block"], chunks=chunks, device=dev)
+    outs = [torch.empty(1, Hs, w["L"], w["D"], dtype=torch.bfloat16).pin_memory() for _ in range(4)]
+    for _ in range(2):
+        pipe.run(*host, *outs)
+    barrier(world); torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        pipe.run(*host, *outs)
+    b.record()
+    torch.cuda.synchronize(); barrier(world)
+    e2e_ms = max_over_ranks(a.elapsed_time(b) / steps, world, dev)
+    fl = attn_flops(w["B"], w["H"], w["L"], w["D"])
+    return {"scaling": "strong", "workload": f"B=1 H=32 L=2048 D=128: {Hs} heads per rank", "ms_per_step": ms,
+            "value": fl / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "e2e": {"value": fl / (e2e_ms * 1e-3) / 1e12, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": 4 * Hs * w["L"] * w["D"] * 2, "d2h_bytes_per_step": 4 * Hs * w["L"] * w["D"] * 2}}
+
+
+SWEEP_LENGTHS = (2048, 4096, 8192, 16384, 32768)
+
+
+def bench_sweep(P, world, rank, dev, peaks):
+    """Scaling sweep: B*H = 256 (B=8, H=32) heads of length L split over the ranks, fwd+bwd through the public API,
+    device-timed (max over ranks).  Inputs are far larger than L2 except at L=2048 (268 MB per rank at N=1)."""
+    out = {}
+    for Lq in SWEEP_LENGTHS:
+        lo, hi = shard_heads(256, world, rank)
+        Hs = hi - lo
+        _, (q, k, v, do) = _make_problem(1, Hs, Lq, 128, dev, 99 + rank)
+        for t in (q, k, v):
+            t.requires_grad_(True)
+        reps = 3 if Lq <= 8192 else 2
+        times = []
+        for i in range(1 + reps):
+            barrier(world); torch.cuda.synchronize()
+            e0, e1, e2 = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e0.record()
+            o = P.fused_landmark_attention(q, k, v, None, block_size=64)
+            e1.record()
+            grads = torch.autograd.grad(o, [q, k, v], do)
+            e2.record()
+            torch.cuda.synchronize()
+            if i > 0:
+                times.append((e0.elapsed_time(e1), e1.elapsed_time(e2)))
+            del o, grads
+        fwd = max_over_ranks(statistics.fmean(t[0] for t in times), world, dev)
+        bwd = max_over_ranks(statistics.fmean(t[1] for t in times), world, dev)
+        fl_f, fl_all = attn_flops(8, 32, Lq, 128, False), attn_flops(8, 32, Lq, 128, True)
+        tf = fl_all / ((fwd + bwd) * 1e-3) / 1e12
+        out[str(Lq)] = {"ms_fwd": fwd, "ms_bwd": bwd, "tflops": tf, "tflops_fwd": fl_f / (fwd * 1e-3) / 1e12,
+                        "tflops_bwd": (fl_all - fl_f) / (bwd * 1e-3) / 1e12,
+                        "frac_of_bf16_peak_per_gpu": tf / world / peaks["bf16_tflops"], "heads_per_rank": Hs}
+        del q, k, v, do
+        torch.cuda.empty_cache()
+    return {"workload": "B*H=256 (B=8,H=32) D=128 block 64 bf16 fwd+bwd, heads split over the ranks (strong scaling)",
+            "launch": "public API, eager", "by_L": out}
+
+
+def bench_grouped_softmax(P, L, dev, peaks):
+    """Stand-alone grouped softmax through the public API at the lm_benchmark training shape and at the LLaMA shape:
+    achieved GB/s of algorithmic bytes (forward: read x, write probs; backward: read x and grad, write grad_x)."""
+    from landmark_attention_b200.grouped_softmax import prepare_landmark_masks
+    res = {}
+    for name, (B, H, T, blk) in {"16x8x512x512_block51": (16, 8, 512, 51), "4x32x2048x2048_block64": (4, 32, 2048, 64)}.items():
+        g = torch.Generator(device=dev).manual_seed(5)
+        x = torch.randn(B, H, T, T, generator=g, device=dev, requires_grad=True)
+        is_mem_row = (torch.arange(T, device=dev) % blk == blk - 1).view(1, T).expand(B, T)
+        hidden = torch.ones(T, T, dtype=torch.bool, device=dev).triu(1)
+        mask, is_mem, last = prepare_landmark_masks(is_mem_row, hidden)
+        grad = torch.randn(B, H, T, T, generator=g, device=dev)
+        mg = T // blk + 3
+
+        def fwd():
+            return P.landmark_grouped_softmax_lm(x, -1, is_mem, mask, last, False, mg)[0]
+
+        def time_it(fn, n=10):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / n
+
+        t_f = time_it(fwd)
+        probs = fwd()
+        t_b = time_it(lambda: torch.autograd.grad(probs, x, grad, retain_graph=True))
+        nbytes = x.numel() * 4
+        res[name] = {"fwd_ms": t_f, "bwd_ms": t_b, "fwd_gbs": 2 * nbytes / (t_f * 1e-3) / 1e9,
+                     "bwd_gbs": 3 * nbytes / (t_b * 1e-3) / 1e9,
+                     "fwd_frac": 2 * nbytes / (t_f * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                     "bwd_frac": 3 * nbytes / (t_b * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        del x, grad, probs
+        torch.cuda.empty_cache()
+    return {"bound": "hbm", "peak": peaks["hbm_gbs"], "unit": "GB/s", "launch": "public API, eager, fp32 logits",
+            "shapes": res}
+
+
 def run_ours(args, world, rank, local):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: this package has no CPU path")
@@ -172,10 +386,7 @@ def run_ours(args, world, rank, local):
     peaks = measured_peaks()
     w = WORKLOAD
     B, H, Lq, D, blk = w["B"], w["H"], w["L"], w["D"], w["block"]
-    g = torch.Generator().manual_seed(1234 + rank)
-    host = [(torch.randn(B, H, Lq, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory() for _ in range(3)]
-    host.append(torch.randn(B, H, Lq, D, generator=g).to(torch.bfloat16).pin_memory())
-    q, k, v, do = [t.to(dev) for t in host]
+    host, (q, k, v, do) = _make_problem(B, H, Lq, D, dev, 1234 + rank, pinned_host=True)
     q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
     flush = torch.empty(384 * 1024 * 1024, dtype=torch.uint8, device=dev)      # 3x the 126 MB L2
     flops_fwd, flops_all = attn_flops(B, H, Lq, D, False), attn_flops(B, H, Lq, D, True)
@@ -193,47 +404,55 @@ def run_ours(args, world, rank, local):
     if L.device_status() != 0:
         raise SystemExit("device status word is non-zero after warm-up: a bounded wait expired")
 
-    # The step is launch-bound from Python (4 kernels of 10-170 us each), so the device-timed number replays the step
-    # from a CUDA graph captured through the public API; forward and backward are captured separately to time each.
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        step()
-        g_fwd, g_bwd = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_fwd, stream=side):
-            out_static = P.fused_landmark_attention(q, k, v, None, block_size=blk)
-        with torch.cuda.graph(g_bwd, pool=g_fwd.pool(), stream=side):
-            grads_static = torch.autograd.grad(out_static, [q, k, v], do)
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
+    # Headline number: the step replayed from CUDA graphs captured through the public API (forward and backward
+    # captured separately to time each); the eager call of the same API is reported beside it (`eager`).
+    g_fwd, g_bwd, out_static, grads_static = _capture_step(P, q, k, v, do, blk)
     ref_out, ref_grads = step()
     g_fwd.replay(); g_bwd.replay()
     torch.cuda.synchronize()
     if not (torch.equal(ref_out, out_static) and all(torch.equal(a, b) for a, b in zip(ref_grads, grads_static))):
         raise SystemExit("graph replay and eager call disagree")
-
-    ev = lambda: torch.cuda.Event(enable_timing=True)
-    marks = []
-    for _ in range(3):
-        g_fwd.replay(); g_bwd.replay()
-    barrier(world); torch.cuda.synchronize()
-    wall0 = time.perf_counter()
-    for _ in range(args.steps):
-        flush.zero_()                                   # evict q/k/v/o from L2; outside the per-step events
-        e0, e1, e2 = ev(), ev(), ev()
-        e0.record()
-        g_fwd.replay()
-        e1.record()
-        g_bwd.replay()
-        e2.record()
-        marks.append((e0, e1, e2))
-    torch.cuda.synchronize(); barrier(world)
-    wall = time.perf_counter() - wall0
-    fwd_ms = [a.elapsed_time(b) for a, b, _ in marks]
-    bwd_ms = [b.elapsed_time(c) for _, b, c in marks]
-    step_ms = statistics.fmean([a.elapsed_time(c) for a, _, c in marks])
-    step_ms = max_over_ranks(step_ms, world, dev)
+    fwd_ms, bwd_ms, tot_ms, wall = _time_graph_steps(g_fwd, g_bwd, flush, args.steps, world)
+    step_ms = max_over_ranks(statistics.fmean(tot_ms), world, dev)
     value = world * flops_all / (step_ms * 1e-3) / 1e12
+
+    # the same public call without graphs, device-resident tensors, L2 flushed before each step
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    eager_marks = []
+    for _ in range(3):
+        step()
+    barrier(world); torch.cuda.synchronize()
+    for _ in range(args.steps):
+        flush.zero_()
+        a, b_ = ev(), ev()
+        a.record()
+        step()
+        b_.record()
+        eager_marks.append((a, b_))
+    torch.cuda.synchronize(); barrier(world)
+    eager_ms = [a.elapsed_time(b_) for a, b_ in eager_marks]
+    eager_step_ms = max_over_ranks(statistics.fmean(eager_ms), world, dev)
+
+    # sustained: back-to-back replays for at least a second (no flush: q/k/v/o stay in L2), clocks sampled meanwhile
+    sustained = None
+    n_sus = max(200, int(1200.0 / max(step_ms, 1e-3)))
+    sus_sampler = ClockSampler(local)
+    barrier(world); torch.cuda.synchronize()
+    if rank == 0:
+        sus_sampler.start()
+        time.sleep(0.25)
+    a, b_ = ev(), ev()
+    a.record()
+    for _ in range(n_sus):
+        g_fwd.replay(); g_bwd.replay()
+    b_.record()
+    torch.cuda.synchronize(); barrier(world)
+    sus_ms = max_over_ranks(a.elapsed_time(b_) / n_sus, world, dev)
+    if rank == 0:
+        sc = sus_sampler.stop()
+        sustained = {"replays": n_sus, "seconds": sus_ms * n_sus * 1e-3, "ms_per_step": sus_ms,
+                     "value": world * flops_all / (sus_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "clocks": sc,
+                     "ms_x_mhz": (sus_ms * sc["sm_mhz"]) if sc.get("sm_mhz") else None}
 
     # end to end through the public API with HOST buffers: pinned inputs in, outputs and gradients back to pinned host
     # memory, all inside the timed region.  HostAttentionPipeline cuts the heads into chunks and overlaps the copies
@@ -263,8 +482,20 @@ def run_ours(args, world, rank, local):
     tensor_bytes = B * H * Lq * D * 2
 
     extra = {}
+    if not args.no_strong:
+        strong = bench_strong(P, world, rank, dev, flush, args.steps, peaks)
+        if rank == 0:
+            extra["strong"] = strong
+    del flush
+    torch.cuda.empty_cache()
+    if not args.no_sweep:
+        sweep = bench_sweep(P, world, rank, dev, peaks)
+        if rank == 0:
+            extra["sweep"] = sweep
     if rank == 0 and not args.no_retrieval:
-        extra = bench_retrieval(P, L, dev, peaks)
+        extra.update(bench_retrieval(P, L, dev, peaks))
+    if rank == 0 and not args.no_grouped_softmax:
+        extra["grouped_softmax"] = bench_grouped_softmax(P, L, dev, peaks)
     if L.device_status() != 0:
         raise SystemExit("device status word is non-zero after the timed region: a bounded wait expired")
     if rank != 0:
@@ -275,9 +506,6 @@ def run_ours(args, world, rank, local):
     dom_ms = bwd_avg if dominant == "backward" else fwd_avg
     achieved = dom_flops / (dom_ms * 1e-3) / 1e12
     cpu_threads = os.cpu_count() or 1
-    cpu_tf, cpu_sec = (None, None)
-    if world == 1 and not args.no_cpu_baseline:
-        cpu_tf, cpu_sec = cpu_oracle_attn(8, cpu_threads, steps=3, warmup=1)
     line = {
         "metric": "landmark attn fwd+bwd TFLOP/s at L=2048 D=128", "value": value, "unit": "TFLOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms,
@@ -287,6 +515,7 @@ def run_ours(args, world, rank, local):
                    "l2": "384 MB buffer written between timed steps", "flops": "7*B*H*L^2*D per step",
                    "launch": "step captured through the public API into CUDA graphs and replayed"},
         "pct_of_bf16_peak": 100.0 * value / world / peaks["bf16_tflops"], "peak_source": peaks["source"],
+        "step_ms": _stats(tot_ms),
         "kernels": {"forward_ms": fwd_avg, "backward_ms": bwd_avg,
                     "forward_tflops": flops_fwd / (fwd_avg * 1e-3) / 1e12,
                     "backward_tflops": (flops_all - flops_fwd) / (bwd_avg * 1e-3) / 1e12},
@@ -294,15 +523,21 @@ def run_ours(args, world, rank, local):
                      "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                      "traffic": DRAM_TRAFFIC[dominant], "traffic_unit": "bytes per launch group, ncu dram read+write",
                      "peak_source": peaks["source"]},
+        "eager": {"ms_per_step": eager_step_ms, "value": world * flops_all / (eager_step_ms * 1e-3) / 1e12,
+                  "step_ms": _stats(eager_ms),
+                  "what": "public API on device-resident tensors, no CUDA graph, L2 flushed before each step"},
+        "sustained": sustained,
         "e2e": {"value": world * flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 4 * tensor_bytes, "d2h_bytes_per_step": 4 * tensor_bytes},
         "gpu_launches": args.steps * 3,      # forward, dQ (+ delta), dK/dV
         "clocks": clocks, "wall_s": wall,
     }
-    if cpu_tf is not None:
-        line["cpu_baseline"] = {"value": cpu_tf, "unit": "TFLOP/s", "cores": cpu_threads, "kind": "port",
-                                "sample": "CPU restatement of the reference's high-level path, 8 of 32 heads x 3 passes, fp32, "
-                                          f"{cpu_sec:.2f} s per pass"}
+    if world == 1 and not args.no_cpu_baseline:
+        cpu_tf, cpu_sec, kind = cpu_headline_sample(4, cpu_threads, steps=3, warmup=1)
+        line["cpu_baseline"] = {"value": cpu_tf, "unit": "TFLOP/s", "cores": cpu_threads, "kind": kind,
+                                "sample": f"{cpu_kind_text(kind)}, 4 of 32 heads x 3 passes, fp32, "
+                                          f"{cpu_sec:.2f} s per pass",
+                                "config1": cpu_config1(cpu_threads)}
     line.update(extra)
     print(json.dumps(line), flush=True)
 
@@ -412,6 +647,9 @@ def main():
     ap.add_argument("--retrieval-only", action="store_true",
                     help="run only the long-context retrieval stages on one GPU and print their JSON object")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-strong", action="store_true")
+    ap.add_argument("--no-grouped-softmax", action="store_true")
     args = ap.parse_args()
     world, rank, local = dist_setup(args.gpus, cpu_only=args.impl == "reference")
     try:

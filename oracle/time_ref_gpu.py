@@ -1,0 +1,144 @@
+"""Time the reference's own GPU code (staged under oracle/_ref/, see make_ref.py) on this machine's GPU.
+TEST INFRASTRUCTURE ONLY: it runs none of this repository's kernels.
+
+    python oracle/time_ref_gpu.py [--out gpurun_out/ref_gpu.json] [--sweep]
+
+What is timed (CUDA events, seeded inputs of the benchmark's shapes):
+  * the reference's Triton kernels through its public `fused_landmark_attention` (forward, forward+backward) at the
+    headline shape B=1 H=32 L=2048 D=128 bf16, with parity against its own high-level path in fp32;
+  * the reference's high-level PyTorch path on the GPU at the same shape (bf16), and
+    torch.nn.functional.scaled_dot_product_attention(is_causal=True) as context;
+  * with --sweep, the Triton kernels at L = 4096 and 8192 with B*H = 32 (the reference's backward kernel runs one
+    program per (batch, head), so longer sequences or more heads take minutes per call and are left out).
+Every section is wrapped: a compile or launch error is recorded as text instead of stopping the run.
+"""
+import argparse
+import json
+import os
+import sys
+import time
+import traceback
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from oracle import ref_runner as R  # noqa: E402
+
+
+def cuda_time(fn, warm, iters):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return dict(ms_min=ts[0], ms_median=ts[len(ts) // 2])
+
+
+def flops(B, H, L, D):
+    return 2 * B * H * L * L * D, 7 * B * H * L * L * D
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "ref_gpu.json"))
+    ap.add_argument("--sweep", action="store_true")
+    a = ap.parse_args()
+    res = {"env": dict(torch=torch.__version__, gpu=torch.cuda.get_device_name(0), staged=R.available())}
+    try:
+        import triton
+        res["env"]["triton"] = triton.__version__
+    except Exception as e:      # noqa: BLE001
+        res["env"]["triton"] = repr(e)
+
+    def save():
+        os.makedirs(os.path.dirname(a.out), exist_ok=True)
+        with open(a.out, "w") as f:
+            json.dump(res, f, indent=1, default=str)
+
+    if not R.available():
+        res["error"] = "oracle/_ref is not staged"
+        save()
+        print(json.dumps(res))
+        return
+    dev = "cuda"
+    fla = R.triton_kernels()
+
+    def case(B, H, L, D, blk, iters, with_highlevel):
+        out = {}
+        g = torch.Generator(device=dev).manual_seed(0)
+        q, k, v = [(torch.randn(B, H, L, D, device=dev, generator=g) * 0.5).to(torch.bfloat16).requires_grad_(True)
+                   for _ in range(3)]
+        do = torch.randn(B, H, L, D, device=dev, generator=g).to(torch.bfloat16)
+        is_mem = torch.arange(L, device=dev) % blk == blk - 1
+        ff, ft = flops(B, H, L, D)
+
+        def t_fwd():
+            with torch.no_grad():
+                return fla.fused_landmark_attention(q, k, v, is_mem, block_size=blk)
+
+        def t_fb():
+            o = fla.fused_landmark_attention(q, k, v, is_mem, block_size=blk)
+            return torch.autograd.grad(o, [q, k, v], do)
+
+        try:
+            t0 = time.perf_counter()
+            o = fla.fused_landmark_attention(q, k, v, is_mem, block_size=blk)
+            gr = torch.autograd.grad(o, [q, k, v], do)
+            torch.cuda.synchronize()
+            out["first_call_s"] = time.perf_counter() - t0
+            if with_highlevel:
+                qf, kf, vf = [t.detach().float() for t in (q, k, v)]
+                exp = R.highlevel_fwd_bwd(qf[:, :4], kf[:, :4], vf[:, :4], do.float()[:, :4], blk)
+                got = (o[:, :4], gr[0][:, :4], gr[1][:, :4], gr[2][:, :4])
+                out["triton_bf16_vs_highlevel_fp32_max_abs_4_heads"] = {
+                    n: (x.float() - e).abs().max().item() for n, x, e in zip(("out", "dq", "dk", "dv"), got, exp)}
+            r = cuda_time(t_fwd, 3, iters)
+            r["tflops_at_median"] = ff / (r["ms_median"] * 1e-3) / 1e12
+            out["triton_fwd"] = r
+            r = cuda_time(t_fb, 3, iters)
+            r["tflops_at_median"] = ft / (r["ms_median"] * 1e-3) / 1e12
+            out["triton_fwd_bwd"] = r
+        except Exception:       # noqa: BLE001
+            out["triton_error"] = traceback.format_exc()[-2000:]
+        if with_highlevel:
+            try:
+                def t_hi():
+                    o = R.highlevel_attention(q, k, v, blk)
+                    return torch.autograd.grad(o, [q, k, v], do)
+                r = cuda_time(t_hi, 2, 5)
+                r["tflops_at_median"] = ft / (r["ms_median"] * 1e-3) / 1e12
+                out["highlevel_bf16_gpu_fwd_bwd"] = r
+            except Exception:   # noqa: BLE001
+                out["highlevel_error"] = traceback.format_exc()[-2000:]
+            try:
+                def t_sdpa():
+                    o = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+                    return torch.autograd.grad(o, [q, k, v], do)
+                r = cuda_time(t_sdpa, 3, iters)
+                r["tflops_at_median"] = ft / (r["ms_median"] * 1e-3) / 1e12
+                out["torch_sdpa_causal_fwd_bwd"] = r
+            except Exception:   # noqa: BLE001
+                out["sdpa_error"] = traceback.format_exc()[-2000:]
+        return out
+
+    res["B1_H32_L2048_D128_bf16"] = case(1, 32, 2048, 128, 64, 10, True)
+    save()
+    print(json.dumps(res["B1_H32_L2048_D128_bf16"]), flush=True)
+    if a.sweep:
+        for L in (4096, 8192):
+            res[f"B1_H32_L{L}_D128_bf16"] = case(1, 32, L, 128, 64, 3, False)
+            save()
+            print(L, json.dumps(res[f"B1_H32_L{L}_D128_bf16"]), flush=True)
+    save()
+
+
+if __name__ == "__main__":
+    main()

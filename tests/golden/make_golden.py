@@ -283,7 +283,7 @@ def gen_llama_retrieval(llama_mem, LlamaLandmarkConfig):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("LMK_REFERENCE_CHECKOUT", ""))
     ap.add_argument("--only", default="")
     a = ap.parse_args()
     sys.path.insert(0, os.path.join(a.reference, "llama"))

@@ -73,8 +73,17 @@ def test_scores_and_gather_llama_layout(dtype):
     mem_pos, _ = O.llama_slot_positions(nblk, top_k, C, blk)
     lm = O.rotary_half_split(pk.view(B, H, nblk, blk, D)[:, :, :, blk - 1], mem_pos.view(1, 1, nblk))
     exp = torch.matmul(q.float(), lm.float().transpose(2, 3)) / math.sqrt(D)
+    # Against the fp32-rotation oracle a bf16 run may differ by up to ~5e-2: the reference (and the kernel, on
+    # purpose) rotates the landmark keys in bf16 -- x*cos + rotate_half(x)*sin with bf16 tables is three bf16
+    # roundings per element -- before a 64-term dot product of N(0,1) values.  The 2e-2 bound of the attention
+    # outputs does not apply to raw scores; the tight check is the next one.
     tol = 1e-4 if dtype == torch.float32 else 6e-2
     assert (scores.cpu() - exp).abs().max().item() < tol
+    # same arithmetic as the reference in this dtype: keys rotated by torch on the same tables, then an fp32 dot product
+    from landmark_attention_b200.retrieval import apply_rotary_half as rot_same
+    lm_same = rot_same(pk.view(B, H, nblk, blk, D)[:, :, :, blk - 1], cos.cpu(), sin.cpu(), mem_pos.view(1, 1, nblk))
+    exp_same = torch.matmul(q.float(), lm_same.float().transpose(2, 3)) / math.sqrt(D)
+    assert (scores.cpu() - exp_same).abs().max().item() < (1e-4 if dtype == torch.float32 else 2e-3)
     sel = P.topk_sorted(scores, top_k)
     assert torch.equal(sel.long(), scores.topk(top_k, dim=-1).indices.sort(dim=-1).values)
     sk, sv = P.gather_kv(pkc, pvc, desc, desc, sel, cos, sin, L.ROTARY_HALF)

@@ -60,10 +60,12 @@ def test_two_rank_plumbing_over_gloo(tmp_path):
 def test_reference_arm_prints_one_line_from_rank0():
     res = _run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                 "--master-addr", "127.0.0.1", "--master-port", "29542", "bench.py", "--impl", "reference",
-                "--gpus", "2", "--steps", "1", "--warmup", "0"], {"LMK_BENCH_CPU_HEADS": "1"})
+                "--gpus", "2", "--steps", "1", "--warmup", "0"],
+               {"LMK_BENCH_CPU_HEADS": "1", "LMK_BENCH_SKIP_CONFIG1": "1"})
     assert res.returncode == 0, res.stderr[-2000:]
     lines = [l for l in res.stdout.splitlines() if l.startswith("{")]
     assert len(lines) == 1
     d = json.loads(lines[0])
     assert d["impl"] == "reference" and d["unit"] == "TFLOP/s" and d["value"] > 0
-    assert d["cpu_baseline"]["kind"] == "port" and d["e2e"]["h2d_bytes_per_step"] == 0
+    # "reference" where oracle/_ref has been staged from a checkout (oracle/make_ref.py), else the restatement
+    assert d["cpu_baseline"]["kind"] in ("reference", "port") and d["e2e"]["h2d_bytes_per_step"] == 0

@@ -75,3 +75,20 @@ def test_static_scratch_rejects_oversized_problems_without_launching():
                                  64, 0.1, L.LMK_BF16, P.PATH_GENERAL, None)
     assert rc == L.LMK_ERR_WORKSPACE
     assert b"exceed the built-in scratch" in lib.lmk_last_error()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs a second GPU")
+def test_static_scratch_on_a_second_device():
+    # every GPU has its own copy of the built-in array; its address is looked up per device, with that device current
+    q0, k0, v0, do0 = _problem(1, 2, 256, 128, torch.bfloat16, 5)
+    first = _backward("static", q0, k0, v0, do0, P.PATH_TCGEN05)          # device 0 resolves its address first
+    with torch.cuda.device(1):
+        q, k, v, do = _problem(1, 2, 256, 128, torch.bfloat16, 5)
+        assert q.device.index == 1
+        expected = _backward("workspace", q, k, v, do, P.PATH_TCGEN05)
+        got = _backward("static", q, k, v, do, P.PATH_TCGEN05)
+        for a, b in zip(got, expected):
+            assert torch.equal(a, b)
+        assert L.device_status() == 0
+    for a, b in zip(first, got):
+        assert torch.equal(a, b.to(a.device))
