@@ -442,6 +442,7 @@ sm100_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t tmem = sm->tmem_base;
   auto tmem_s = [&](int w, int sb) { return tmem + (uint32_t)(w * 128 + sb * 64); };
   auto tmem_o = [&](int w) { return tmem + 256u + (uint32_t)w * 128u; };
+  grid_dep_launch();      // a dependent kernel (the backward pass) may do its set-up while this grid drains
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
@@ -1062,6 +1063,7 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const int tq0 = unit_tq0(pair), n_items = n_tiles - tq0;
       // the row statistics of the next item are fetched one item ahead, so their latency is never exposed
       const int64_t grow0 = (int64_t)bh * Lq + tq0 * kQTile + row;
+      if (u == 0) grid_dep_wait();     // delta comes from the dQ kernel, which may still be running (see the launch)
       float nM = M_ptr[grow0], nL = L_ptr[grow0], nDelta = delta_ptr[grow0];
       for (int i = 0; i < n_items; ++i, ++it) {
         const int tq = tq0 + i;
@@ -1139,6 +1141,11 @@ sm100_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
 // ---------------------------------------------------------------------------------------------- backward: dQ
 constexpr int kDqStages = 4;
+// The dQ kernel has a fourth single-thread role: S = Q K^T and dP = dO V^T are issued by two different threads.  With
+// the A operand in TMEM an N = 64 product needs only 32 clk of the tensor pipe, but one thread cannot issue such
+// instructions faster than one per ~45 clk; two issuers together reach the pipe's rate (measured with an issue-rate
+// microbenchmark: 44.7 clk per instruction from one thread, 32 clk per instruction from two).
+constexpr int kDqThreads = kBwdThreads + 32;
 
 struct DqSmem {
   uint64_t qdo_full;
@@ -1160,7 +1167,7 @@ struct DqSmem {
 // unit is drained by one warpgroup (the two warpgroups alternate); only the unit's first accumulating MMA waits for
 // the drain.  All barrier phases derive from counters that run across units.
 template <bool kBf16>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kDqThreads, 1)
 sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                     const __grid_constant__ CUtensorMap tm_o, const float* __restrict__ L_ptr,
@@ -1190,7 +1197,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   if (tid == 0) {
     mbar_init(smem_u32(&sm->qdo_full), 1);
     mbar_init(smem_u32(&sm->ops_ready), 256);
-    mbar_init(smem_u32(&sm->ops_free), 1);
+    mbar_init(smem_u32(&sm->ops_free), 2);          // the S issuer and the dP issuer
     mbar_init(smem_u32(&sm->delta_read), 256);
     for (int s = 0; s < kDqStages; ++s) {
       mbar_init(smem_u32(&sm->full[s]), 1);
@@ -1198,7 +1205,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_init(smem_u32(&sm->ds_ready[s]), 128);
     }
     for (int s = 0; s < kSdpBufs; ++s) {
-      mbar_init(smem_u32(&sm->sdp_full[s]), 1);
+      mbar_init(smem_u32(&sm->sdp_full[s]), 2);     // S product done + dP product done
       mbar_init(smem_u32(&sm->sdp_free[s]), 128);
     }
     mbar_init(smem_u32(&sm->acc_full[0]), 1);
@@ -1216,6 +1223,11 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   // shared memory 2 x 32 KB per block (half of the kernel's shared-memory operand traffic), and their shared-memory
   // tiles are free for the next unit's loads as soon as the prologue has copied them.
   const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dq = tmem + 256, tmem_q = tmem + 384, tmem_do = tmem + 448;
+  // Everything above (barriers, TMEM) overlapped the tail of the kernel before this one in the stream; any of this
+  // kernel's inputs may come from it, so nothing is read from global memory before this point.  The dK/dV kernel that
+  // follows may start its CTAs as SMs free up: it only depends on this kernel for `delta`.
+  grid_dep_wait();
+  grid_dep_launch();
 
   if (warp == kBwdGroups * 4) {
     if (lane == 0) {
@@ -1251,11 +1263,15 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
     }
     __syncwarp();
-  } else if (warp == kBwdGroups * 4 + 1) {
+  } else if (warp == kBwdGroups * 4 + 1 || warp == kBwdGroups * 4 + 3) {
+    // warp +1 issues S = Q K^T, warp +3 issues dP = dO V^T; both walk through the same items and wait for the same
+    // barriers (each is a waiter of its own on full / sdp_free / ops_ready and sees every phase)
     if (lane == 0) {
       constexpr uint32_t fmt = kBf16 ? 1u : 0u;
       constexpr uint32_t idesc_s = instr_desc_f16(fmt, 128, 64, 0, 0);
-      const uint64_t dk0 = smem_desc_sw128(k_slot(0), 16, 1024), dv0 = smem_desc_sw128(v_slot(0), 16, 1024);
+      const bool is_s = warp == kBwdGroups * 4 + 1;
+      const uint64_t db0 = smem_desc_sw128(is_s ? k_slot(0) : v_slot(0), 16, 1024);
+      const uint32_t t_out = is_s ? tmem_s : tmem_dp, t_a = is_s ? tmem_q : tmem_do;
       int it = 0, u = 0;
       for (int w = unit_of(0); w < n_units; w = unit_of(++u)) {
         const int total = unit_items(unit_tile(w));
@@ -1266,14 +1282,10 @@ sm100_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           if (it >= kSdpBufs)
             mbar_wait(smem_u32(&sm->sdp_free[sb]), ((it / kSdpBufs) & 1) ^ 1, &g_lmk_status, kErrDqMma);
           tc_fence_after();
-          const uint64_t dk = desc_advance(dk0, (uint32_t)s * 32768u), dv = desc_advance(dv0, (uint32_t)s * 32768u);
+          const uint64_t db = desc_advance(db0, (uint32_t)s * 32768u);
 #pragma unroll
           for (int kk = 0; kk < kD / 16; ++kk)      // A from TMEM: 8 columns = 16 features per K-step
-            mma_f16_ts(tmem_s + sb * 64, tmem_q + kk * 8, desc_advance(dk, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
-#pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk)
-            mma_f16_ts(tmem_dp + sb * 64, tmem_do + kk * 8, desc_advance(dv, kmajor_step(kk, kHalfTile)), idesc_s,
-                       kk > 0);
+            mma_f16_ts(t_out + sb * 64, t_a + kk * 8, desc_advance(db, kmajor_step(kk, kHalfTile)), idesc_s, kk > 0);
           mma_commit(smem_u32(&sm->sdp_full[sb]));
         }
         mma_commit(smem_u32(&sm->ops_free));        // the next unit's Q / dO rows may be written
@@ -1676,14 +1688,28 @@ int attn_sm100_bwd(const AttnParams& p, int dtype, cudaStream_t st) {
   const int dkv_units = ((p.Lk / kBlk + 1) / 2) * p.B * p.H;
   const int dq_units = (p.Lq / kQTile) * p.B * p.H;
   dim3 grid_dkv(dkv_units < n_sm ? dkv_units : n_sm), grid_dq(dq_units < n_sm ? dq_units : n_sm);
+  // Both launches carry the programmatic-stream-serialization attribute.  The dQ kernel waits for the kernel before it
+  // right after its set-up (only the set-up overlaps).  The dK/dV kernel reads q, k, v, dO, L, M, which were complete
+  // before the dQ kernel started, and `delta`, which the dQ kernel writes: its loads and S / dP products start on
+  // every SM the dQ kernel has left, and only its softmax threads wait (griddepcontrol.wait) before they read delta.
+  cudaLaunchAttribute pdl[1];
+  pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg_dq = {}, cfg_dkv = {};
+  cfg_dq.gridDim = grid_dq;  cfg_dq.blockDim = dim3(kDqThreads);  cfg_dq.dynamicSmemBytes = smem_dq;  cfg_dq.stream = st;
+  cfg_dq.attrs = pdl;  cfg_dq.numAttrs = 1;
+  cfg_dkv.gridDim = grid_dkv;  cfg_dkv.blockDim = dim3(kBwdThreads);  cfg_dkv.dynamicSmemBytes = smem_dkv;
+  cfg_dkv.stream = st;  cfg_dkv.attrs = pdl;  cfg_dkv.numAttrs = 1;
+  const float* Lc = p.L;
+  const float* Mc = p.M;
+  const float* deltac = delta;
+  const int BH = p.B * p.H;
 #define LMK_BWD_LAUNCH(BF)                                                                                          \
   do {                                                                                                              \
-    /* the dQ kernel also produces delta = rowsum(O * dO), which the dK/dV kernel launched after it reads */         \
-    sm100_bwd_dq_kernel<BF><<<grid_dq, kBwdThreads, smem_dq, st>>>(tq, tk, tv, tdo, to, p.L, p.M, delta, p.dq, p.H, \
-                                                                   p.B * p.H, p.Lq, p.Lk, p.scale, scale_log2);     \
-    sm100_bwd_dkv_kernel<BF><<<grid_dkv, kBwdThreads, smem_dkv, st>>>(tq, tk, tv, tdo, p.L, p.M, delta, p.dk, p.dv, \
-                                                                     p.H, p.B * p.H, p.Lq, p.Lk, p.scale,           \
-                                                                     scale_log2);                                   \
+    LMK_CUDA(cudaLaunchKernelEx(&cfg_dq, sm100_bwd_dq_kernel<BF>, tq, tk, tv, tdo, to, Lc, Mc, delta, p.dq, p.H, BH, \
+                                p.Lq, p.Lk, p.scale, scale_log2));                                                  \
+    LMK_CUDA(cudaLaunchKernelEx(&cfg_dkv, sm100_bwd_dkv_kernel<BF>, tq, tk, tv, tdo, Lc, Mc, deltac, p.dk, p.dv,    \
+                                p.H, BH, p.Lq, p.Lk, p.scale, scale_log2));                                         \
   } while (0)
   if (dtype == LMK_BF16) LMK_BWD_LAUNCH(true);
   else LMK_BWD_LAUNCH(false);

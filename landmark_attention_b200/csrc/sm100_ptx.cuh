@@ -60,6 +60,13 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ---------------------------------------------------------------------------------------------- dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before it in the
+// stream is still running; grid_dep_wait() blocks until that kernel has completed and its writes are visible (a no-op
+// without the attribute).  grid_dep_launch() lets the NEXT kernel of the stream start its CTAs as soon as SMs free up.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

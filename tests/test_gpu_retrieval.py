@@ -79,11 +79,13 @@ def test_scores_and_gather_llama_layout(dtype):
     # outputs does not apply to raw scores; the tight check is the next one.
     tol = 1e-4 if dtype == torch.float32 else 6e-2
     assert (scores.cpu() - exp).abs().max().item() < tol
-    # same arithmetic as the reference in this dtype: keys rotated by torch on the same tables, then an fp32 dot product
+    # closer to the reference's arithmetic in this dtype: keys rotated by torch on the same tables (rounded to the
+    # dtype after every step), then an fp32 dot product.  The scoring kernel keeps the rotated key in fp32 (it skips
+    # the last rounding), which leaves up to half a bf16 step on each of the 64 terms.
     from landmark_attention_b200.retrieval import apply_rotary_half as rot_same
     lm_same = rot_same(pk.view(B, H, nblk, blk, D)[:, :, :, blk - 1], cos.cpu(), sin.cpu(), mem_pos.view(1, 1, nblk))
     exp_same = torch.matmul(q.float(), lm_same.float().transpose(2, 3)) / math.sqrt(D)
-    assert (scores.cpu() - exp_same).abs().max().item() < (1e-4 if dtype == torch.float32 else 2e-3)
+    assert (scores.cpu() - exp_same).abs().max().item() < (1e-4 if dtype == torch.float32 else 1.5e-2)
     sel = P.topk_sorted(scores, top_k)
     assert torch.equal(sel.long(), scores.topk(top_k, dim=-1).indices.sort(dim=-1).values)
     sk, sv = P.gather_kv(pkc, pvc, desc, desc, sel, cos, sin, L.ROTARY_HALF)
