@@ -131,6 +131,41 @@ int lmk_attn_bwd_static(const void* q, const void* k, const void* v, const void*
                         int block, float sm_scale, int dtype, int path, void* stream);
 
 /*
+ * Fused landmark attention with landmarks at ARBITRARY key positions, forward.
+ * Replaces the attention of CausalSelfAttention.forward without cache -- scores, causal fill, the mask block, the
+ * grouped softmax and att @ v (lm_benchmark/models/landmark.py:196-236 with :210-224 and :37-119) -- in one kernel
+ * family on the tensor cores; no [B,H,Lq,Lk] tensor (scores, boolean masks, probabilities) is ever materialised.
+ *   q [B,H,Lq,D], k,v [B,H,Lk,D] (strided, already rotated), o [B,H,Lq,D] dense.
+ *   is_mem: one byte per (batch row, key), non-zero = landmark; row b starts at is_mem + b * is_mem_stride
+ *     (landmark.py:368 builds it per batch row; windows are cut at random offsets, optim/utils.py:21-26).
+ *   Causal with the query rows aligned to the end of the keys (query i sits at key position Lk - Lq + i).
+ *   R [B*H, Lq] and A [B*H, max_groups, Lq] fp32 are written for the backward pass (log2-domain normalisers of the
+ *     outer softmax and of every closed landmark group).
+ *   max_groups: upper bound on the number of landmarks before any query (the reference's max_mem_cnt - 1,
+ *     landmark.py:88-119); lmk_attn_mask_supported returns the largest value this build accepts (0: shape not
+ *     supported).  A row with more landmarks sets the device status word (lmk_device_status) and gets undefined output.
+ *   Shape contract: bf16/fp16, D = 128, Lq a multiple of 128, Lk and Lk - Lq multiples of 64, Lk <= 32768.
+ */
+int lmk_attn_mask_supported(int B, int H, int Lq, int Lk, int D, int dtype);
+int lmk_attn_mask_fwd(const void* q, const void* k, const void* v, const uint8_t* is_mem, int64_t is_mem_stride,
+                      void* o, float* R, float* A, int B, int H, int Lq, int Lk, int D,
+                      const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                      int max_groups, float sm_scale, int dtype, void* stream);
+
+/*
+ * Backward of lmk_attn_mask_fwd (what autograd derives for lm_benchmark/models/landmark.py:196-236 through
+ * LandmarkGroupedSoftmaxFunction.backward, :66-86).  o, dO, dQ dense [B,H,Lq,D]; dK, dV dense [B,H,Lk,D]; R, A from
+ * the forward call; workspace >= lmk_attn_mask_bwd_workspace(...) bytes, 256-byte aligned, contents irrelevant.
+ */
+size_t lmk_attn_mask_bwd_workspace(int B, int H, int Lq, int max_groups);
+int lmk_attn_mask_bwd(const void* q, const void* k, const void* v, const uint8_t* is_mem, int64_t is_mem_stride,
+                      const void* o, const void* dO, const float* R, const float* A,
+                      void* dQ, void* dK, void* dV, void* workspace, size_t workspace_bytes,
+                      int B, int H, int Lq, int Lk, int D,
+                      const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                      int max_groups, float sm_scale, int dtype, void* stream);
+
+/*
  * Stand-alone landmark grouped softmax over the last dimension of x [B,H,Lq,Lk].
  * Replaces LandmarkGroupedSoftmaxFunction.forward + landmark_grouped_softmax
  *   (llama/llama_mem.py:168-243; lm_benchmark/models/landmark.py:37-119).

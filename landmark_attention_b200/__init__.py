@@ -9,6 +9,7 @@ from .fused import (FusedLandmarkAttention, attn_forward_with_stats, fused_landm
 from .host_pipeline import HostAttentionPipeline  # noqa: F401
 from .grouped_softmax import (landmark_grouped_softmax, landmark_grouped_softmax_lm,  # noqa: F401
                               lm_landmark_attention, prepare_landmark_masks)
+from .masked import landmark_attention_masked, masked_attention_supported  # noqa: F401
 from .mem_cache import MemLMCache, MemLMCacheStorage  # noqa: F401
 from .retrieval import (gather_kv, landmark_scores, llama_retrieval_attention, make_desc,  # noqa: F401
                         rotary_tables_half, rotary_tables_interleaved, selected_logits, selected_pv, topk_sorted)

@@ -44,6 +44,14 @@ PROTOTYPES = {
     "lmk_attn_bwd_static": (c_int, [c_void_p] * 10 + [c_int, c_int, c_int, c_int, c_int,
                                                       POINTER(c_int64), POINTER(c_int64), POINTER(c_int64),
                                                       c_int, c_float, c_int, c_int, c_void_p]),
+    "lmk_attn_mask_supported": (c_int, [c_int] * 6),
+    "lmk_attn_mask_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                  c_int, c_int, c_int, c_int, c_int, POINTER(c_int64), POINTER(c_int64),
+                                  POINTER(c_int64), c_int, c_float, c_int, c_void_p]),
+    "lmk_attn_mask_bwd_workspace": (c_size_t, [c_int] * 4),
+    "lmk_attn_mask_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64] + [c_void_p] * 7 +
+                          [c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int, POINTER(c_int64), POINTER(c_int64),
+                           POINTER(c_int64), c_int, c_float, c_int, c_void_p]),
     "lmk_grouped_softmax_fwd": (c_int, [c_void_p, POINTER(c_int64), c_void_p, POINTER(c_int64), c_void_p,
                                         POINTER(c_int64), c_void_p, POINTER(c_int64), c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),

@@ -196,3 +196,65 @@ extern "C" int lmk_attn_bwd_static(const void* q, const void* k, const void* v, 
   return lmk_attn_bwd(q, k, v, o, dO, L, M, dQ, dK, dV, scratch, sizeof(float) * (size_t)LMK_STATIC_SCRATCH_FLOATS, B,
                       H, Lq, Lk, D, q_strides, k_strides, v_strides, block, sm_scale, dtype, path, stream);
 }
+
+// ------------------------------------------------------------------------------------------------ arbitrary landmarks
+namespace {
+int check_mask_common(const void* q, const void* k, const void* v, const uint8_t* is_mem, int B, int H, int Lq, int Lk,
+                      int D, const int64_t* qs, const int64_t* ks, const int64_t* vs, int max_groups, int dtype) {
+  LMK_CHECK_ARG(q && k && v && is_mem, "masked attention: q, k, v or is_mem is null");
+  LMK_CHECK_ARG(qs && ks && vs, "masked attention: stride arrays are required");
+  LMK_CHECK_ARG(B >= 1 && H >= 1 && Lq >= 1 && Lk >= Lq, "masked attention: bad sizes (B=%d H=%d Lq=%d Lk=%d)", B, H, Lq, Lk);
+  LMK_CHECK_ARG((int64_t)B * H <= 65535, "masked attention: B*H = %lld exceeds 65535", (long long)B * H);
+  LMK_CHECK_ARG(max_groups >= 1, "masked attention: max_groups must be positive");
+  if (!attn_mask_sm100_supported(B, H, Lq, Lk, D, dtype))
+    return fail(LMK_ERR_UNSUPPORTED,
+                "masked attention needs bf16/fp16, D=128, Lq a multiple of 128, Lk and Lk-Lq multiples of 64, Lk <= 32768 "
+                "(got dtype=%d D=%d Lq=%d Lk=%d)", dtype, D, Lq, Lk);
+  if (max_groups > attn_mask_sm100_max_groups())
+    return fail(LMK_ERR_UNSUPPORTED, "masked attention keeps statistics for at most %d landmark groups per row (got %d)",
+                attn_mask_sm100_max_groups(), max_groups);
+  return LMK_OK;
+}
+}  // namespace
+
+extern "C" int lmk_attn_mask_supported(int B, int H, int Lq, int Lk, int D, int dtype) {
+  return attn_mask_sm100_supported(B, H, Lq, Lk, D, dtype) ? attn_mask_sm100_max_groups() : 0;
+}
+
+extern "C" int lmk_attn_mask_fwd(const void* q, const void* k, const void* v, const uint8_t* is_mem,
+                                 int64_t is_mem_stride, void* o, float* R, float* A, int B, int H, int Lq, int Lk, int D,
+                                 const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                                 int max_groups, float sm_scale, int dtype, void* stream) {
+  int rc = check_mask_common(q, k, v, is_mem, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, max_groups, dtype);
+  if (rc != LMK_OK) return rc;
+  LMK_CHECK_ARG(o && R && A, "attn_mask_fwd: o, R or A is null");
+  AttnParams p{};
+  fill(p, q, k, v, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, 0, sm_scale);
+  p.o = o;
+  return attn_mask_sm100_fwd(p, is_mem, is_mem_stride, R, A, max_groups, dtype, (cudaStream_t)stream);
+}
+
+extern "C" size_t lmk_attn_mask_bwd_workspace(int B, int H, int Lq, int max_groups) {
+  if (B < 1 || H < 1 || Lq < 1 || max_groups < 1) return 0;
+  return attn_mask_sm100_bwd_workspace(B, H, Lq, max_groups);
+}
+
+extern "C" int lmk_attn_mask_bwd(const void* q, const void* k, const void* v, const uint8_t* is_mem,
+                                 int64_t is_mem_stride, const void* o, const void* dO, const float* R, const float* A,
+                                 void* dQ, void* dK, void* dV, void* workspace, size_t workspace_bytes, int B, int H,
+                                 int Lq, int Lk, int D, const int64_t q_strides[3], const int64_t k_strides[3],
+                                 const int64_t v_strides[3], int max_groups, float sm_scale, int dtype, void* stream) {
+  int rc = check_mask_common(q, k, v, is_mem, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, max_groups, dtype);
+  if (rc != LMK_OK) return rc;
+  LMK_CHECK_ARG(o && dO && R && A && dQ && dK && dV, "attn_mask_bwd: null tensor pointer");
+  const size_t need = attn_mask_sm100_bwd_workspace(B, H, Lq, max_groups);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(LMK_ERR_WORKSPACE, "attn_mask_bwd: workspace of %zu bytes required, %zu given", need, workspace_bytes);
+  LMK_CHECK_ARG(((uintptr_t)workspace & 255) == 0, "attn_mask_bwd: workspace must be 256-byte aligned");
+  AttnParams p{};
+  fill(p, q, k, v, B, H, Lq, Lk, D, q_strides, k_strides, v_strides, 0, sm_scale);
+  p.o = const_cast<void*>(o); p.dO = dO;
+  p.dq = dQ; p.dk = dK; p.dv = dV;
+  p.workspace = workspace; p.workspace_bytes = workspace_bytes;
+  return attn_mask_sm100_bwd(p, is_mem, is_mem_stride, R, A, max_groups, dtype, (cudaStream_t)stream);
+}

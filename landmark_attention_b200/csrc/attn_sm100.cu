@@ -1626,6 +1626,12 @@ bool attn_sm100_operands_ok(const AttnParams& p, bool backward) {
 
 void attn_sm100_set_max_ctas(int n) { g_max_ctas.store(n > 0 ? n : 0); }
 
+int tensor_map_4d(CUtensorMap* m, const void* ptr, int dtype, int B, int H, int L, const int64_t st[3], int box_rows) {
+  bind_context();
+  return make_map_4d(m, ptr, dtype, B, H, L, st, box_rows);
+}
+bool tensor_map_operand_ok(const void* p, const int64_t st[3]) { return tma_ok(p, st); }
+
 int attn_sm100_fwd(const AttnParams& p, int dtype, cudaStream_t st) {
   if (!tma_ok(p.q, p.qs) || !tma_ok(p.k, p.ks) || !tma_ok(p.v, p.vs))
     return fail(LMK_ERR_UNSUPPORTED, "tcgen05 path needs 16-byte aligned q/k/v with strides that are multiples of 8");

@@ -124,11 +124,18 @@ def prepare_landmark_masks(is_mem_row, attn_mask):
 
 def lm_landmark_attention(q, k, v, is_mem_row, sm_scale=None, max_groups=None):
     """Attention of lm_benchmark's CausalSelfAttention.forward without cache (landmark.py:196-236): q, k rotated,
-    landmarks at arbitrary per-row positions is_mem_row [B, T].  QK^T and PV are library matmuls; the grouped softmax
-    is this package's kernel."""
+    landmarks at arbitrary per-row positions is_mem_row [B, T].
+
+    bf16/fp16 with head dim 128 and T a multiple of 128 runs as ONE fused operator on the tensor cores
+    (masked.landmark_attention_masked: no score, mask or probability tensor exists).  Other shapes and fp32 use the
+    unfused route: library matmuls around this package's grouped-softmax kernel, masks as broadcast views."""
+    from .masked import DEFAULT_MAX_GROUPS, landmark_attention_masked, masked_attention_supported
     B, H, T, D = q.shape
     if sm_scale is None:
         sm_scale = 1.0 / (D ** 0.5)
+    fused_groups = DEFAULT_MAX_GROUPS if max_groups is None else int(max_groups)
+    if masked_attention_supported(q, k, fused_groups):
+        return landmark_attention_masked(q, k, v, is_mem_row, sm_scale, fused_groups)
     att = torch.matmul(q, k.transpose(-2, -1)) * sm_scale
     hidden = torch.ones(T, T, dtype=torch.bool, device=q.device).triu(1)
     mask, is_mem, last = prepare_landmark_masks(is_mem_row, hidden)
