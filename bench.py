@@ -376,6 +376,78 @@ def bench_grouped_softmax(P, L, dev, peaks):
             "shapes": res}
 
 
+def bench_config3(P, L, world, rank, local, dev, args, peaks):
+    """BASELINE config 3: (a) the fused arbitrary-landmark attention operator alone at B=16 H=8 T=512 D=128 with a
+    landmark every 51 tokens at random window offsets, forward + backward, next to the unfused route (library matmuls
+    around the grouped-softmax kernel); (b) one optimizer step of the 12-layer landmark GPT, data-parallel over the
+    ranks with NCCL gradient all-reduce, in tokens/s."""
+    import bench_lm
+    cfg = dict(bench_lm.CONFIG)
+    B, H, T, D = cfg["batch_size"], cfg["n_head"], cfg["sequence_length"], cfg["n_embd"] // cfg["n_head"]
+    res = {}
+    g = torch.Generator(device=dev).manual_seed(31 + rank)
+    q, k, v = [(torch.randn(B, H, T, D, generator=g, device=dev) * 0.5).to(torch.bfloat16).requires_grad_(True)
+               for _ in range(3)]
+    do = torch.randn(B, H, T, D, generator=g, device=dev).to(torch.bfloat16)
+    gh = torch.Generator().manual_seed(32 + rank)
+    offs = torch.randint(0, 51, (B,), generator=gh)
+    is_mem = ((torch.arange(T).view(1, T) + offs.view(B, 1)) % 51 == 50).to(dev)
+    mg = cfg["max_groups_for_softmax"]
+
+    def fused():
+        o = P.landmark_attention_masked(q, k, v, is_mem, max_groups=mg)
+        return torch.autograd.grad(o, [q, k, v], do)
+
+    def unfused():
+        att = torch.matmul(q, k.transpose(-2, -1)) * (D ** -0.5)
+        hidden = torch.ones(T, T, dtype=torch.bool, device=dev).triu(1)
+        mask, im, last = P.prepare_landmark_masks(is_mem, hidden)
+        att = att.masked_fill(mask, float("-inf"))
+        probs, _ = P.landmark_grouped_softmax_lm(att, -1, im, mask, last, False, mg)
+        o = torch.matmul(probs.to(v.dtype), v)
+        return torch.autograd.grad(o, [q, k, v], do)
+
+    def time_it(fn, n=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    fl = attn_flops(B, H, T, D)
+    t_f, t_u = time_it(fused), time_it(unfused)
+    res["config3_attention"] = {
+        "workload": "B=16 H=8 T=512 D=128 bf16, landmark every 51 tokens at random window offsets, fwd+bwd, public API, eager",
+        "fused_ms": t_f, "tflops": fl / (t_f * 1e-3) / 1e12, "frac_of_bf16_peak": fl / (t_f * 1e-3) / 1e12 / peaks["bf16_tflops"],
+        "unfused_ms": t_u, "unfused_what": "torch.matmul + grouped-softmax kernel on a materialised [16,8,512,512] tensor + torch.matmul",
+        "flops": "7*B*H*T^2*D", "kernel_launches_per_call": 3}
+    del q, k, v, do
+    torch.manual_seed(5)               # same initial weights on every rank (DDP broadcasts rank 0's anyway)
+    model = bench_lm.LandmarkGPT(cfg, P.lm_landmark_attention).to(dev)
+    n_params = sum(p.numel() for p in model.parameters())
+    if world > 1:
+        from torch.nn.parallel import DistributedDataParallel as DDP
+        model = DDP(model, device_ids=[local])
+    steps = max(3, min(args.steps, 10))
+    out = bench_lm.train_step_bench(model, cfg, world, rank, dev, steps, 3, barrier, max_over_ranks)
+    res["config3"] = {
+        "metric": "training tokens/s of the 12-layer landmark GPT (n_embd 1024, 8 heads, seq 512, batch 16/GPU, bf16 autocast)",
+        "value": out["tokens_per_s"], "unit": "tokens/s", "ms_per_step": out["ms_per_step"], "steps": steps,
+        "n_gpus": world, "parallelism": f"dp{world}" + (" (NCCL gradient all-reduce through DistributedDataParallel)" if world > 1 else ""),
+        "params": n_params, "allreduce_bytes_per_step": 4 * n_params if world > 1 else 0,
+        "loss_first": out["loss_first"], "loss_last": out["loss_last"], "data": "synthetic (uniform ids, landmark every 50 tokens)",
+        "attention": "lmk::masked_attention (fused tcgen05 kernels, no [B,H,T,T] tensor)",
+        "h2d_bytes_per_step": out["h2d_bytes_per_step"], "d2h_bytes_per_step": out["d2h_bytes_per_step"]}
+    del model
+    torch.cuda.empty_cache()
+    return res
+
+
 def run_ours(args, world, rank, local):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: this package has no CPU path")
@@ -492,6 +564,10 @@ def run_ours(args, world, rank, local):
         sweep = bench_sweep(P, world, rank, dev, peaks)
         if rank == 0:
             extra["sweep"] = sweep
+    if not args.no_config3:
+        c3 = bench_config3(P, L, world, rank, local, dev, args, peaks)
+        if rank == 0:
+            extra.update(c3)
     if rank == 0 and not args.no_retrieval:
         extra.update(bench_retrieval(P, L, dev, peaks))
     if rank == 0 and not args.no_grouped_softmax:
@@ -650,6 +726,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-strong", action="store_true")
     ap.add_argument("--no-grouped-softmax", action="store_true")
+    ap.add_argument("--no-config3", action="store_true")
     args = ap.parse_args()
     world, rank, local = dist_setup(args.gpus, cpu_only=args.impl == "reference")
     try:

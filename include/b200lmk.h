@@ -281,6 +281,24 @@ int lmk_selected_logits(const void* q, const void* k_cache, const lmk_cache_desc
 int lmk_selected_pv(const void* probs, int64_t ld, int64_t col0, const void* v_cache, const lmk_cache_desc* vdesc,
                     const int32_t* idx, void* out, int B, int H, int T, int D, int dtype, void* stream);
 
+/*
+ * Attention over the selected blocks in ONE kernel, merged with the attention over the local keys: replaces the
+ * gather + rotary + q k^T of llama/llama_mem.py:386-404, the prefix columns of the grouped softmax (:415-420, 462-466)
+ * and the prefix value product (:468-474) without writing logits or probabilities to memory.
+ *   Every selected block is a closed landmark group: its rows 0..block-2 share the probability of its landmark (row
+ *   block-1), split by a softmax inside the block; the landmark rows themselves carry no value weight.
+ *   o_local [B,H,local_rows,D] (dtype) and R_local [B*H, local_rows] (fp32), local_rows >= T, of which rows 0..T-1 are
+ *   read: the attention output over the local keys normalised on its own, and log2 of its share of the outer softmax
+ *   (what lmk_attn_mask_fwd writes as o and R, possibly for a query count padded to its tile size).  Both NULL:
+ *   attention over the selected blocks alone.
+ *   out [B,H,T,D] dense = (2^R o_local + sum_i 2^(x_i) o_i) / (2^R + sum_i 2^(x_i)), x_i the landmark logits (log2
+ *   domain), o_i the in-block softmax-weighted value sums.  q, caches, idx, rotary arguments as for lmk_selected_logits.
+ */
+int lmk_selected_attend(const void* q, const void* k_cache, const lmk_cache_desc* kdesc, const void* v_cache,
+                        const lmk_cache_desc* vdesc, const int32_t* idx, const void* cos_table, const void* sin_table,
+                        int n_pos, int rotary, const void* o_local, const float* R_local, int64_t local_rows, void* out,
+                        int B, int H, int T, int D, float sm_scale, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

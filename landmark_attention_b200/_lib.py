@@ -70,6 +70,9 @@ PROTOTYPES = {
     "lmk_selected_logits": (c_int, [c_void_p, c_void_p, POINTER(CacheDesc), c_void_p, c_void_p, c_void_p, c_int,
                                     c_int, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_float, c_int,
                                     c_void_p]),
+    "lmk_selected_attend": (c_int, [c_void_p, c_void_p, POINTER(CacheDesc), c_void_p, POINTER(CacheDesc), c_void_p,
+                                    c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_int,
+                                    c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "lmk_selected_pv": (c_int, [c_void_p, c_int64, c_int64, c_void_p, POINTER(CacheDesc), c_void_p, c_void_p, c_int,
                                 c_int, c_int, c_int, c_int, c_void_p]),
 }

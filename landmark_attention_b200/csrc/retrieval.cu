@@ -429,6 +429,92 @@ __device__ __forceinline__ void ld16(const void* p, uint32_t (&w)[4]) {
   w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
 }
 
+// This lane's share of q . rot(k_row): `krow` points at the lane's 16-byte vector of the low half of the row (its partner
+// vector of the high half is HALF elements further), cr / sr at the same vectors of the cos / sin rows of the key's position.
+// 16-bit types rotate on packed pairs with the rounding steps of the gather kernel; the dot product accumulates in fp32.
+template <typename T, int VEC>
+__device__ __forceinline__ float rotated_row_dot(const T* krow, const T* cr, const T* sr, int HALF, int rotary,
+                                                 const float (&q0)[VEC], const float (&q1)[VEC]) {
+  float acc0 = 0.f, acc1 = 0.f;
+    if constexpr (sizeof(T) == 2) {
+      uint32_t xl[4], xh[4];
+      ld16(krow, xl);
+      ld16(krow + HALF, xh);
+      if (rotary != LMK_ROTARY_NONE) {
+        uint32_t cl[4], ch[4], sl[4], sh[4], pl[4], ph[4];
+        ld16(cr, cl);
+        ld16(cr + HALF, ch);
+        ld16(sr, sl);
+        ld16(sr + HALF, sh);
+        if (rotary == LMK_ROTARY_HALF) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {        // rotate_half: (-x[d + D/2], x[d])
+            pl[u] = xh[u] ^ 0x80008000u;
+            ph[u] = xl[u];
+          }
+        } else {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {        // interleaved pairs: (x0, x1) -> (-x1, x0)
+            pl[u] = __byte_perm(xl[u], xl[u], 0x1032) ^ 0x00008000u;
+            ph[u] = __byte_perm(xh[u], xh[u], 0x1032) ^ 0x00008000u;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          xl[u] = Packed<T>::add(Packed<T>::mul(xl[u], cl[u]), Packed<T>::mul(pl[u], sl[u]));
+          xh[u] = Packed<T>::add(Packed<T>::mul(xh[u], ch[u]), Packed<T>::mul(ph[u], sh[u]));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float f0, f1, g0, g1;
+        Packed<T>::to_f32(xl[u], f0, f1);
+        Packed<T>::to_f32(xh[u], g0, g1);
+        acc0 = fmaf(q0[2 * u], f0, acc0);
+        acc1 = fmaf(q0[2 * u + 1], f1, acc1);
+        acc0 = fmaf(q1[2 * u], g0, acc0);
+        acc1 = fmaf(q1[2 * u + 1], g1, acc1);
+      }
+    } else {
+      float xl[VEC], xh[VEC];
+      load_vec_f32<T, VEC>(krow, xl);
+      load_vec_f32<T, VEC>(krow + HALF, xh);
+      if (rotary != LMK_ROTARY_NONE) {
+        float cl[VEC], ch[VEC], sl[VEC], sh[VEC], ol[VEC], oh[VEC];
+        load_vec_f32<T, VEC>(cr, cl);
+        load_vec_f32<T, VEC>(cr + HALF, ch);
+        load_vec_f32<T, VEC>(sr, sl);
+        load_vec_f32<T, VEC>(sr + HALF, sh);
+        if (rotary == LMK_ROTARY_HALF) {
+#pragma unroll
+          for (int u = 0; u < VEC; ++u) {
+            ol[u] = __fadd_rn(__fmul_rn(xl[u], cl[u]), __fmul_rn(-xh[u], sl[u]));
+            oh[u] = __fadd_rn(__fmul_rn(xh[u], ch[u]), __fmul_rn(xl[u], sh[u]));
+          }
+        } else {
+#pragma unroll
+          for (int u = 0; u < VEC; u += 2) {
+            ol[u] = __fadd_rn(__fmul_rn(xl[u], cl[u]), __fmul_rn(-xl[u + 1], sl[u]));
+            ol[u + 1] = __fadd_rn(__fmul_rn(xl[u + 1], cl[u + 1]), __fmul_rn(xl[u], sl[u + 1]));
+            oh[u] = __fadd_rn(__fmul_rn(xh[u], ch[u]), __fmul_rn(-xh[u + 1], sh[u]));
+            oh[u + 1] = __fadd_rn(__fmul_rn(xh[u + 1], ch[u + 1]), __fmul_rn(xh[u], sh[u + 1]));
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) {
+          xl[u] = ol[u];
+          xh[u] = oh[u];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < VEC; ++u) {
+        acc0 = fmaf(q0[u], xl[u], acc0);
+        acc1 = fmaf(q1[u], xh[u], acc1);
+      }
+    }
+  return acc0 + acc1;
+}
+
 template <typename T, int LPR>
 __global__ void __launch_bounds__(128, kSelMinBlocks) selected_logits_kernel(const T* __restrict__ q, const T* __restrict__ kc,
                                                               lmk_cache_desc kd, const int32_t* __restrict__ idx,
@@ -464,90 +550,13 @@ __global__ void __launch_bounds__(128, kSelMinBlocks) selected_logits_kernel(con
 #pragma unroll kSelUnroll
     for (int r0 = 0; r0 < blk; r0 += RPS) {
       const int r = r0 + rsub;
-      float acc0 = 0.f, acc1 = 0.f;
+      float acc = 0.f;
       if (r < blk) {
         const T* krow = ksrc + (int64_t)r * kd.stride_row;
         const int pos = max(0, min(pos0 + r, n_pos - 1));
-        const T* cr = cos_t + (int64_t)pos * D + d0;
-        const T* sr = sin_t + (int64_t)pos * D + d0;
-        if constexpr (sizeof(T) == 2) {
-          uint32_t xl[4], xh[4];
-          ld16(krow, xl);
-          ld16(krow + HALF, xh);
-          if (rotary != LMK_ROTARY_NONE) {
-            uint32_t cl[4], ch[4], sl[4], sh[4], pl[4], ph[4];
-            ld16(cr, cl);
-            ld16(cr + HALF, ch);
-            ld16(sr, sl);
-            ld16(sr + HALF, sh);
-            if (rotary == LMK_ROTARY_HALF) {
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {        // rotate_half: (-x[d + D/2], x[d])
-                pl[u] = xh[u] ^ 0x80008000u;
-                ph[u] = xl[u];
-              }
-            } else {
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {        // interleaved pairs: (x0, x1) -> (-x1, x0)
-                pl[u] = __byte_perm(xl[u], xl[u], 0x1032) ^ 0x00008000u;
-                ph[u] = __byte_perm(xh[u], xh[u], 0x1032) ^ 0x00008000u;
-              }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              xl[u] = Packed<T>::add(Packed<T>::mul(xl[u], cl[u]), Packed<T>::mul(pl[u], sl[u]));
-              xh[u] = Packed<T>::add(Packed<T>::mul(xh[u], ch[u]), Packed<T>::mul(ph[u], sh[u]));
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float f0, f1, g0, g1;
-            Packed<T>::to_f32(xl[u], f0, f1);
-            Packed<T>::to_f32(xh[u], g0, g1);
-            acc0 = fmaf(q0[2 * u], f0, acc0);
-            acc1 = fmaf(q0[2 * u + 1], f1, acc1);
-            acc0 = fmaf(q1[2 * u], g0, acc0);
-            acc1 = fmaf(q1[2 * u + 1], g1, acc1);
-          }
-        } else {
-          float xl[VEC], xh[VEC];
-          load_vec_f32<T, VEC>(krow, xl);
-          load_vec_f32<T, VEC>(krow + HALF, xh);
-          if (rotary != LMK_ROTARY_NONE) {
-            float cl[VEC], ch[VEC], sl[VEC], sh[VEC], ol[VEC], oh[VEC];
-            load_vec_f32<T, VEC>(cr, cl);
-            load_vec_f32<T, VEC>(cr + HALF, ch);
-            load_vec_f32<T, VEC>(sr, sl);
-            load_vec_f32<T, VEC>(sr + HALF, sh);
-            if (rotary == LMK_ROTARY_HALF) {
-#pragma unroll
-              for (int u = 0; u < VEC; ++u) {
-                ol[u] = __fadd_rn(__fmul_rn(xl[u], cl[u]), __fmul_rn(-xh[u], sl[u]));
-                oh[u] = __fadd_rn(__fmul_rn(xh[u], ch[u]), __fmul_rn(xl[u], sh[u]));
-              }
-            } else {
-#pragma unroll
-              for (int u = 0; u < VEC; u += 2) {
-                ol[u] = __fadd_rn(__fmul_rn(xl[u], cl[u]), __fmul_rn(-xl[u + 1], sl[u]));
-                ol[u + 1] = __fadd_rn(__fmul_rn(xl[u + 1], cl[u + 1]), __fmul_rn(xl[u], sl[u + 1]));
-                oh[u] = __fadd_rn(__fmul_rn(xh[u], ch[u]), __fmul_rn(-xh[u + 1], sh[u]));
-                oh[u + 1] = __fadd_rn(__fmul_rn(xh[u + 1], ch[u + 1]), __fmul_rn(xh[u], sh[u + 1]));
-              }
-            }
-#pragma unroll
-            for (int u = 0; u < VEC; ++u) {
-              xl[u] = ol[u];
-              xh[u] = oh[u];
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < VEC; ++u) {
-            acc0 = fmaf(q0[u], xl[u], acc0);
-            acc1 = fmaf(q1[u], xh[u], acc1);
-          }
-        }
+        acc = rotated_row_dot<T, VEC>(krow, cos_t + (int64_t)pos * D + d0, sin_t + (int64_t)pos * D + d0, HALF, rotary,
+                                      q0, q1);
       }
-      float acc = acc0 + acc1;
 #pragma unroll
       for (int o = LP / 2; o >= 1; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (sub == 0 && r < blk) out_row[(int64_t)i * blk + r] = from_f32<T>(acc);
@@ -600,6 +609,119 @@ __global__ void __launch_bounds__(128) selected_pv_kernel(const T* __restrict__ 
     float sum = 0.f;
     for (int g = 0; g < groups; ++g) sum += red[g * D + d];
     out[((int64_t)bh * Tq + t) * D + d] = from_f32<T>(sum);
+  }
+}
+
+// Attention over the selected blocks, fused with the merge into the attention over the local keys: nothing between
+// the block reads and the final output goes through global memory (no logits, no probabilities).  One CTA per
+// (token, batch*head); warp i takes selected block i (then i + 4, ...):
+//   logits of the block's rows (keys rotated at their slot positions, read in place) -> softmax over the block's
+//   non-landmark rows and the landmark logit x_i (log2 domain) -> o_i = sum_r s_r V[r]  (all in shared memory / registers)
+// and then all threads combine, with R the log2 of the local keys' share of the outer softmax:
+//   out = (2^(R - m) O_local + sum_i 2^(x_i - m) o_i) / (2^(R - m) + sum_i 2^(x_i - m)),  m = max(R, x_i).
+// This is the grouped softmax of llama/llama_mem.py:222-243 over [selected blocks | local keys] written out for the
+// prefix pattern of :415 (every selected block is a closed group whose last row is its landmark).
+template <typename T, int LPR>
+__global__ void __launch_bounds__(128) selected_attend_kernel(const T* __restrict__ q, const T* __restrict__ kc,
+                                                              lmk_cache_desc kd, const T* __restrict__ vc,
+                                                              lmk_cache_desc vd, const int32_t* __restrict__ idx,
+                                                              const T* __restrict__ cos_t, const T* __restrict__ sin_t,
+                                                              int n_pos, int rotary, const T* __restrict__ o_local,
+                                                              const float* __restrict__ R_local, int64_t local_rows,
+                                                              T* __restrict__ out, int H, int Tq, float scale) {
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int D = LPR * VEC, HALF = D / 2, LP = LPR / 2, RPS = 32 / LP;
+  constexpr int VGROUPS = 32 / LPR > 0 ? 32 / LPR : 1;      // value rows a warp reads per step
+  struct __align__(16) Vec { T v[VEC]; };
+  extern __shared__ __align__(16) float att_smem[];
+  const int t = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / H, h = bh - b * H;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane % LP, rsub = lane / LP, d0 = sub * VEC;
+  const int blk = kd.block, N = kd.n_blocks, top_k = kd.top_k;
+  float* lg = att_smem;                         // [top_k][blk] logits, then probabilities inside the block
+  float* osel = lg + ((top_k * blk + 3) & ~3);  // [top_k][D]
+  float* xsel = osel + top_k * D;               // [top_k] landmark logits, log2 domain
+  float q0[VEC], q1[VEC];
+  load_vec_f32<T, VEC>(q + ((int64_t)bh * Tq + t) * D + d0, q0);
+  load_vec_f32<T, VEC>(q + ((int64_t)bh * Tq + t) * D + HALF + d0, q1);
+#pragma unroll
+  for (int u = 0; u < VEC; ++u) {
+    q0[u] *= scale;
+    q1[u] *= scale;
+  }
+  const int32_t* idx_row = idx + ((int64_t)bh * Tq + t) * top_k;
+  const T* kbase = kc + b * kd.stride_b + h * kd.stride_h;
+  const T* vbase = vc + b * vd.stride_b + h * vd.stride_h;
+  constexpr float kL2e = 1.4426950408889634f;
+  for (int i = warp; i < top_k; i += 4) {
+    const int sel = idx_row[i];
+    const bool recent = logical_age(sel, kd.ring_start, N) >= N - top_k;
+    const int pos0 = kd.pos_base + (i + (recent ? 1 : 0)) * blk;
+    const T* ksrc = kbase + (int64_t)sel * kd.stride_block + d0;
+    float* lrow = lg + i * blk;
+    for (int r0 = 0; r0 < blk; r0 += RPS) {
+      const int r = r0 + rsub;
+      float acc = 0.f;
+      if (r < blk) {
+        const int pos = max(0, min(pos0 + r, n_pos - 1));
+        acc = rotated_row_dot<T, VEC>(ksrc + (int64_t)r * kd.stride_row, cos_t + (int64_t)pos * D + d0,
+                                      sin_t + (int64_t)pos * D + d0, HALF, rotary, q0, q1);
+      }
+#pragma unroll
+      for (int o = LP / 2; o >= 1; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (sub == 0 && r < blk) lrow[r] = acc * kL2e;
+    }
+    __syncwarp();
+    // softmax inside the block over rows 0 .. blk-2; the last row is the landmark
+    float mx = -INFINITY;
+    for (int r = lane; r < blk - 1; r += 32) mx = fmaxf(mx, lrow[r]);
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int r = lane; r < blk - 1; r += 32) den += exp2f(lrow[r] - mx);
+    den = warp_sum(den);
+    const float x_lm = lrow[blk - 1];
+    __syncwarp();
+    const float rden = den > 0.f ? 1.f / den : 0.f;
+    for (int r = lane; r < blk; r += 32) lrow[r] = r < blk - 1 ? exp2f(lrow[r] - mx) * rden : 0.f;
+    if (lane == 0) xsel[i] = x_lm;
+    __syncwarp();
+    // o_i = sum_r p_r V[r]: LPR lanes cover one value row, VGROUPS rows per step
+    const int vcol = lane % LPR, rg = lane / LPR;
+    float acc[VEC];
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) acc[u] = 0.f;
+    const T* vsrc = vbase + (int64_t)sel * vd.stride_block + vcol * VEC;
+    if (rg < VGROUPS) {
+#pragma unroll 4
+      for (int r = rg; r < blk; r += VGROUPS) {
+        const Vec v = *reinterpret_cast<const Vec*>(vsrc + (int64_t)r * vd.stride_row);
+        const float p = lrow[r];
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) acc[u] = fmaf(p, to_f32(v.v[u]), acc[u]);
+      }
+    }
+#pragma unroll
+    for (int o = LPR; o < 32; o <<= 1)
+#pragma unroll
+      for (int u = 0; u < VEC; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+    if (lane < LPR)
+#pragma unroll
+      for (int u = 0; u < VEC; ++u) osel[i * D + vcol * VEC + u] = acc[u];
+  }
+  __syncthreads();
+  float Rl = R_local != nullptr ? R_local[(int64_t)bh * local_rows + t] : -INFINITY;
+  if (Rl == INFINITY) Rl = -INFINITY;            // no local key is visible to this query
+  float m = Rl;
+  for (int i = 0; i < top_k; ++i) m = fmaxf(m, xsel[i]);
+  const float w_loc = m == -INFINITY ? 0.f : exp2f(Rl - m);
+  float Z = w_loc;
+  for (int i = 0; i < top_k; ++i) Z += m == -INFINITY ? 0.f : exp2f(xsel[i] - m);
+  const float rZ = Z > 0.f ? 1.f / Z : 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float sum = (R_local != nullptr && w_loc > 0.f) ? w_loc * to_f32(o_local[((int64_t)bh * local_rows + t) * D + d]) : 0.f;
+    for (int i = 0; i < top_k; ++i) sum = fmaf(m == -INFINITY ? 0.f : exp2f(xsel[i] - m), osel[i * D + d], sum);
+    out[((int64_t)bh * Tq + t) * D + d] = from_f32<T>(sum * rZ);
   }
 }
 
@@ -836,6 +958,64 @@ extern "C" int lmk_selected_pv(const void* probs, int64_t ld, int64_t col0, cons
   else if (dtype == LMK_F16) LMK_SP_LAUNCH(__half);
   else LMK_SP_LAUNCH(__nv_bfloat16);
 #undef LMK_SP_LAUNCH
+  LMK_CUDA(cudaGetLastError());
+  return LMK_OK;
+}
+
+extern "C" int lmk_selected_attend(const void* q, const void* k_cache, const lmk_cache_desc* kdesc, const void* v_cache,
+                                   const lmk_cache_desc* vdesc, const int32_t* idx, const void* cos_table,
+                                   const void* sin_table, int n_pos, int rotary, const void* o_local,
+                                   const float* R_local, int64_t local_rows, void* out, int B, int H, int T, int D,
+                                   float sm_scale, int dtype, void* stream) {
+  int rc = check_desc(kdesc, "selected_attend");
+  if (rc != LMK_OK) return rc;
+  if ((rc = check_desc(vdesc, "selected_attend")) != LMK_OK) return rc;
+  LMK_CHECK_ARG(q && k_cache && v_cache && idx && out, "selected_attend: null pointer");
+  LMK_CHECK_ARG((R_local == nullptr) == (o_local == nullptr), "selected_attend: o_local and R_local go together");
+  LMK_CHECK_ARG(R_local == nullptr || local_rows >= T, "selected_attend: local_rows %lld < T %d", (long long)local_rows, T);
+  LMK_CHECK_ARG((((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)cos_table | (uintptr_t)sin_table) &
+                 15) == 0, "selected_attend: q, caches and rotary tables must be 16-byte aligned");
+  LMK_CHECK_ARG(dtype == LMK_F32 || dtype == LMK_F16 || dtype == LMK_BF16, "selected_attend: unknown dtype %d", dtype);
+  LMK_CHECK_ARG(B >= 0 && H >= 1 && T >= 0 && D >= 1, "selected_attend: bad shape");
+  LMK_CHECK_ARG(kdesc->block == vdesc->block && kdesc->top_k == vdesc->top_k && kdesc->n_blocks == vdesc->n_blocks &&
+                    kdesc->ring_start == vdesc->ring_start, "selected_attend: key and value descriptors disagree");
+  LMK_CHECK_ARG(kdesc->block >= 2, "selected_attend: a block needs at least one key before its landmark");
+  const int vec = dtype == LMK_F32 ? 4 : 8;
+  const int lpr = D / vec;
+  LMK_CHECK_ARG(D % vec == 0 && (lpr == 4 || lpr == 8 || lpr == 16 || lpr == 32),
+                "selected_attend: D=%d must be 4, 8, 16 or 32 vectors of 16 bytes", D);
+  for (const lmk_cache_desc* d : {kdesc, vdesc})
+    LMK_CHECK_ARG(d->stride_row % vec == 0 && d->stride_block % vec == 0 && d->stride_h % vec == 0 &&
+                      d->stride_b % vec == 0, "selected_attend: cache strides must be multiples of %d elements", vec);
+  LMK_CHECK_ARG(rotary == LMK_ROTARY_NONE || (cos_table && sin_table && n_pos >= 1),
+                "selected_attend: rotary needs cos/sin tables");
+  LMK_CHECK_ARG(rotary == LMK_ROTARY_NONE || rotary == LMK_ROTARY_HALF || rotary == LMK_ROTARY_INTERLEAVED,
+                "selected_attend: unknown rotary mode %d", rotary);
+  LMK_CHECK_ARG(kdesc->top_k >= 1, "selected_attend: top_k must be at least 1");
+  if (B == 0 || T == 0) return LMK_OK;
+  LMK_CHECK_ARG((int64_t)B * H <= 65535, "selected_attend: grid too large");
+  const size_t smem = (size_t)(((kdesc->top_k * kdesc->block + 3) & ~3) + kdesc->top_k * D + kdesc->top_k) * sizeof(float);
+  LMK_CHECK_ARG(smem <= 48 * 1024, "selected_attend: top_k * (block + D) = %d x (%d + %d) floats do not fit in shared memory",
+                kdesc->top_k, kdesc->block, D);
+  dim3 grid(T, B * H);
+  cudaStream_t st = (cudaStream_t)stream;
+#define LMK_SA_LAUNCH(TT, LPR)                                                                                        \
+  selected_attend_kernel<TT, LPR><<<grid, 128, smem, st>>>((const TT*)q, (const TT*)k_cache, *kdesc,                 \
+                                                           (const TT*)v_cache, *vdesc, idx, (const TT*)cos_table,    \
+                                                           (const TT*)sin_table, n_pos, rotary, (const TT*)o_local,  \
+                                                           R_local, local_rows, (TT*)out, H, T, sm_scale)
+#define LMK_SA_DISPATCH(TT)                     \
+  switch (lpr) {                                \
+    case 4: LMK_SA_LAUNCH(TT, 4); break;        \
+    case 8: LMK_SA_LAUNCH(TT, 8); break;        \
+    case 16: LMK_SA_LAUNCH(TT, 16); break;      \
+    default: LMK_SA_LAUNCH(TT, 32); break;      \
+  }
+  if (dtype == LMK_F32) { LMK_SA_DISPATCH(float) }
+  else if (dtype == LMK_F16) { LMK_SA_DISPATCH(__half) }
+  else { LMK_SA_DISPATCH(__nv_bfloat16) }
+#undef LMK_SA_DISPATCH
+#undef LMK_SA_LAUNCH
   LMK_CUDA(cudaGetLastError());
   return LMK_OK;
 }

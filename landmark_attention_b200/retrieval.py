@@ -135,18 +135,88 @@ def selected_pv(probs, v_cache, vdesc, idx, col0=0, dim=None):
     return out
 
 
-def llama_retrieval_attention(q, k_new, v_new, past_k, past_v, mem_freq, cache_top_k, position_ids=None,
-                              chunk_is_mem=None, cos=None, sin=None, return_debug=False, materialize=None):
+def selected_attend(q, k_cache, v_cache, kdesc, vdesc, idx, cos=None, sin=None, rotary=L.ROTARY_NONE, sm_scale=None,
+                    o_local=None, R_local=None):
+    """Attention of every query over ITS selected blocks in one kernel, merged with the attention over the local keys.
+
+    o_local [B,H,Tl,D] / R_local [B*H,Tl] (Tl >= T) are the output and the log2 outer-softmax share of the local keys as
+    `lmk::masked_attention_fwd` returns them; None: attend over the selected blocks alone.  No logits or probabilities
+    are written to memory.  Fuses llama/llama_mem.py:386-404, the prefix part of :462-466 and :468-474."""
+    L.require_cuda(q, k_cache, v_cache, idx)
+    q = q.contiguous()
+    B, H, T, D = q.shape
+    assert idx.dtype == torch.int32 and idx.is_contiguous() and idx.shape == (B, H, T, kdesc.top_k)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    local_rows = 0
+    if o_local is not None:
+        assert o_local.is_contiguous() and R_local.is_contiguous() and o_local.dtype == q.dtype
+        local_rows = o_local.shape[2]
+        assert o_local.shape == (B, H, local_rows, D) and R_local.shape == (B * H, local_rows)
+    out = torch.empty((B, H, T, D), device=q.device, dtype=q.dtype)
+    n_pos = 0 if cos is None else cos.shape[0]
+    rc = L.lib().lmk_selected_attend(L.ptr(q), L.ptr(k_cache), ctypes.byref(kdesc), L.ptr(v_cache), ctypes.byref(vdesc),
+                                     L.ptr(idx), L.ptr(cos), L.ptr(sin), n_pos, rotary, L.ptr(o_local), L.ptr(R_local),
+                                     local_rows, L.ptr(out), B, H, T, D, float(sm_scale), L.dtype_code(q),
+                                     L.stream_ptr(q.device))
+    L.check(rc, "lmk_selected_attend")
+    return out
+
+
+class LandmarkKVCache:
+    """Preallocated un-rotated key/value cache [B,H,capacity,D] for chunked inference: `append` copies only the new
+    chunk, so a layer never re-copies what it already holds (the reference re-concatenates the whole cache on every call,
+    llama/llama_mem.py:424-425)."""
+
+    def __init__(self, batch, heads, capacity, dim, dtype, device):
+        self.k = torch.empty((batch, heads, capacity, dim), dtype=dtype, device=device)
+        self.v = torch.empty((batch, heads, capacity, dim), dtype=dtype, device=device)
+        self.length = 0
+
+    def views(self):
+        return self.k[:, :, :self.length], self.v[:, :, :self.length]
+
+    def append(self, k_new, v_new):
+        n = k_new.shape[2]
+        if self.length + n > self.k.shape[2]:
+            raise ValueError(f"cache capacity {self.k.shape[2]} exceeded ({self.length} + {n})")
+        self.k[:, :, self.length:self.length + n].copy_(k_new)
+        self.v[:, :, self.length:self.length + n].copy_(v_new)
+        self.length += n
+        return self.views()
+
+
+def _pad_rows(x, rows):
+    if x.shape[2] == rows:
+        return x.contiguous()
+    out = x.new_zeros((*x.shape[:2], rows, x.shape[3]))
+    out[:, :, :x.shape[2]] = x
+    return out
+
+
+def llama_retrieval_attention(q, k_new, v_new, past_k=None, past_v=None, mem_freq=None, cache_top_k=None,
+                              position_ids=None, chunk_is_mem=None, cos=None, sin=None, return_debug=False,
+                              materialize=None, cache=None, aggregate=None, fused=None):
     """Attention of one chunk against a landmark block cache, as LlamaAttention.forward does with
-    `mem_freq`/`cache_top_k` set and use_flash=False (llama/llama_mem.py:296-298, 318-430, 447-474).
+    `mem_freq`/`cache_top_k` set (llama/llama_mem.py:296-298, 318-430, 447-474).
 
     q, k_new, v_new: [B,H,T,D] projections of the chunk BEFORE rotary; past_k/past_v: [B,H,C,D] un-rotated cache
-    (:424,436).  chunk_is_mem: bool [1,T] landmark flags of the chunk (default: regular in absolute position).
-    materialize: True gathers the selected blocks into [B,H,T,top_k*block,D] copies as the reference does
-    (:386-398); False (default, unless return_debug asks for the copies) reads them in place with the fused
-    selected-block kernels.
+    (:424,436), or `cache`, a LandmarkKVCache that is appended to in place.  chunk_is_mem: bool [1,T] landmark flags of
+    the chunk (default: regular in absolute position).
+    aggregate: None = one block selection per (head, token) on the raw scores (the reference's default, :378-384);
+      "max_over_tokens" = one selection per head from the softmax of the scores maximised over the chunk's tokens, the
+      selected blocks prepended to the keys and the whole thing run through fused landmark attention (the reference's
+      route with offload_cache_to_cpu, :369-377, 400-406, 445).
+    Three implementations of the default mode, same results within the 16-bit tolerances:
+      fused (default where it applies: 16-bit, D=128, no partial block in the cache): local keys through the
+        tensor-core operator for arbitrary landmark positions, selected blocks read in place by one kernel that also
+        merges the two parts -- no logits, probabilities or gathered copies in memory;
+      materialize=False: selected-block logits / value sums read in place, grouped softmax on a logits buffer;
+      materialize=True (what the reference does, :386-398): gathered [B,H,T,top_k*block,D] copies and matmuls.
     Returns (attn_output [B,H,T,D], new (past_k, past_v)).
     """
+    if cache is not None:
+        past_k, past_v = cache.views()
     if materialize is None:
         materialize = return_debug
     B, H, T, D = q.shape
@@ -172,8 +242,51 @@ def llama_retrieval_attention(q, k_new, v_new, past_k, past_v, mem_freq, cache_t
     kst, vst = past_k.stride(), past_v.stride()
     kdesc = L.CacheDesc(kst[0], kst[1], kst[2] * block, kst[2], num_mems, 0, block, top_k, prefix_len)
     vdesc = L.CacheDesc(vst[0], vst[1], vst[2] * block, vst[2], num_mems, 0, block, top_k, prefix_len)
+
+    def new_cache():
+        if cache is not None:
+            return cache.append(k_new, v_new)
+        return torch.cat((past_k, k_new), dim=2), torch.cat((past_v, v_new), dim=2)
+
+    if aggregate == "max_over_tokens":
+        # one set of blocks per head; the chunk then attends to [selected blocks | chunk] with the regular landmark
+        # pattern, which is fused landmark attention with top_k history blocks (:400-406, 445)
+        assert inc == 0, "max_over_tokens needs whole blocks in the cache (the fused kernel's history is whole blocks)"
+        probs = landmark_scores(qr, past_k, kdesc, cos, sin, L.ROTARY_HALF, scale, softmax=True)
+        sel = topk_sorted(probs, top_k, mode="max_over_tokens")                       # [B,H,1,top_k]
+        sel_k, sel_v = gather_kv(past_k, past_v, kdesc, vdesc, sel, cos, sin, L.ROTARY_HALF, dim=D)
+        from .fused import fused_landmark_attention
+        keys = torch.cat((sel_k.view(B, H, top_k * block, D), kr), dim=2)
+        vals = torch.cat((sel_v.view(B, H, top_k * block, D), v_new), dim=2)
+        out = fused_landmark_attention(qr, keys, vals, None, sm_scale=scale, block_size=block)
+        if return_debug:
+            return out, new_cache(), dict(scores=probs, sel=sel, sel_k=sel_k, sel_v=sel_v)
+        return out, new_cache()
+    if aggregate is not None:
+        raise NotImplementedError(f"aggregate={aggregate!r}")
+
     scores = landmark_scores(qr, past_k, kdesc, cos, sin, L.ROTARY_HALF, scale)
     sel = topk_sorted(scores, top_k)
+    if chunk_is_mem is None:
+        chunk_is_mem = (position_ids % block == block - 1).view(1, T)
+
+    from .masked import _fwd as masked_fwd, masked_attention_supported
+    t_pad = ((T + 127) // 128) * 128
+    if fused is None:
+        fused = (not materialize and not return_debug and inc == 0 and top_k >= 1 and q.dtype != torch.float32
+                 and D == 128 and t_pad <= 32768)
+    if fused:
+        # local part: landmark attention of the chunk over itself on the tensor cores, rows padded to whole tiles
+        # (padding keys lie after every real query, so causality hides them); then one kernel for the selected blocks
+        # and the merge of the two parts
+        assert inc == 0 and not materialize
+        qp, kp, vp = _pad_rows(qr, t_pad), _pad_rows(kr, t_pad), _pad_rows(v_new, t_pad)
+        im = torch.zeros((B, t_pad), dtype=torch.uint8, device=dev)
+        im[:, :T] = chunk_is_mem.to(torch.uint8).expand(B, T)
+        o_loc, r_loc, _ = masked_fwd(qp, kp, vp, im, scale, 64)
+        out = selected_attend(qr, past_k, past_v, kdesc, vdesc, sel, cos, sin, L.ROTARY_HALF, scale, o_loc, r_loc)
+        return out, new_cache()
+
     n_pre = top_k * block
     sel_k = sel_v = None
     if materialize:
@@ -185,8 +298,6 @@ def llama_retrieval_attention(q, k_new, v_new, past_k, past_v, mem_freq, cache_t
     keys = torch.cat((k_inc, kr), dim=2)
     vals = torch.cat((past_v[:, :, full:], v_new), dim=2)
     local = torch.matmul(qr, keys.transpose(2, 3)) * scale
-    if chunk_is_mem is None:
-        chunk_is_mem = (position_ids % block == block - 1).view(1, T)
     hidden = torch.ones(T, T, dtype=torch.bool, device=dev).triu(1)
     mask_c, is_mem_c, last_c = prepare_landmark_masks(chunk_is_mem, hidden)
     fmin = torch.finfo(local.dtype).min
@@ -209,7 +320,6 @@ def llama_retrieval_attention(q, k_new, v_new, past_k, past_v, mem_freq, cache_t
         out = torch.matmul(p_local, vals) + torch.matmul(probs[..., :n_pre].unsqueeze(3), sel_v).squeeze(3)
     else:
         out = torch.matmul(p_local, vals) + selected_pv(probs.contiguous(), past_v, vdesc, sel, 0, dim=D)
-    new_cache = (torch.cat((past_k, k_new), dim=2), torch.cat((past_v, v_new), dim=2))
     if return_debug:
-        return out, new_cache, dict(scores=scores, sel=sel, sel_k=sel_k, sel_v=sel_v, probs=probs)
-    return out, new_cache
+        return out, new_cache(), dict(scores=scores, sel=sel, sel_k=sel_k, sel_v=sel_v, probs=probs)
+    return out, new_cache()

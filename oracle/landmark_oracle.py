@@ -259,7 +259,7 @@ def llama_selected_key_positions(sel_idx, num_mems: int, top_k: int, prefix_len:
 
 
 def llama_retrieval_attention(q, k_new, v_new, past_k, past_v, block: int, top_k: int,
-                              position_ids=None, chunk_is_mem=None, return_debug: bool = False):
+                              position_ids=None, chunk_is_mem=None, return_debug: bool = False, sel=None):
     """LLaMA long-context attention with landmark retrieval (mode A: per head and token).
 
     Reference: LlamaAttention.forward cache branch, llama/llama_mem.py:296-298,318-430,447-474,
@@ -269,11 +269,14 @@ def llama_retrieval_attention(q, k_new, v_new, past_k, past_v, block: int, top_k
     past_k/past_v: [B,H,C,D] un-rotated cache.  The chunk's landmark pattern is regular in
     absolute position (token at position p is a landmark iff p % block == block-1) unless
     chunk_is_mem (bool [1,T]) says otherwise.
+    sel (int64 [B,H,T,top_k], optional): use this block selection instead of the top-k of this function's own scores
+    (parity of 16-bit kernels is defined "given the same landmark scores": near-ties would otherwise flip).
     Returns [B,H,T,D].
     """
     B, H, T, D = q.shape
     C = past_k.shape[2]
     scale = 1.0 / math.sqrt(D)
+    sel_given = sel
     if position_ids is None:
         position_ids = torch.arange(C, C + T, dtype=torch.long)
     qr = rotary_half_split(q, position_ids.view(1, 1, T))
@@ -295,7 +298,7 @@ def llama_retrieval_attention(q, k_new, v_new, past_k, past_v, block: int, top_k
     mem_pos, prefix_len = llama_slot_positions(num_mems, tk, full, block)
     lm_keys = rotary_half_split(kb[:, :, :, block - 1], mem_pos.view(1, 1, num_mems))
     scores = torch.matmul(qr, lm_keys.transpose(2, 3)) / math.sqrt(D)       # [B,H,T,num_mems]
-    sel = sorted_topk(scores, tk)                                           # [B,H,T,tk]
+    sel = sorted_topk(scores, tk) if sel_given is None else sel_given       # [B,H,T,tk]
     key_pos = llama_selected_key_positions(sel, num_mems, tk, prefix_len, block)  # [B,H,T,tk*block]
     gidx = sel.view(B, H, T, tk, 1, 1).expand(B, H, T, tk, block, D)
     sel_k = torch.take_along_dim(kb.unsqueeze(2).expand(B, H, T, num_mems, block, D), gidx, dim=3)

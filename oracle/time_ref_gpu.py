@@ -50,6 +50,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "ref_gpu.json"))
     ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--config3", action="store_true",
+                    help="also time one optimizer step of the reference's own lm_benchmark GPT (models/landmark.py GPTBase) "
+                         "at 12 layers, n_embd 1024, 8 heads, seq 512, batch 16, bf16 autocast, on one GPU")
     a = ap.parse_args()
     res = {"env": dict(torch=torch.__version__, gpu=torch.cuda.get_device_name(0), staged=R.available())}
     try:
@@ -137,7 +140,43 @@ def main():
             res[f"B1_H32_L{L}_D128_bf16"] = case(1, 32, L, 128, 64, 3, False)
             save()
             print(L, json.dumps(res[f"B1_H32_L{L}_D128_bf16"]), flush=True)
+    if a.config3:
+        try:
+            res["config3_reference_gpt"] = config3(dev)
+        except Exception:       # noqa: BLE001
+            res["config3_reference_gpt"] = traceback.format_exc()[-2000:]
+        print(json.dumps(res["config3_reference_gpt"]), flush=True)
     save()
+
+
+def config3(dev):
+    """The reference's GPTBase with its own attention (score matrix, mask block, grouped softmax), same data, optimizer
+    and step loop as bench.py's config 3 entry."""
+    import types
+    import bench_lm
+    lm = R.lm_landmark()
+    c = bench_lm.CONFIG
+    cfg = types.SimpleNamespace(vocab_size=c["vocab_size"], n_embd=c["n_embd"], n_head=c["n_head"], n_layer=c["n_layer"],
+                                sequence_length=c["sequence_length"], dropout=0.0, bias=False, positional_encoder="rotary",
+                                softmax_func="mem_opt", lm_cache="none", postpone_lm_cache=True,
+                                max_groups_for_softmax=c["max_groups_for_softmax"], group_dropout=None,
+                                enable_rem_score=False, landmark_id=bench_lm.LANDMARK_ID, mem_freq=c["mem_freq"],
+                                mem_cache_freq=None)
+    torch.manual_seed(5)
+    ref = lm.GPTBase(cfg).to(dev)
+
+    class Wrap(torch.nn.Module):
+        def __init__(self, m):
+            super().__init__()
+            self.m = m
+
+        def forward(self, x, y):
+            return self.m(x, targets=y)["loss"]
+
+    out = bench_lm.train_step_bench(Wrap(ref), c, 1, 0, torch.device(dev), 5, 2, lambda w: None, lambda x, w, d: x)
+    return {"what": "reference GPTBase (lm_benchmark/models/landmark.py) training step, eager (no torch.compile), 1 GPU",
+            "tokens_per_s": out["tokens_per_s"], "ms_per_step": out["ms_per_step"], "loss_first": out["loss_first"],
+            "loss_last": out["loss_last"]}
 
 
 if __name__ == "__main__":

@@ -262,3 +262,121 @@ def test_scores_on_tensor_cores(dtype):
     assert ((scores - ref).abs() > 0).float().mean().item() < 0.02
     sel = P.topk_sorted(scores, top_k)
     assert torch.equal(sel.long(), scores.topk(top_k, dim=-1).indices.sort(dim=-1).values)
+
+
+def _blocks_attention_reference(q, pk, pv, sel, blk, key_pos, scale):
+    """Attention over the selected blocks alone, each a closed landmark group (fp32 torch on CPU)."""
+    B, H, T, D = q.shape
+    top_k = sel.shape[-1]
+    nblk = pk.shape[2] // blk
+    gi = sel.view(B, H, T, top_k, 1, 1).expand(B, H, T, top_k, blk, D)
+    ek = torch.take_along_dim(pk.view(B, H, 1, nblk, blk, D).expand(B, H, T, nblk, blk, D), gi, dim=3)
+    ev = torch.take_along_dim(pv.view(B, H, 1, nblk, blk, D).expand(B, H, T, nblk, blk, D), gi, dim=3)
+    ek = O.rotary_half_split(ek.reshape(B, H, T, top_k * blk, D).float(), key_pos).view(B, H, T, top_k, blk, D)
+    logits = torch.einsum("bhtd,bhtird->bhtir", q.float(), ek) * scale
+    inner = torch.softmax(logits[..., : blk - 1], dim=-1)
+    outer = torch.softmax(logits[..., blk - 1], dim=-1)                       # over the landmarks of the blocks
+    o_i = torch.einsum("bhtir,bhtird->bhtid", inner, ev.float()[..., : blk - 1, :])
+    return torch.einsum("bhti,bhtid->bhtd", outer, o_i)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_selected_attend_alone(dtype):
+    # one kernel: logits of the selected blocks, softmax inside each block, outer softmax over their landmarks, value sums
+    torch.manual_seed(8)
+    B, H, T, D, blk, nblk, top_k = 2, 2, 7, 64, 8, 20, 3
+    C = nblk * blk
+    q = torch.randn(B, H, T, D).to(dtype)
+    pk, pv = torch.randn(B, H, C, D).to(dtype), torch.randn(B, H, C, D).to(dtype)
+    prefix_len = C - (top_k + 1) * blk
+    cos, sin = P.rotary_tables_half(C + T + 1, D, dtype, DEV)
+    pkc, pvc = pk.to(DEV), pv.to(DEV)
+    st = pkc.stride()
+    desc = L.CacheDesc(st[0], st[1], st[2] * blk, st[2], nblk, 0, blk, top_k, prefix_len)
+    sel = P.topk_sorted(P.landmark_scores(q.to(DEV), pkc, desc, cos, sin, L.ROTARY_HALF), top_k)
+    out = P.selected_attend(q.to(DEV), pkc, pvc, desc, desc, sel, cos, sin, L.ROTARY_HALF)
+    selc = sel.long().cpu()
+    kpos = O.llama_selected_key_positions(selc, nblk, top_k, prefix_len, blk)
+    exp = _blocks_attention_reference(q, pk, pv, selc, blk, kpos, 1.0 / math.sqrt(D))
+    assert (out.float().cpu() - exp).abs().max().item() < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+def test_retrieval_call_site_bf16_long_context_shape():
+    # the long-context shape per head: cache of 32768 tokens in blocks of 32, chunk of 258, top-4 per (head, token), bf16.
+    # Default route = fused (tensor-core local attention + one selected-block kernel); the oracle gets the kernel's own
+    # selection (parity is defined given the same scores), which itself is checked bit-exactly against torch.topk.
+    torch.manual_seed(12)
+    B, H, T, D, blk, C, top_k = 1, 2, 258, 128, 32, 32768, 4
+    dtype = torch.bfloat16
+    q, k, v = [(torch.randn(B, H, T, D) * 0.5).to(dtype) for _ in range(3)]
+    pk, pv = (torch.randn(B, H, C, D) * 0.5).to(dtype), torch.randn(B, H, C, D).to(dtype)
+    qc, kc, vc, pkc, pvc = [t.to(DEV) for t in (q, k, v, pk, pv)]
+    out_mat, _, dbg = P.llama_retrieval_attention(qc, kc, vc, pkc, pvc, blk - 1, top_k, return_debug=True)
+    sel = dbg["sel"].long()
+    assert torch.equal(sel, dbg["scores"].topk(top_k, dim=-1).indices.sort(dim=-1).values)
+    out_fused, _ = P.llama_retrieval_attention(qc, kc, vc, pkc, pvc, blk - 1, top_k)
+    out_inplace, _ = P.llama_retrieval_attention(qc, kc, vc, pkc, pvc, blk - 1, top_k, fused=False)
+    exp = O.llama_retrieval_attention(q.float(), k.float(), v.float(), pk.float(), pv.float(), blk, top_k, sel=sel.cpu())
+    for name, got in (("fused", out_fused), ("in place", out_inplace), ("materialised", out_mat)):
+        err = (got.float().cpu() - exp).abs().max().item()
+        assert err < 2e-2, f"{name}: {err}"
+        rel = ((got.float().cpu() - exp).norm() / exp.norm()).item()
+        assert rel < 1e-2, f"{name}: rel-L2 {rel}"
+    # gather_kv at this shape against torch (values: pure copy; keys: torch's arithmetic on the same tables)
+    nblk = C // blk
+    cos, sin = P.rotary_tables_half(C + T + 1, D, dtype, DEV)
+    selc = sel[:, :, :16].cpu()
+    kpos = O.llama_selected_key_positions(selc, nblk, top_k, C - (top_k + 1) * blk, blk)
+    gi = selc.view(B, H, 16, top_k, 1, 1).expand(B, H, 16, top_k, blk, D)
+    ek = torch.take_along_dim(pk.view(B, H, 1, nblk, blk, D).expand(B, H, 16, nblk, blk, D), gi, dim=3)
+    ev = torch.take_along_dim(pv.view(B, H, 1, nblk, blk, D).expand(B, H, 16, nblk, blk, D), gi, dim=3)
+    from landmark_attention_b200.retrieval import apply_rotary_half
+    assert torch.equal(dbg["sel_v"][:, :, :16].cpu(), ev.reshape(B, H, 16, top_k * blk, D))
+    assert torch.equal(dbg["sel_k"][:, :, :16].cpu(),
+                       apply_rotary_half(ek.reshape(B, H, 16, top_k * blk, D), cos.cpu(), sin.cpu(), kpos))
+    assert L.device_status() == 0
+
+
+def test_preallocated_cache_appends_in_place():
+    torch.manual_seed(13)
+    B, H, D, blk, top_k = 1, 2, 128, 32, 2
+    dtype = torch.bfloat16
+    C0, T = 32 * 6, 64
+    pk, pv = [torch.randn(B, H, C0, D).to(dtype).to(DEV) for _ in range(2)]
+    chunks = [[torch.randn(B, H, T, D).to(dtype).to(DEV) for _ in range(3)] for _ in range(2)]
+    cache = P.LandmarkKVCache(B, H, C0 + 2 * T, D, dtype, DEV)
+    cache.append(pk, pv)
+    base_k = cache.k.data_ptr()
+    past = (pk, pv)
+    for q, k, v in chunks:
+        ref, past = P.llama_retrieval_attention(q, k, v, past[0], past[1], blk - 1, top_k)
+        got, views = P.llama_retrieval_attention(q, k, v, mem_freq=blk - 1, cache_top_k=top_k, cache=cache)
+        assert torch.equal(ref, got)
+        assert views[0].data_ptr() == base_k and views[0].shape[2] == past[0].shape[2]
+        assert torch.equal(views[0], past[0]) and torch.equal(views[1], past[1])
+
+
+def test_max_over_tokens_route():
+    # one block selection per head (softmax of the scores, maximum over the chunk's tokens), selected blocks prepended
+    # to the chunk, regular fused landmark attention with top_k history blocks
+    torch.manual_seed(14)
+    B, H, T, D, blk, nblk, top_k = 1, 3, 32, 32, 16, 12, 2
+    C = nblk * blk
+    q, k, v = [torch.randn(B, H, T, D) for _ in range(3)]
+    pk, pv = torch.randn(B, H, C, D), torch.randn(B, H, C, D)
+    out, _, dbg = P.llama_retrieval_attention(q.to(DEV), k.to(DEV), v.to(DEV), pk.to(DEV), pv.to(DEV), blk - 1, top_k,
+                                              aggregate="max_over_tokens", return_debug=True)
+    pos = torch.arange(C, C + T)
+    qr, kr = O.rotary_half_split(q, pos.view(1, 1, T)), O.rotary_half_split(k, pos.view(1, 1, T))
+    mem_pos, prefix_len = O.llama_slot_positions(nblk, top_k, C, blk)
+    lm = O.rotary_half_split(pk.view(B, H, nblk, blk, D)[:, :, :, blk - 1], mem_pos.view(1, 1, nblk))
+    probs = torch.softmax(torch.matmul(qr, lm.transpose(2, 3)) / math.sqrt(D), dim=-1)
+    sel = O.sorted_topk(probs.amax(dim=2, keepdim=True), top_k)                       # [B,H,1,top_k]
+    assert torch.equal(dbg["sel"].long().cpu(), sel)
+    kpos = O.llama_selected_key_positions(sel, nblk, top_k, prefix_len, blk)
+    gi = sel.view(B, H, 1, top_k, 1, 1).expand(B, H, 1, top_k, blk, D)
+    ek = torch.take_along_dim(pk.view(B, H, 1, nblk, blk, D), gi, dim=3).reshape(B, H, 1, top_k * blk, D)
+    ev = torch.take_along_dim(pv.view(B, H, 1, nblk, blk, D), gi, dim=3).reshape(B, H, top_k * blk, D)
+    ek = O.rotary_half_split(ek, kpos).view(B, H, top_k * blk, D)
+    exp = O.landmark_attention(qr, torch.cat((ek, kr), 2), torch.cat((ev, v), 2), blk)
+    assert (out.cpu() - exp).abs().max().item() < 1e-4
