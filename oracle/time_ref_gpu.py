@@ -50,6 +50,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "ref_gpu.json"))
     ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--retrieval", action="store_true",
+                    help="also time the reference's own LlamaAttention.forward cache branch (llama/llama_mem.py:318-430) for "
+                         "one layer at the long-context shape: 32 heads of 128, cache 32768 tokens in blocks of 32, chunk 258, top-4")
     ap.add_argument("--config3", action="store_true",
                     help="also time one optimizer step of the reference's own lm_benchmark GPT (models/landmark.py GPTBase) "
                          "at 12 layers, n_embd 1024, 8 heads, seq 512, batch 16, bf16 autocast, on one GPU")
@@ -140,6 +143,13 @@ def main():
             res[f"B1_H32_L{L}_D128_bf16"] = case(1, 32, L, 128, 64, 3, False)
             save()
             print(L, json.dumps(res[f"B1_H32_L{L}_D128_bf16"]), flush=True)
+    if a.retrieval:
+        try:
+            res["retrieval_reference_layer"] = retrieval_layer(dev)
+        except Exception:       # noqa: BLE001
+            res["retrieval_reference_layer"] = traceback.format_exc()[-2000:]
+        print(json.dumps(res["retrieval_reference_layer"]), flush=True)
+        save()
     if a.config3:
         try:
             res["config3_reference_gpt"] = config3(dev)
@@ -147,6 +157,51 @@ def main():
             res["config3_reference_gpt"] = traceback.format_exc()[-2000:]
         print(json.dumps(res["config3_reference_gpt"]), flush=True)
     save()
+
+
+def retrieval_layer(dev):
+    """One LlamaAttention layer of the reference with a filled cache, driven the way LlamaModel.forward drives it
+    (mask construction of llama/llama_mem.py:36-50 and :804-815, then LlamaAttention.forward with cache_top_k / mem_freq)."""
+    lm = R.llama_mem()
+    from llama_landmark_config import LlamaLandmarkConfig
+    H, D, C, T, blk, top_k = 32, 128, 32768, 258, 32, 4
+    cfg = LlamaLandmarkConfig(hidden_size=H * D, num_attention_heads=H, num_hidden_layers=1, intermediate_size=11008,
+                              max_position_embeddings=C + T + 8, vocab_size=32001, mem_freq=blk - 1)
+    torch.manual_seed(0)
+    attn = lm.LlamaAttention(cfg).to(dev).to(torch.bfloat16).eval()
+    g = torch.Generator(device=dev).manual_seed(7)
+    pk = torch.randn(1, H, C, D, generator=g, device=dev).to(torch.bfloat16)
+    pv = torch.randn(1, H, C, D, generator=g, device=dev).to(torch.bfloat16)
+    hidden = torch.randn(1, T, H * D, generator=g, device=dev).to(torch.bfloat16)
+    position_ids = torch.arange(C, C + T, device=dev).view(1, T)
+    is_mem_row = (position_ids % blk == blk - 1)
+    fmin = torch.finfo(torch.bfloat16).min
+
+    def masks():
+        mask = torch.full((T, T), fmin, device=dev, dtype=torch.bfloat16).triu(1)
+        mask = torch.cat([torch.zeros(T, C, dtype=torch.bfloat16, device=dev), mask], dim=-1)[None, None]
+        is_mem = is_mem_row.unsqueeze(1).unsqueeze(2)
+        mem_ids = torch.where(mask[..., -T:] < -1, 0, torch.cumsum(is_mem, -1) - is_mem.int())
+        last = torch.amax(mem_ids, -1, keepdim=True) == mem_ids
+        mask = mask.clone()
+        mask[..., -T:].masked_fill_(last & is_mem, fmin)
+        last = last.logical_and(mask[..., -T:] > -1)
+        is_mem = is_mem.logical_and(mask[..., -T:] > -1)
+        return mask, is_mem, last
+
+    def layer():
+        with torch.no_grad():
+            mask, is_mem, last = masks()
+            return attn(hidden, attention_mask=mask, position_ids=position_ids, past_key_value=(pk, pv), use_cache=True,
+                        is_mem=is_mem, last_section_mask=last, cache_top_k=top_k, mem_freq=blk - 1)[0]
+
+    out = layer()
+    r = cuda_time(layer, 2, 5)
+    r["tok_per_s_32_layers"] = 250.0 / (32 * r["ms_median"] * 1e-3)
+    r["what"] = ("reference LlamaAttention.forward, cache branch, one layer incl. its q/k/v/o projections and mask "
+                 "preparation, bf16, H=32 D=128 cache 32768 block 32 chunk 258 top-4 per (head, token)")
+    r["finite"] = bool(torch.isfinite(out.float()).all())
+    return r
 
 
 def config3(dev):
