@@ -220,6 +220,23 @@ typedef struct {
 } lmk_cache_desc;
 
 /*
+ * Append whole blocks to a block cache and keep a dense array of their landmark keys.
+ * Replaces the ring-buffer writes of MemLMCacheStorage.store_in_cache (lm_benchmark/models/caches/mem_cache.py:140-158)
+ * and adds what that code does not keep: landmark_keys, where block slot s of (b, h) holds the un-rotated key of the
+ * block's last row, so that lmk_landmark_scores can read the landmark keys contiguously (pass it a descriptor
+ * with stride_block = the array's slot stride and stride_row = 0).
+ *   k_src, v_src [B,H,n_store*block,D] with element strides {batch, head, row} (the chunk's whole blocks, oldest first);
+ *   block i is written to physical slot (first_slot + i) mod capacity of k_cache / v_cache, addressed through the
+ *   descriptors' strides (any layout: the reference's [B,capacity,block,H,D] or a head-major [B,H,capacity,block,D]);
+ *   landmark_keys (nullable) with element strides {batch, head, slot}.  16-byte aligned pointers, D * sizeof(dtype) and
+ *   all strides multiples of 16 bytes.  The descriptors' n_blocks / ring_start / top_k / pos_base are not used.
+ */
+int lmk_cache_store(const void* k_src, const void* v_src, const int64_t src_strides[3], void* k_cache, void* v_cache,
+                    const lmk_cache_desc* kdesc, const lmk_cache_desc* vdesc, void* landmark_keys,
+                    const int64_t landmark_strides[3], int B, int H, int n_store, int first_slot, int capacity, int D,
+                    int dtype, void* stream);
+
+/*
  * Landmark scores: scores[b,h,t,n] = sm_scale * q[b,h,t,:] . rot(K[b,h,n,block-1,:], slot position of n).
  * Replaces llama/llama_mem.py:357-367 and lm_benchmark/models/caches/mem_cache.py:51-61.
  *   q [B,H,T,D] dense (already rotated), k_cache per desc, cos/sin tables [n_pos, D] in `dtype` (NULL with

@@ -14,7 +14,7 @@ LIB_DIR = os.path.join(HERE, "lib")
 OBJ_DIR = os.path.join(HERE, "_obj")
 LIB_PATH = os.path.join(LIB_DIR, "libb200lmk.so")
 SOURCES = ["api.cu", "attn_general.cu", "attn_sm100.cu", "attn_mask_sm100.cu", "grouped_softmax.cu", "retrieval.cu",
-           "scores_sm100.cu"]
+           "scores_sm100.cu", "cache_store.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

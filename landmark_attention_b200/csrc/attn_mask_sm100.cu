@@ -132,7 +132,7 @@ struct Online {
 };
 
 // ---------------------------------------------------------------------------------------------- forward
-constexpr int kMfStages = 3;
+constexpr int kMfStages = 2;      // 2 stages + statistics sized for the launch keep two CTAs on an SM at training shapes
 constexpr int kMfThreads = 192;
 
 struct MfSmem {
@@ -146,10 +146,13 @@ struct MfSmem {
   uint32_t tmem_base;
 };
 
-constexpr size_t kMfSmemBytes = 1024 + 32768 + kMfStages * 32768 + kMaxGroups * kQT * 4 + kMaxKeyTiles * 12 + sizeof(MfSmem);
+// dynamic shared memory of the forward kernel for G groups and n_kt key tiles (n_kt rounded up to an even count)
+__host__ __device__ constexpr size_t mf_smem_bytes(int G, int n_kt) {
+  return 1024 + 32768 + kMfStages * 32768 + (size_t)G * kQT * 4 + (size_t)((n_kt + 1) & ~1) * 12 + sizeof(MfSmem);
+}
 
 template <bool kBf16>
-__global__ void __launch_bounds__(kMfThreads, 1)
+__global__ void __launch_bounds__(kMfThreads, 2)
 sm100_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const uint8_t* __restrict__ is_mem, int64_t is_mem_stride,
                       void* __restrict__ o_ptr, float* __restrict__ R_ptr, float* __restrict__ A_ptr, int H, int Lq,
@@ -161,10 +164,11 @@ sm100_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t q_tile = base;
   auto k_slot = [&](int s) { return base + 32768u + (uint32_t)s * 32768u; };       // K tile, later P
   auto v_slot = [&](int s) { return base + 32768u + (uint32_t)s * 32768u + 16384u; };
+  const int kt_cap = (Lk / kKT + 1) & ~1;                                           // entries of the two tables below
   float* Asm = reinterpret_cast<float*>(gen + 32768 + kMfStages * 32768);           // [G][128]
-  uint64_t* kmask = reinterpret_cast<uint64_t*>(gen + 32768 + kMfStages * 32768 + kMaxGroups * kQT * 4);
-  int* gbase = reinterpret_cast<int*>(kmask + kMaxKeyTiles);
-  MfSmem* sm = reinterpret_cast<MfSmem*>(gbase + kMaxKeyTiles);
+  uint64_t* kmask = reinterpret_cast<uint64_t*>(Asm + (size_t)G * kQT);
+  int* gbase = reinterpret_cast<int*>(kmask + kt_cap);
+  MfSmem* sm = reinterpret_cast<MfSmem*>(gbase + kt_cap);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = Lq / kQT;
@@ -865,6 +869,17 @@ sm100_mask_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       const uint64_t rest = from >= 64 ? 0ull : (mask >> from) << from;
       return rest ? k0 + (__ffsll((long long)rest) - 1) : next_lm;
     };
+    // closing landmark of the e-th group that meets the tile (uniform), for the first four groups
+    const int n_grp = __popcll(mask) + 1;
+    int lm_of[4];
+    {
+      uint64_t rest = mask;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        lm_of[e] = rest ? k0 + (__ffsll((long long)rest) - 1) : next_lm;
+        rest &= rest - 1;
+      }
+    }
     for (int i = 0; i < n_items; ++i) {
       const int sb = i & 1;
       const int tq = t_first + i;
@@ -884,10 +899,20 @@ sm100_mask_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         sub = delta;
         return R;
       };
-      int g = g0;
-      int lmpos = closing(0);
-      float sub;
-      float z = zof(g, lmpos, sub);
+      // The statistics of the first four groups that meet this tile are fetched up front, all loads in flight at once
+      // and overlapped with the wait for S / dP (a fetch at every group change would put a global-memory round trip
+      // into the row walk each time); tiles with more groups fetch the rest on demand.
+      float zq[4], sq[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        zq[e] = R;
+        sq[e] = delta;
+        if (e < n_grp) zq[e] = zof(g0 + e, lm_of[e], sq[e]);
+      }
+      int g = g0, gi = 0;
+      int lmpos = lm_of[0];
+      float sub = sq[0];
+      float z = zq[0];
       mbar_wait(smem_u32(&sm->sdp_full[sb]), (i / 2) & 1, status, kErrMaskDkv + 2);
       tc_fence_after();
       float xv[64], dp[64];
@@ -923,8 +948,14 @@ sm100_mask_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
             p[e] = 0.f;
             d[e] = (j <= lim && j != own) ? ex2(xv[j] - R) * (sub - delta) * scale : 0.f;
             ++g;
-            lmpos = closing(j + 1);
-            z = zof(g, lmpos, sub);
+            ++gi;
+            if (gi < 4) {
+              z = gi == 1 ? zq[1] : (gi == 2 ? zq[2] : zq[3]);
+              sub = gi == 1 ? sq[1] : (gi == 2 ? sq[2] : sq[3]);
+            } else {
+              lmpos = closing(j + 1);
+              z = zof(g, lmpos, sub);
+            }
           } else {
             const float pj = j <= lim ? ex2(xv[j] - z) : 0.f;
             p[e] = pj;
@@ -992,8 +1023,8 @@ int mask_kernel_attributes() {
   std::lock_guard<std::mutex> lock(mu);
   if (!facts[dev].ready) {
     const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
-    LMK_CUDA(cudaFuncSetAttribute(sm100_mask_fwd_kernel<true>, attr, (int)kMfSmemBytes));
-    LMK_CUDA(cudaFuncSetAttribute(sm100_mask_fwd_kernel<false>, attr, (int)kMfSmemBytes));
+    LMK_CUDA(cudaFuncSetAttribute(sm100_mask_fwd_kernel<true>, attr, (int)mf_smem_bytes(kMaxGroups, kMaxKeyTiles)));
+    LMK_CUDA(cudaFuncSetAttribute(sm100_mask_fwd_kernel<false>, attr, (int)mf_smem_bytes(kMaxGroups, kMaxKeyTiles)));
     LMK_CUDA(cudaFuncSetAttribute(sm100_mask_bwd_dq_kernel<true>, attr, (int)mq_smem_bytes(kMaxGroups)));
     LMK_CUDA(cudaFuncSetAttribute(sm100_mask_bwd_dq_kernel<false>, attr, (int)mq_smem_bytes(kMaxGroups)));
     LMK_CUDA(cudaFuncSetAttribute(sm100_mask_bwd_dkv_kernel<true>, attr, (int)kMkSmemBytes));
@@ -1027,12 +1058,13 @@ int attn_mask_sm100_fwd(const AttnParams& p, const uint8_t* is_mem, int64_t is_m
   if (!status) return fail(LMK_ERR_CUDA, "cannot resolve the device status word");
   const float scale_log2 = p.scale * kLog2e;
   dim3 grid(p.B * p.H, p.Lq / kQT);
+  const size_t smem = mf_smem_bytes(G, p.Lk / kKT);
   if (dtype == LMK_BF16)
-    sm100_mask_fwd_kernel<true><<<grid, kMfThreads, kMfSmemBytes, st>>>(tq, tk, tv, is_mem, is_mem_stride, p.o, R, A,
-                                                                         p.H, p.Lq, p.Lk, G, scale_log2, status);
+    sm100_mask_fwd_kernel<true><<<grid, kMfThreads, smem, st>>>(tq, tk, tv, is_mem, is_mem_stride, p.o, R, A, p.H, p.Lq,
+                                                                 p.Lk, G, scale_log2, status);
   else
-    sm100_mask_fwd_kernel<false><<<grid, kMfThreads, kMfSmemBytes, st>>>(tq, tk, tv, is_mem, is_mem_stride, p.o, R, A,
-                                                                          p.H, p.Lq, p.Lk, G, scale_log2, status);
+    sm100_mask_fwd_kernel<false><<<grid, kMfThreads, smem, st>>>(tq, tk, tv, is_mem, is_mem_stride, p.o, R, A, p.H, p.Lq,
+                                                                  p.Lk, G, scale_log2, status);
   LMK_CUDA(cudaGetLastError());
   return LMK_OK;
 }

@@ -3,9 +3,13 @@
 Same interface as the reference (lm_benchmark/models/caches/cache.py:17-35, mem_cache.py:21-217):
 `retrieve_for_query(q, cache_context, pos_emb_closure, start_index)`, `store_in_cache(keys, values_dict)`,
 `clear_state()`, and the id bookkeeping of `MemLMCache.forward / get_final_logits`.
-The ring buffer keeps the reference's layout [B, capacity, block, H, D]; selection, the gather and the rotation of
-gathered keys run in CUDA kernels; the rotary convention is lm_benchmark's interleaved one.
+The ring buffer keeps the reference's layout [B, capacity, block, H, D] by default; `layout="head_major"` stores it as
+[B, H, capacity, block, D], where a block of one head is one contiguous run of block * D elements (the gather then reads
+whole blocks instead of `block` separate rows).  In both layouts `store_in_cache` also keeps the blocks' landmark keys
+in a dense [B, H, capacity, D] array, which is what the scoring kernel reads.  Selection, the gather, the rotation of
+gathered keys and the block writes run in CUDA kernels; the rotary convention is lm_benchmark's interleaved one.
 """
+import ctypes
 import math
 
 import torch
@@ -42,14 +46,22 @@ class MemLMCacheStorage(nn.Module):
     """Per-layer storage (mem_cache.py:21-158).  `config` needs batch_size, mem_cache_size, mem_cache_freq, n_head,
     n_embd, cache_topk, cache_selection_method."""
 
-    def __init__(self, config, layer=None, dtype=torch.float32, device="cuda"):
+    def __init__(self, config, layer=None, dtype=torch.float32, device="cuda", layout="reference"):
         super().__init__()
         self.config = config
         hs = config.n_embd // config.n_head
         blk = config.mem_cache_freq + 1
-        shape = (config.batch_size, config.mem_cache_size, blk, config.n_head, hs)
+        if layout == "reference":
+            shape = (config.batch_size, config.mem_cache_size, blk, config.n_head, hs)
+        elif layout == "head_major":
+            shape = (config.batch_size, config.n_head, config.mem_cache_size, blk, hs)
+        else:
+            raise ValueError(f"unknown cache layout {layout!r}")
+        self.layout = layout
         self.register_buffer("cache_mem_k", torch.empty(shape, dtype=dtype, device=device), persistent=False)
         self.register_buffer("cache_mem_v", torch.empty(shape, dtype=dtype, device=device), persistent=False)
+        lm_shape = (config.batch_size, config.n_head, config.mem_cache_size, hs)
+        self.register_buffer("cache_lm_k", torch.empty(lm_shape, dtype=dtype, device=device), persistent=False)
         tail = (config.batch_size, config.n_head, blk, hs)
         self.register_buffer("last_incomplete_k", torch.empty(tail, dtype=dtype, device=device), persistent=False)
         self.register_buffer("last_incomplete_v", torch.empty(tail, dtype=dtype, device=device), persistent=False)
@@ -63,6 +75,25 @@ class MemLMCacheStorage(nn.Module):
         self.cache_iter = 0
         self.cache_size = 0
 
+    @property
+    def block(self):
+        return self.config.mem_cache_freq + 1
+
+    @property
+    def capacity(self):
+        return self.config.mem_cache_size
+
+    def _descs(self, n, ring_start, top_k):
+        """(key, value, landmark-key) descriptors addressed as (batch, head, block slot, row)."""
+        def order(st):
+            return (st[0], st[3], st[1], st[2]) if self.layout == "reference" else (st[0], st[1], st[2], st[3])
+        blk = self.block
+        k = L.CacheDesc(*order(self.cache_mem_k.stride()), n, ring_start, blk, top_k, 0)
+        v = L.CacheDesc(*order(self.cache_mem_v.stride()), n, ring_start, blk, top_k, 0)
+        ls = self.cache_lm_k.stride()
+        lm = L.CacheDesc(ls[0], ls[1], ls[2], 0, n, ring_start, blk, top_k, 0)      # every "row" of a slot is its landmark key
+        return k, v, lm
+
     def _rotary(self, n_pos, dim, dtype, device):
         if self._tables is None or self._tables[0].shape[0] < n_pos or self._tables[0].dtype != dtype:
             self._tables = rotary_tables_interleaved(max(n_pos, 4096), dim, dtype, device)
@@ -75,8 +106,7 @@ class MemLMCacheStorage(nn.Module):
         key rotations than the model expects."""
         _require_plain_rotary(pos_emb_closure, q.shape[-1])
         B, nh, T, hs = q.shape
-        blk = self.cache_mem_k.shape[2]
-        cap = self.cache_mem_k.shape[1]
+        blk, cap = self.block, self.capacity
         top_k = self.config.cache_topk
         scale = 1.0 / math.sqrt(hs)
         cos, sin = self._rotary(max(start_index + T, (top_k + 2) * blk) + 1, hs, q.dtype, q.device)
@@ -90,11 +120,8 @@ class MemLMCacheStorage(nn.Module):
             return att_incomplete, {'v': last_v.clone(), 'is_mem': last_mem.clone()}
         n = min(self.cache_size, cap)
         ring_start = self.cache_iter % n if self.cache_size >= cap else 0
-        st = self.cache_mem_k.stride()      # [B, cap, blk, H, D] addressed as (b, h, block, row)
-        kdesc = L.CacheDesc(st[0], st[3], st[1], st[2], n, ring_start, blk, min(top_k, n), 0)
-        sv = self.cache_mem_v.stride()
-        vdesc = L.CacheDesc(sv[0], sv[3], sv[1], sv[2], n, ring_start, blk, min(top_k, n), 0)
-        scores = landmark_scores(q, self.cache_mem_k, kdesc, cos, sin, L.ROTARY_INTERLEAVED, scale, softmax=True)
+        kdesc, vdesc, lmdesc = self._descs(n, ring_start, min(top_k, n))
+        scores = landmark_scores(q, self.cache_lm_k, lmdesc, cos, sin, L.ROTARY_INTERLEAVED, scale, softmax=True)
         sel = topk_sorted(scores, kdesc.top_k, self.config.cache_selection_method, ring_start)
         if sel.shape != (B, nh, T, kdesc.top_k):
             sel = sel.expand(B, nh, T, kdesc.top_k).contiguous()
@@ -111,7 +138,7 @@ class MemLMCacheStorage(nn.Module):
     def store_in_cache(self, keys, values_dict):
         """mem_cache.py:111-158: append whole blocks to the ring buffer, keep the unfinished tail aside."""
         B = keys.shape[0]
-        blk, cap = self.cache_mem_k.shape[2], self.cache_mem_k.shape[1]
+        blk, cap = self.block, self.capacity
         inc0 = self.last_incomplete_len
         k = torch.cat((self.last_incomplete_k[:B, :, :inc0], keys), dim=-2)
         v = torch.cat((self.last_incomplete_v[:B, :, :inc0], values_dict['v']), dim=-2)
@@ -127,19 +154,22 @@ class MemLMCacheStorage(nn.Module):
         assert im[..., -1].all()
         assert not im[..., :-1].any()
         added = im.shape[1]
-        kb = k[:, :, :full].transpose(1, 2).reshape(B, added, blk, nh, hs)
-        vb = v[:, :, :full].transpose(1, 2).reshape(B, added, blk, nh, hs)
-        dropped = max(0, added - cap)
-        kb, vb = kb[:, dropped:], vb[:, dropped:]
+        dropped = max(0, added - cap)           # more blocks than the ring holds: only the newest `cap` are kept
         self.cache_iter = (self.cache_iter + dropped) % cap
         self.cache_size += dropped
         added -= dropped
-        first = min(added, cap - self.cache_iter)
-        self.cache_mem_k[:B, self.cache_iter:self.cache_iter + first].copy_(kb[:, :first])
-        self.cache_mem_v[:B, self.cache_iter:self.cache_iter + first].copy_(vb[:, :first])
-        if added > first:
-            self.cache_mem_k[:B, :added - first].copy_(kb[:, first:])
-            self.cache_mem_v[:B, :added - first].copy_(vb[:, first:])
+        if added > 0:
+            # one kernel writes the blocks into their ring slots (wrapping) and their landmark keys into the dense array
+            ks, vs = k[:, :, dropped * blk:full], v[:, :, dropped * blk:full]
+            if ks.stride(3) != 1 or ks.stride() != vs.stride():
+                ks, vs = ks.contiguous(), vs.contiguous()
+            kdesc, vdesc, _ = self._descs(cap, 0, 0)
+            rc = L.lib().lmk_cache_store(L.ptr(ks), L.ptr(vs), L.I64x3(ks.stride(0), ks.stride(1), ks.stride(2)),
+                                         L.ptr(self.cache_mem_k), L.ptr(self.cache_mem_v), ctypes.byref(kdesc),
+                                         ctypes.byref(vdesc), L.ptr(self.cache_lm_k),
+                                         L.I64x3(*self.cache_lm_k.stride()[:3]), B, nh, added, self.cache_iter, cap, hs,
+                                         L.dtype_code(ks), L.stream_ptr(ks.device))
+            L.check(rc, "lmk_cache_store")
         self.cache_iter = (self.cache_iter + added) % cap if self.cache_iter + added >= cap else self.cache_iter + added
         self.cache_size += added
 

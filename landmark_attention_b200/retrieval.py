@@ -323,3 +323,93 @@ def llama_retrieval_attention(q, k_new, v_new, past_k=None, past_v=None, mem_fre
     if return_debug:
         return out, new_cache(), dict(scores=scores, sel=sel, sel_k=sel_k, sel_v=sel_v, probs=probs)
     return out, new_cache()
+
+
+class OffloadedLandmarkCache:
+    """Landmark block cache whose whole blocks live in pinned HOST memory (llama/llama_mem.py:326-327, 393-398, 427-428:
+    the reference's `offload_cache_to_cpu`).
+
+    What stays on the device: the landmark key of every block (1/block of the keys: enough to score all blocks) and the
+    unfinished tail block.  What crosses the host link per chunk and layer: only the top_k blocks each head selects
+    (one selection per head, the maximum over the chunk's tokens of the softmaxed scores, as the reference does with
+    offloading), read by the gather kernel straight from the mapped pinned buffers -- no host round trip for the indices,
+    no staging copy -- and, in the other direction, the chunk's finished blocks.
+    """
+
+    def __init__(self, batch, heads, capacity_blocks, block, dim, dtype, device):
+        self.block, self.capacity = block, capacity_blocks
+        self.k_host = torch.empty((batch, heads, capacity_blocks * block, dim), dtype=dtype).pin_memory()
+        self.v_host = torch.empty((batch, heads, capacity_blocks * block, dim), dtype=dtype).pin_memory()
+        self.lm_keys = torch.empty((batch, heads, capacity_blocks, dim), dtype=dtype, device=device)
+        self.tail_k = torch.empty((batch, heads, block, dim), dtype=dtype, device=device)
+        self.tail_v = torch.empty((batch, heads, block, dim), dtype=dtype, device=device)
+        self.n_blocks, self.tail_len = 0, 0
+        self.device = torch.device(device)
+
+    @property
+    def length(self):
+        return self.n_blocks * self.block + self.tail_len
+
+    def append(self, k_new, v_new):
+        """Append un-rotated keys / values [B,H,T,D]: finished blocks go to the host buffers (asynchronous copies on the
+        current stream) and their landmark keys to the device array; the rest waits in the device tail."""
+        blk = self.block
+        k = torch.cat((self.tail_k[:, :, :self.tail_len], k_new), dim=2)
+        v = torch.cat((self.tail_v[:, :, :self.tail_len], v_new), dim=2)
+        n_full = k.shape[2] // blk
+        if self.n_blocks + n_full > self.capacity:
+            raise ValueError(f"cache capacity of {self.capacity} blocks exceeded")
+        if n_full:
+            lo, hi = self.n_blocks * blk, (self.n_blocks + n_full) * blk
+            self.k_host[:, :, lo:hi].copy_(k[:, :, :n_full * blk], non_blocking=True)
+            self.v_host[:, :, lo:hi].copy_(v[:, :, :n_full * blk], non_blocking=True)
+            self.lm_keys[:, :, self.n_blocks:self.n_blocks + n_full].copy_(k[:, :, blk - 1:n_full * blk:blk])
+            self.n_blocks += n_full
+        self.tail_len = k.shape[2] - n_full * blk
+        self.tail_k[:, :, :self.tail_len].copy_(k[:, :, n_full * blk:])
+        self.tail_v[:, :, :self.tail_len].copy_(v[:, :, n_full * blk:])
+
+    def attend(self, q, k_new, v_new, cache_top_k, cos=None, sin=None, return_debug=False):
+        """Attention of the chunk q, k_new, v_new [B,H,T,D] (before rotary) over [selected blocks | chunk], then
+        `append`.  Same result as llama_retrieval_attention(..., aggregate="max_over_tokens") on a device-resident
+        cache with the same contents."""
+        from .fused import fused_landmark_attention
+        assert self.tail_len == 0, "offloaded attention needs whole blocks in the cache (as the fused route does)"
+        B, H, T, D = q.shape
+        blk, n, C = self.block, self.n_blocks, self.n_blocks * self.block
+        dev = q.device
+        if cos is None:
+            cos, sin = rotary_tables_half(C + T + 1, D, q.dtype, dev)
+        scale = 1.0 / math.sqrt(D)
+        pos = torch.arange(C, C + T, device=dev)
+        qr, kr = apply_rotary_half(q, cos, sin, pos), apply_rotary_half(k_new, cos, sin, pos)
+        top_k = min(cache_top_k, n)
+        prefix_len = C - (top_k + 1) * blk
+        ls = self.lm_keys.stride()
+        lmdesc = L.CacheDesc(ls[0], ls[1], ls[2], 0, n, 0, blk, top_k, prefix_len)
+        hs = self.k_host.stride()
+        hdesc = L.CacheDesc(hs[0], hs[1], hs[2] * blk, hs[2], n, 0, blk, top_k, prefix_len)
+        probs = landmark_scores(qr, self.lm_keys, lmdesc, cos, sin, L.ROTARY_HALF, scale, softmax=True)
+        sel = topk_sorted(probs, top_k, mode="max_over_tokens")                       # [B,H,1,top_k], on the device
+        # the gather kernel reads the selected blocks from the mapped pinned buffers: top_k * block rows per head
+        sel_k, sel_v = _gather_from_host(self.k_host, self.v_host, hdesc, sel, cos, sin, D, dev)
+        keys = torch.cat((sel_k.view(B, H, top_k * blk, D), kr), dim=2)
+        vals = torch.cat((sel_v.view(B, H, top_k * blk, D), v_new), dim=2)
+        out = fused_landmark_attention(qr, keys, vals, None, sm_scale=scale, block_size=blk)
+        self.append(k_new, v_new)
+        if return_debug:
+            return out, dict(sel=sel, sel_k=sel_k, sel_v=sel_v)
+        return out
+
+
+def _gather_from_host(k_host, v_host, desc, idx, cos, sin, dim, device):
+    """lmk_gather_kv with the cache pointers in pinned (mapped) host memory and the outputs on the device."""
+    B, H, T, top_k = idx.shape
+    k_out = torch.empty((B, H, T, top_k * desc.block, dim), device=device, dtype=k_host.dtype)
+    v_out = torch.empty_like(k_out)
+    assert k_host.is_pinned() and v_host.is_pinned()
+    rc = L.lib().lmk_gather_kv(L.ptr(k_host), L.ptr(v_host), ctypes.byref(desc), ctypes.byref(desc), L.ptr(idx),
+                               L.ptr(cos), L.ptr(sin), cos.shape[0], L.ROTARY_HALF, L.ptr(k_out), L.ptr(v_out), B, H, T,
+                               dim, L.dtype_code(k_host), L.stream_ptr(device))
+    L.check(rc, "lmk_gather_kv")
+    return k_out, v_out

@@ -212,14 +212,15 @@ def test_llama_cache_branch_selected_blocks_match_oracle():
     assert (out.cpu() - exp).abs().max().item() < 1e-4
 
 
+@pytest.mark.parametrize("layout", ["reference", "head_major"])
 @pytest.mark.parametrize("method", ["per_token_and_head", "max_over_heads", "max_over_tokens"])
-def test_block_cache_against_golden(golden, method):
+def test_block_cache_against_golden(golden, method, layout):
     g = golden(f"memcache_{method}.pt")
     r0 = g["records"][0]
     B, H, _, D = r0["q"].shape
     cfg = type("C", (), dict(batch_size=B, mem_cache_size=g["capacity"], mem_cache_freq=g["blk"] - 1, n_head=H,
                              n_embd=H * D, cache_topk=g["top_k"], cache_selection_method=method))()
-    store = P.MemLMCacheStorage(cfg, None, dtype=torch.float32, device=DEV)
+    store = P.MemLMCacheStorage(cfg, None, dtype=torch.float32, device=DEV, layout=layout)
     for r in g["records"]:
         att, d = store.retrieve_for_query(r["q"].to(DEV), None, None, r["start_index"])
         assert att.shape == r["att_prefix"].shape
@@ -380,3 +381,28 @@ def test_max_over_tokens_route():
     ek = O.rotary_half_split(ek, kpos).view(B, H, top_k * blk, D)
     exp = O.landmark_attention(qr, torch.cat((ek, kr), 2), torch.cat((ev, v), 2), blk)
     assert (out.cpu() - exp).abs().max().item() < 1e-4
+
+
+def test_offloaded_cache_reads_only_selected_blocks_from_host():
+    # whole blocks in pinned host memory, landmark keys on the device; same attention as the device-resident cache
+    torch.manual_seed(15)
+    B, H, D, blk, top_k = 1, 3, 64, 16, 2
+    dtype = torch.float32
+    C0, T = blk * 10, 32
+    pk, pv = torch.randn(B, H, C0, D).to(DEV), torch.randn(B, H, C0, D).to(DEV)
+    off = P.OffloadedLandmarkCache(B, H, 16, blk, D, dtype, DEV)
+    off.append(pk, pv)
+    assert off.n_blocks == 10 and off.tail_len == 0 and off.k_host.is_pinned() and not off.k_host.is_cuda
+    past = (pk, pv)
+    for step in range(2):
+        q, k, v = [torch.randn(B, H, T, D).to(DEV) for _ in range(3)]
+        ref, past, dbg = P.llama_retrieval_attention(q, k, v, past[0], past[1], blk - 1, top_k,
+                                                     aggregate="max_over_tokens", return_debug=True)
+        got, odbg = off.attend(q, k, v, top_k, return_debug=True)
+        assert torch.equal(odbg["sel"], dbg["sel"])
+        assert torch.equal(odbg["sel_k"], dbg["sel_k"]) and torch.equal(odbg["sel_v"], dbg["sel_v"])
+        assert torch.equal(got, ref)
+    torch.cuda.synchronize()
+    assert off.n_blocks == 14
+    assert torch.equal(off.k_host[:, :, :off.length].to(DEV), past[0])
+    assert torch.equal(off.lm_keys[:, :, :off.n_blocks], past[0][:, :, blk - 1::blk])
