@@ -42,9 +42,9 @@ def measured_peaks():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at the benchmark shape, from an ncu capture of this script
-# (cold L2): forward 50.4 MB; backward = dQ launch 84.9 MB + dK/dV launch 70.5 MB.  The algorithmic operand bytes are
+# (cold L2): forward 50.4 MB; backward = dQ launch 84.9 MB + dK/dV launch 70.8 MB.  The algorithmic operand bytes are
 # 50.3 MB (q, k, v) and 84 + 67 MB (q, k, v, o, dO / q, k, v, dO): nothing is re-read from HBM; results stay in L2.
-DRAM_TRAFFIC = {"forward": 50.4e6, "backward": 155.4e6}
+DRAM_TRAFFIC = {"forward": 50.4e6, "backward": 155.7e6}
 # dram read + write of one gather_kv launch at the retrieval shape, from an ncu capture (profiles/gather_kv_config4.md)
 GATHER_DRAM_BYTES = 808e6
 

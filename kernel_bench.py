@@ -28,6 +28,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--only", default="both", choices=["both", "fwd", "bwd"])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
+    ap.add_argument("--masked", action="store_true",
+                    help="time the arbitrary-landmark fused attention (lmk_attn_mask_fwd / _bwd) instead: a landmark after "
+                         "every block-1 tokens at a different random window offset per batch row")
     ap.add_argument("--grouped-softmax", action="store_true",
                     help="time the stand-alone grouped softmax (forward and backward) on [B,H,L,L] fp32 logits instead")
     a = ap.parse_args()
@@ -35,6 +38,8 @@ def main():
     dev = torch.device("cuda")
     if a.grouped_softmax:
         return grouped_softmax_bench(a, dev)
+    if a.masked:
+        return masked_bench(a, dt, dev)
     g = torch.Generator().manual_seed(0)
     B, H, Lq, D = a.B, a.H, a.L, a.D
     q, k, v = [(torch.randn(B, H, Lq, D, generator=g) * 0.5).to(dt).to(dev) for _ in range(3)]
@@ -82,6 +87,38 @@ def main():
         parts.append(f"bwd {t:.1f} us ({5 * fl / t / 1e6:.0f} TFLOP/s)")
     parts.append(f"status {L.device_status()}")
     print("  ".join(parts))
+
+
+def masked_bench(a, dt, dev):
+    """Forward and backward of the arbitrary-landmark operator through its registered ops (one C-ABI call each)."""
+    from landmark_attention_b200.masked import _bwd, _fwd
+    B, H, T, D = a.B, a.H, a.L, a.D
+    g = torch.Generator().manual_seed(0)
+    q, k, v = [(torch.randn(B, H, T, D, generator=g) * 0.5).to(dt).to(dev) for _ in range(3)]
+    do = torch.randn(B, H, T, D, generator=g).to(dt).to(dev)
+    offs = torch.randint(0, a.block, (B,), generator=g)
+    im = ((torch.arange(T).view(1, T) + offs.view(B, 1)) % a.block == a.block - 1).to(dev)
+    groups = min(64, T // a.block + 2)
+    scale = D ** -0.5
+    o, R, A = _fwd(q, k, v, im, scale, groups)
+
+    def timeit(f):
+        for _ in range(a.warmup):
+            f()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.iters):
+            f()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / a.iters * 1e3
+
+    fl = B * H * T * T * D
+    t_f = timeit(lambda: _fwd(q, k, v, im, scale, groups))
+    t_b = timeit(lambda: _bwd(q, k, v, im, o, do, R, A, scale, groups))
+    print(f"masked B={B} H={H} T={T} D={D} landmark every {a.block} {a.dtype}  fwd {t_f:.1f} us ({2 * fl / t_f / 1e6:.0f} TFLOP/s)  "
+          f"bwd {t_b:.1f} us ({5 * fl / t_b / 1e6:.0f} TFLOP/s)  status {L.device_status()}")
 
 
 def grouped_softmax_bench(a, dev):
