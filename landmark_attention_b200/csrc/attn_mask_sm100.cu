@@ -63,17 +63,22 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
-// one row (64 16-bit values as 32 packed words) of a [128 x 64] K-major tile with the 128-byte swizzle
-__device__ __forceinline__ void store_row_sw128(uint32_t tile_base, int row, const uint32_t (&w)[32]) {
+// Tiles written by the softmax threads are [128 x 64] 16-bit, K-major, with the 128-byte swizzle.
+// 16 consecutive keys (8 packed words) of one row of such a tile: 16-byte chunks 2c and 2c+1 of the row
+__device__ __forceinline__ void store_row16_sw128(uint32_t tile_base, int row, int c, const uint32_t (&w)[8]) {
   const uint32_t row_addr = tile_base + row * 128;
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    uint32_t addr = row_addr + ((c ^ (row & 7)) << 4);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * c]), "r"(w[4 * c + 1]),
-                 "r"(w[4 * c + 2]), "r"(w[4 * c + 3])
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t addr = row_addr + (((2 * c + h) ^ (row & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * h]), "r"(w[4 * h + 1]),
+                 "r"(w[4 * h + 2]), "r"(w[4 * h + 3])
                  : "memory");
   }
 }
+
+// The softmax threads walk a 64-key tile in four chunks of 16 keys loaded from TMEM inside a runtime loop: the code of
+// one chunk (a branch-free path for chunks without a landmark, a per-key path otherwise) stays resident in the
+// instruction cache and the row needs 16 registers instead of 64.
 
 // ---------------------------------------------------------------------------------------------- landmark bookkeeping
 // kmask[t] bit j = key 64 t + j of batch row b is a landmark; gbase[t] = landmarks before tile t.  Built by the
@@ -290,78 +295,86 @@ sm100_mask_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const int kt = i < n_kt ? i : i - n_kt;
       mbar_wait(smem_u32(&sm->s_full[sb]), (i / 2) & 1, status, kErrMaskFwd + 2);
       tc_fence_after();
-      float sv[64];
-      {
-        uint32_t ra[32], rb[32];
-        tmem_ld_32x32b_x32(tmem_s0 + sb * 64 + lane_base, ra);
-        tmem_ld_32x32b_x32(tmem_s0 + sb * 64 + 32 + lane_base, rb);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          sv[j] = __uint_as_float(ra[j]) * scale_log2;
-          sv[32 + j] = __uint_as_float(rb[j]) * scale_log2;
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&sm->s_free[sb]));
       const RowTile rt = row_tile(kt, kd, jl_own);
       const uint64_t mask = kmask[kt];
       int g = gbase[kt];
-      if (i < n_kt) {
-        // ---------------- pass 1: statistics
+      const uint32_t ts = tmem_s0 + sb * 64 + lane_base;
+      auto zof = [&](int gg) { return gg < c_row ? Asm[(gg < G ? gg : G - 1) * kQT + row] + R : R; };
+      float z = i < n_kt ? 0.f : zof(g);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float sv[16];
+        {
+          uint32_t xr[16];
+          tmem_ld_32x32b_x16(ts + c * 16, xr);
+          tmem_ld_wait();
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
-          if (((mask >> (4 * c4)) & 0xfull) == 0ull) {       // no landmark among these four keys (uniform)
-            const int j = 4 * c4;
-            grp.add4(j <= rt.lim ? sv[j] : -INFINITY, j + 1 <= rt.lim ? sv[j + 1] : -INFINITY,
-                     j + 2 <= rt.lim ? sv[j + 2] : -INFINITY, j + 3 <= rt.lim ? sv[j + 3] : -INFINITY);
+          for (int e = 0; e < 16; ++e) sv[e] = __uint_as_float(xr[e]) * scale_log2;
+        }
+        if (c == 3) {                 // the S buffer has been read for the last time
+          tc_fence_before();
+          mbar_arrive(smem_u32(&sm->s_free[sb]));
+        }
+        const uint32_t m16 = (uint32_t)(mask >> (16 * c)) & 0xffffu;      // uniform
+        const int j0 = 16 * c;
+        if (i < n_kt) {
+          // ---------------- pass 1: statistics
+          if (m16 == 0u) {
+#pragma unroll
+            for (int e = 0; e < 16; e += 4)
+              grp.add4(j0 + e <= rt.lim ? sv[e] : -INFINITY, j0 + e + 1 <= rt.lim ? sv[e + 1] : -INFINITY,
+                       j0 + e + 2 <= rt.lim ? sv[e + 2] : -INFINITY, j0 + e + 3 <= rt.lim ? sv[e + 3] : -INFINITY);
           } else {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = 4 * c4 + e;
-              if ((mask >> j) & 1ull) {                       // landmark (uniform)
+            for (int e = 0; e < 16; ++e) {
+              const int j = j0 + e;
+              if ((m16 >> e) & 1u) {                          // landmark (uniform)
                 if (j <= rt.lim && j != rt.own) {             // it closes group g for this row
-                  const float A = grp.s > 0.f ? grp.m + __log2f(grp.s) - sv[j] : INFINITY;
+                  const float A = grp.s > 0.f ? grp.m + __log2f(grp.s) - sv[e] : INFINITY;
                   if (g < G) Asm[g * kQT + row] = A;
-                  outer.add(sv[j]);
+                  outer.add(sv[e]);
                   grp.reset();
                 }
                 ++g;
               } else if (j <= rt.lim) {
-                grp.add(sv[j]);
+                grp.add(sv[e]);
               }
             }
           }
-        }
-        if (i == n_kt - 1) {
-          // the open group is the row's own section: its keys enter the outer softmax directly
-          if (grp.s > 0.f) outer.merge(grp.m, grp.s);
-          R = outer.s > 0.f ? outer.m + __log2f(outer.s) : INFINITY;
-        }
-      } else {
-        // ---------------- pass 2: probabilities
-        uint32_t w[32];
-        auto zof = [&](int gg) { return gg < c_row ? Asm[(gg < G ? gg : G - 1) * kQT + row] + R : R; };
-        float z = zof(g);
+        } else {
+          // ---------------- pass 2: probabilities
+          uint32_t w[8];
+          if (m16 == 0u) {
 #pragma unroll
-        for (int jp = 0; jp < 32; ++jp) {
-          float p[2];
+            for (int e = 0; e < 16; e += 2)
+              w[e / 2] = pack2<kBf16>(j0 + e <= rt.lim ? ex2(sv[e] - z) : 0.f,
+                                      j0 + e + 1 <= rt.lim ? ex2(sv[e + 1] - z) : 0.f);
+          } else {
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int j = 2 * jp + e;
-            if ((mask >> j) & 1ull) {                         // landmark keys carry no weight; next group starts
-              p[e] = 0.f;
-              ++g;
-              z = zof(g);
-            } else {
-              p[e] = j <= rt.lim ? ex2(sv[j] - z) : 0.f;
+            for (int e = 0; e < 16; e += 2) {
+              float p[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                if ((m16 >> (e + h)) & 1u) {                  // landmark keys carry no weight; next group starts
+                  p[h] = 0.f;
+                  ++g;
+                  z = zof(g);
+                } else {
+                  p[h] = j0 + e + h <= rt.lim ? ex2(sv[e + h] - z) : 0.f;
+                }
+              }
+              w[e / 2] = pack2<kBf16>(p[0], p[1]);
             }
           }
-          w[jp] = pack2<kBf16>(p[0], p[1]);
+          store_row16_sw128(k_slot(s), row, c, w);
         }
-        store_row_sw128(k_slot(s), row, w);
-        fence_proxy_async_smem();
       }
+      if (i == n_kt - 1) {
+        // the open group is the row's own section: its keys enter the outer softmax directly
+        if (grp.s > 0.f) outer.merge(grp.m, grp.s);
+        R = outer.s > 0.f ? outer.m + __log2f(outer.s) : INFINITY;
+      }
+      if (i >= n_kt) fence_proxy_async_smem();
       mbar_arrive(smem_u32(&sm->p_ready[s]));
     }
     // statistics for the backward pass: R per row, A per (group, row) for the groups the row sees
@@ -591,74 +604,92 @@ sm100_mask_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
       const int kt = i < n_kt ? i : i - n_kt;
       mbar_wait(smem_u32(&sm->sdp_full[sb]), (i / 2) & 1, status, kErrMaskDq + 2);
       tc_fence_after();
-      float xv[64], dp[64];
-      {
-        uint32_t ra[32], rb[32];
-        tmem_ld_32x32b_x32(tmem_s + sb * 64 + lane_base, ra);
-        tmem_ld_32x32b_x32(tmem_s + sb * 64 + 32 + lane_base, rb);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          xv[j] = __uint_as_float(ra[j]) * scale_log2;
-          xv[32 + j] = __uint_as_float(rb[j]) * scale_log2;
-        }
-        tmem_ld_32x32b_x32(tmem_dp + sb * 64 + lane_base, ra);
-        tmem_ld_32x32b_x32(tmem_dp + sb * 64 + 32 + lane_base, rb);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          dp[j] = __uint_as_float(ra[j]);
-          dp[32 + j] = __uint_as_float(rb[j]);
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&sm->sdp_free[sb]));
       const RowTile rt = row_tile(kt, kd, jl_own);
       const uint64_t mask = kmask[kt];
       int g = gbase[kt];
       float z = zof(g);
-      if (i < n_kt) {
-        // ---------------- pass 1: nD_g = (sum_{j in g} P_j dP_j) / G_g for every closed group
+      float sub = (i >= n_kt && g < c_row) ? nDsm[(g < G ? g : G - 1) * kQT + row] : delta;
+      const uint32_t ts = tmem_s + sb * 64 + lane_base, td = tmem_dp + sb * 64 + lane_base;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float xv[16], dp[16];
+        {
+          uint32_t xr[16], dr[16];
+          tmem_ld_32x32b_x16(ts + c * 16, xr);
+          tmem_ld_32x32b_x16(td + c * 16, dr);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          if ((mask >> j) & 1ull) {
-            if (j <= rt.lim && j != rt.own) {
-              const float Gp = ex2(xv[j] - R);
-              const float nd = Gp > 0.f ? __fdividef(T, Gp) : 0.f;
-              if (g < G) nDsm[g * kQT + row] = nd;
-              T = 0.f;
-            }
-            ++g;
-            z = zof(g);
-          } else if (j <= rt.lim) {
-            T = fmaf(ex2(xv[j] - z), dp[j], T);
+          for (int e = 0; e < 16; ++e) {
+            xv[e] = __uint_as_float(xr[e]) * scale_log2;
+            dp[e] = __uint_as_float(dr[e]);
           }
         }
-      } else {
-        // ---------------- pass 2: dS
-        float sub = g < c_row ? nDsm[(g < G ? g : G - 1) * kQT + row] : delta;
-        uint32_t w[32];
+        if (c == 3) {                 // S and dP have been read for the last time
+          tc_fence_before();
+          mbar_arrive(smem_u32(&sm->sdp_free[sb]));
+        }
+        const uint32_t m16 = (uint32_t)(mask >> (16 * c)) & 0xffffu;      // uniform
+        const int j0 = 16 * c;
+        if (i < n_kt) {
+          // ---------------- pass 1: nD_g = (sum_{j in g} P_j dP_j) / G_g for every closed group
+          if (m16 == 0u) {
+            float t0 = 0.f, t1 = 0.f;                          // two chains instead of one 16-deep dependency
 #pragma unroll
-        for (int jp = 0; jp < 32; ++jp) {
-          float d[2];
+            for (int e = 0; e < 16; e += 2) {
+              t0 = fmaf(j0 + e <= rt.lim ? ex2(xv[e] - z) : 0.f, dp[e], t0);
+              t1 = fmaf(j0 + e + 1 <= rt.lim ? ex2(xv[e + 1] - z) : 0.f, dp[e + 1], t1);
+            }
+            T += t0 + t1;
+          } else {
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int j = 2 * jp + e;
-            if ((mask >> j) & 1ull) {
-              // landmark l_g: dS = G_g (nD_g - delta) scale when it closes a group for this row (then sub = nD_g)
-              d[e] = (j <= rt.lim && j != rt.own) ? ex2(xv[j] - R) * (sub - delta) * scale : 0.f;
-              ++g;
-              z = zof(g);
-              sub = g < c_row ? nDsm[(g < G ? g : G - 1) * kQT + row] : delta;
-            } else {
-              d[e] = j <= rt.lim ? ex2(xv[j] - z) * (dp[j] - sub) * scale : 0.f;
+            for (int e = 0; e < 16; ++e) {
+              const int j = j0 + e;
+              if ((m16 >> e) & 1u) {
+                if (j <= rt.lim && j != rt.own) {
+                  const float Gp = ex2(xv[e] - R);
+                  const float nd = Gp > 0.f ? __fdividef(T, Gp) : 0.f;
+                  if (g < G) nDsm[g * kQT + row] = nd;
+                  T = 0.f;
+                }
+                ++g;
+                z = zof(g);
+              } else if (j <= rt.lim) {
+                T = fmaf(ex2(xv[e] - z), dp[e], T);
+              }
             }
           }
-          w[jp] = pack2<kBf16>(d[0], d[1]);
+        } else {
+          // ---------------- pass 2: dS
+          uint32_t w[8];
+          if (m16 == 0u) {
+#pragma unroll
+            for (int e = 0; e < 16; e += 2)
+              w[e / 2] = pack2<kBf16>(j0 + e <= rt.lim ? ex2(xv[e] - z) * (dp[e] - sub) * scale : 0.f,
+                                      j0 + e + 1 <= rt.lim ? ex2(xv[e + 1] - z) * (dp[e + 1] - sub) * scale : 0.f);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; e += 2) {
+              float d[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int j = j0 + e + h;
+                if ((m16 >> (e + h)) & 1u) {
+                  // landmark l_g: dS = G_g (nD_g - delta) scale when it closes a group for this row (then sub = nD_g)
+                  d[h] = (j <= rt.lim && j != rt.own) ? ex2(xv[e + h] - R) * (sub - delta) * scale : 0.f;
+                  ++g;
+                  z = zof(g);
+                  sub = g < c_row ? nDsm[(g < G ? g : G - 1) * kQT + row] : delta;
+                } else {
+                  d[h] = j <= rt.lim ? ex2(xv[e + h] - z) * (dp[e + h] - sub) * scale : 0.f;
+                }
+              }
+              w[e / 2] = pack2<kBf16>(d[0], d[1]);
+            }
+          }
+          store_row16_sw128(v_slot(s), row, c, w);
         }
-        store_row_sw128(v_slot(s), row, w);
-        fence_proxy_async_smem();
       }
+      if (i >= n_kt) fence_proxy_async_smem();
       mbar_arrive(smem_u32(&sm->ds_ready[s]));
     }
     {
@@ -915,59 +946,70 @@ sm100_mask_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       float z = zq[0];
       mbar_wait(smem_u32(&sm->sdp_full[sb]), (i / 2) & 1, status, kErrMaskDkv + 2);
       tc_fence_after();
-      float xv[64], dp[64];
-      {
-        uint32_t ra[32], rb[32];
-        tmem_ld_32x32b_x32(tmem_s + sb * 64 + lane_base, ra);
-        tmem_ld_32x32b_x32(tmem_s + sb * 64 + 32 + lane_base, rb);
-        tmem_ld_wait();
+      // the P / dS tiles are free once the accumulating products of the previous item have read them
+      if (i >= 1) mbar_wait(smem_u32(&sm->pds_free), (i - 1) & 1, status, kErrMaskDkv + 2);
+      const uint32_t ts = tmem_s + sb * 64 + lane_base, td = tmem_dp + sb * 64 + lane_base;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float xv[16], dp[16];
+        {
+          uint32_t xr[16], dr[16];
+          tmem_ld_32x32b_x16(ts + c * 16, xr);
+          tmem_ld_32x32b_x16(td + c * 16, dr);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          xv[j] = __uint_as_float(ra[j]) * scale_log2;
-          xv[32 + j] = __uint_as_float(rb[j]) * scale_log2;
-        }
-        tmem_ld_32x32b_x32(tmem_dp + sb * 64 + lane_base, ra);
-        tmem_ld_32x32b_x32(tmem_dp + sb * 64 + 32 + lane_base, rb);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          dp[j] = __uint_as_float(ra[j]);
-          dp[32 + j] = __uint_as_float(rb[j]);
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&sm->sdp_free[sb]));
-      uint32_t wp[32], wd[32];
-#pragma unroll
-      for (int jp = 0; jp < 32; ++jp) {
-        float p[2], d[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int j = 2 * jp + e;
-          if ((mask >> j) & 1ull) {
-            p[e] = 0.f;
-            d[e] = (j <= lim && j != own) ? ex2(xv[j] - R) * (sub - delta) * scale : 0.f;
-            ++g;
-            ++gi;
-            if (gi < 4) {
-              z = gi == 1 ? zq[1] : (gi == 2 ? zq[2] : zq[3]);
-              sub = gi == 1 ? sq[1] : (gi == 2 ? sq[2] : sq[3]);
-            } else {
-              lmpos = closing(j + 1);
-              z = zof(g, lmpos, sub);
-            }
-          } else {
-            const float pj = j <= lim ? ex2(xv[j] - z) : 0.f;
-            p[e] = pj;
-            d[e] = pj * (dp[j] - sub) * scale;
+          for (int e = 0; e < 16; ++e) {
+            xv[e] = __uint_as_float(xr[e]) * scale_log2;
+            dp[e] = __uint_as_float(dr[e]);
           }
         }
-        wp[jp] = pack2<kBf16>(p[0], p[1]);
-        wd[jp] = pack2<kBf16>(d[0], d[1]);
+        if (c == 3) {
+          tc_fence_before();
+          mbar_arrive(smem_u32(&sm->sdp_free[sb]));
+        }
+        const uint32_t m16 = (uint32_t)(mask >> (16 * c)) & 0xffffu;      // uniform
+        const int j0 = 16 * c;
+        uint32_t wp[8], wd[8];
+        if (m16 == 0u) {
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            const float p0 = j0 + e <= lim ? ex2(xv[e] - z) : 0.f;
+            const float p1 = j0 + e + 1 <= lim ? ex2(xv[e + 1] - z) : 0.f;
+            wp[e / 2] = pack2<kBf16>(p0, p1);
+            wd[e / 2] = pack2<kBf16>(p0 * (dp[e] - sub) * scale, p1 * (dp[e + 1] - sub) * scale);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            float p[2], d[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int j = j0 + e + h;
+              if ((m16 >> (e + h)) & 1u) {
+                p[h] = 0.f;
+                d[h] = (j <= lim && j != own) ? ex2(xv[e + h] - R) * (sub - delta) * scale : 0.f;
+                ++g;
+                ++gi;
+                if (gi < 4) {
+                  z = gi == 1 ? zq[1] : (gi == 2 ? zq[2] : zq[3]);
+                  sub = gi == 1 ? sq[1] : (gi == 2 ? sq[2] : sq[3]);
+                } else {
+                  lmpos = closing(j + 1);
+                  z = zof(g, lmpos, sub);
+                }
+              } else {
+                const float pj = j <= lim ? ex2(xv[e + h] - z) : 0.f;
+                p[h] = pj;
+                d[h] = pj * (dp[e + h] - sub) * scale;
+              }
+            }
+            wp[e / 2] = pack2<kBf16>(p[0], p[1]);
+            wd[e / 2] = pack2<kBf16>(d[0], d[1]);
+          }
+        }
+        store_row16_sw128(p_tile, row, c, wp);
+        store_row16_sw128(ds_tile, row, c, wd);
       }
-      if (i >= 1) mbar_wait(smem_u32(&sm->pds_free), (i - 1) & 1, status, kErrMaskDkv + 2);
-      store_row_sw128(p_tile, row, wp);
-      store_row_sw128(ds_tile, row, wd);
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(&sm->pds_ready));
     }
