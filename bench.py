@@ -342,10 +342,12 @@ def bench_grouped_softmax(P, L, dev, peaks):
     res = {}
     for name, (B, H, T, blk) in {"16x8x512x512_block51": (16, 8, 512, 51), "4x32x2048x2048_block64": (4, 32, 2048, 64)}.items():
         g = torch.Generator(device=dev).manual_seed(5)
-        x = torch.randn(B, H, T, T, generator=g, device=dev, requires_grad=True)
+        x = torch.randn(B, H, T, T, generator=g, device=dev)
         is_mem_row = (torch.arange(T, device=dev) % blk == blk - 1).view(1, T).expand(B, T)
         hidden = torch.ones(T, T, dtype=torch.bool, device=dev).triu(1)
         mask, is_mem, last = prepare_landmark_masks(is_mem_row, hidden)
+        # the call site fills the hidden scores with -inf before the softmax (lm_benchmark/models/landmark.py:224)
+        x = x.masked_fill_(mask, float("-inf")).requires_grad_(True)
         grad = torch.randn(B, H, T, T, generator=g, device=dev)
         mg = T // blk + 3
 

@@ -170,7 +170,7 @@ int lmk_attn_mask_bwd(const void* q, const void* k, const void* v, const uint8_t
  * Replaces LandmarkGroupedSoftmaxFunction.forward + landmark_grouped_softmax
  *   (llama/llama_mem.py:168-243; lm_benchmark/models/landmark.py:37-119).
  *   x: dtype `dtype`, element strides x_strides {b,h,row}, last dim contiguous.
- *   is_mem, last_section, hidden (nullable): bool bytes, broadcastable, element strides {b,h,row,col}
+ *   is_mem, last_section, hidden (nullable): bool bytes (0 or 1), broadcastable, element strides {b,h,row,col}
  *     (0 = broadcast).  `hidden` is the lm_benchmark attn_mask argument.
  *   probs: fp32 dense [B,H,Lq,Lk].  group_prob (nullable): fp32 dense [B,H,Lq,max_mem_cnt]
  *     (slot g = probability of the landmark closing group g, last slot = total last-section probability).

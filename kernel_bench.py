@@ -132,6 +132,7 @@ def grouped_softmax_bench(a, dev):
     is_mem_row = (torch.arange(Lq, device=dev) % a.block == a.block - 1).view(1, Lq)
     hidden = torch.ones(Lq, Lq, dtype=torch.bool, device=dev).triu(1)
     mask, is_mem, last = prepare_landmark_masks(is_mem_row, hidden)
+    x.masked_fill_(mask, float("-inf"))            # as the call site does (lm_benchmark/models/landmark.py:224)
     grad = torch.randn(B, H, Lq, Lq, generator=g).to(dev)
     probs, gx = torch.empty_like(x), torch.empty_like(x)
     max_groups = Lq // a.block + 2

@@ -16,7 +16,7 @@ def _as_u8(mask):
         return None
     if mask.dtype == torch.bool:
         return mask.view(torch.uint8) if mask.is_contiguous() or mask.dim() == 0 else mask.to(torch.uint8)
-    return mask.to(torch.uint8)
+    return (mask != 0).to(torch.uint8)        # the kernels read bit 0 of every byte
 
 
 def _prep(x, is_mem, last, hidden):

@@ -69,3 +69,39 @@ def test_long_rows_and_many_groups():
     exp = O.grouped_softmax(xm, is_mem, last, attn_mask=mask, guards=True)
     got, _ = P.landmark_grouped_softmax_lm(xm.to(DEV), -1, is_mem.to(DEV), mask.to(DEV), last.to(DEV), False, 130)
     assert (got.cpu() - exp).abs().max().item() < 1e-6
+
+
+@pytest.mark.parametrize("Lk,density,dtype", [(333, 0.3, torch.float32), (1000, 0.05, torch.float32),
+                                               (2048, 0.02, torch.bfloat16), (777, 0.5, torch.float16),
+                                               (4096, 0.01, torch.float32), (5000, 0.01, torch.float32)])
+@pytest.mark.parametrize("guards", [True, False])
+def test_random_masks_any_length(Lk, density, dtype, guards):
+    # arbitrary landmark positions (several per eight keys at the higher densities), row lengths that are not a
+    # multiple of the vector width, rows that start at unaligned addresses, both flavours, forward and backward
+    g = torch.Generator().manual_seed(Lk)
+    B, H, Lq = 2, 2, 5
+    is_mem = torch.rand(B, 1, Lq, Lk, generator=g) < density
+    last = (torch.rand(B, 1, Lq, Lk, generator=g) < 0.1) & ~is_mem
+    last[..., 0] = True
+    is_mem[..., 0] = False
+    hidden = (torch.rand(1, 1, Lq, Lk, generator=g) < 0.2) & ~last & ~is_mem if guards else None
+    x = (torch.randn(B, H, Lq, Lk, generator=g) * 3).to(dtype)
+    if guards:
+        x = x.masked_fill(hidden, float("-inf"))
+    gp = torch.randn(B, H, Lq, Lk, generator=g)
+    n_lm = int(is_mem.sum(-1).max()) + 2
+    xo = x.float().detach().requires_grad_(True)
+    exp = O.grouped_softmax(xo, is_mem, last, attn_mask=hidden, guards=guards)
+    (gx_exp,) = torch.autograd.grad(exp, [xo], gp)
+    xd = x.to(DEV).detach().requires_grad_(True)
+    if guards:
+        got, _ = P.landmark_grouped_softmax_lm(xd, -1, is_mem.to(DEV), hidden.to(DEV), last.to(DEV), False, n_lm)
+    else:
+        got = P.landmark_grouped_softmax(xd, -1, is_mem.to(DEV), last.to(DEV), max_groups=n_lm)
+    assert (got.detach().cpu() - exp.detach()).abs().max().item() < 2e-6
+    (gx,) = torch.autograd.grad(got, [xd], gp.to(DEV))
+    tol = 2e-5 if dtype == torch.float32 else 2e-2          # the gradient is rounded to the 16-bit input type
+    assert (gx.float().cpu() - gx_exp).abs().max().item() < tol
+    again = P.landmark_grouped_softmax_lm(xd, -1, is_mem.to(DEV), hidden.to(DEV), last.to(DEV), False, n_lm)[0] \
+        if guards else P.landmark_grouped_softmax(xd, -1, is_mem.to(DEV), last.to(DEV), max_groups=n_lm)
+    assert torch.equal(again, got)                           # sums are taken in a fixed order
