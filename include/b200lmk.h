@@ -237,6 +237,27 @@ int lmk_cache_store(const void* k_src, const void* v_src, const int64_t src_stri
                     int dtype, void* stream);
 
 /*
+ * Everything a LLaMA layer does to one chunk's projections before its landmark attention, in one launch
+ * (replaces apply_rotary_pos_emb on the chunk, llama/llama_mem.py:127-149 and :335, and the cache concatenation of
+ * :424-425; the padded copies and flags feed lmk_attn_mask_fwd).  16-bit types, rotate-half rotary.
+ *   q, k, v [B,H,T,D] un-rotated, element strides {batch, head, row}, last dim contiguous.
+ *   cos_table, sin_table [n_pos, D] of the same dtype; row t is rotated at position min(pos0 + t, n_pos - 1) with the
+ *     roundings of the tensor formulation (x * cos and rotate_half(x) * sin rounded, then their sum).
+ *   q_rot [B,H,T,D] dense: rotated queries.  q_pad, k_pad, v_pad [B,H,t_pad,D] dense: rotated queries, rotated keys and
+ *     values with rows T .. t_pad-1 zero.  flags_pad [B,t_pad]: landmark flags of the rows, chunk_flags[t] (T bytes,
+ *     nullable) or (pos0 + t) % block == block - 1; 0 for padding rows.
+ *   cache_k, cache_v (nullable, both or none): un-rotated k, v are also written to rows cache_pos .. cache_pos + T - 1
+ *     of a cache addressed with element strides cache_strides {batch, head, row}.
+ * All pointers 16-byte aligned, strides multiples of 8 elements, D a power of two times 16 up to 2048.
+ */
+int lmk_chunk_prepare(const void* q, const void* k, const void* v, const int64_t q_strides[3],
+                      const int64_t k_strides[3], const int64_t v_strides[3], const void* cos_table,
+                      const void* sin_table, int n_pos, int64_t pos0, const uint8_t* chunk_flags, int block,
+                      void* q_rot, void* q_pad, void* k_pad, void* v_pad, uint8_t* flags_pad, void* cache_k,
+                      void* cache_v, const int64_t cache_strides[3], int64_t cache_pos, int B, int H, int T, int t_pad,
+                      int D, int dtype, void* stream);
+
+/*
  * Landmark scores: scores[b,h,t,n] = sm_scale * q[b,h,t,:] . rot(K[b,h,n,block-1,:], slot position of n).
  * Replaces llama/llama_mem.py:357-367 and lm_benchmark/models/caches/mem_cache.py:51-61.
  *   q [B,H,T,D] dense (already rotated), k_cache per desc, cos/sin tables [n_pos, D] in `dtype` (NULL with

@@ -61,6 +61,10 @@ PROTOTYPES = {
     "lmk_cache_store": (c_int, [c_void_p, c_void_p, POINTER(c_int64), c_void_p, c_void_p, POINTER(CacheDesc),
                                 POINTER(CacheDesc), c_void_p, POINTER(c_int64), c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p]),
+    "lmk_chunk_prepare": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(c_int64), POINTER(c_int64), POINTER(c_int64),
+                                  c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_void_p, POINTER(c_int64), c_int64, c_int, c_int,
+                                  c_int, c_int, c_int, c_int, c_void_p]),
     "lmk_landmark_scores_workspace": (c_size_t, [c_int] * 6),
     "lmk_landmark_scores": (c_int, [c_void_p, c_void_p, POINTER(CacheDesc), c_void_p, c_void_p, c_int, c_int,
                                     c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_size_t,

@@ -622,7 +622,7 @@ __global__ void __launch_bounds__(128) selected_pv_kernel(const T* __restrict__ 
 // This is the grouped softmax of llama/llama_mem.py:222-243 over [selected blocks | local keys] written out for the
 // prefix pattern of :415 (every selected block is a closed group whose last row is its landmark).
 template <typename T, int LPR>
-__global__ void __launch_bounds__(128) selected_attend_kernel(const T* __restrict__ q, const T* __restrict__ kc,
+__global__ void __launch_bounds__(128, 8) selected_attend_kernel(const T* __restrict__ q, const T* __restrict__ kc,
                                                               lmk_cache_desc kd, const T* __restrict__ vc,
                                                               lmk_cache_desc vd, const int32_t* __restrict__ idx,
                                                               const T* __restrict__ cos_t, const T* __restrict__ sin_t,

@@ -75,7 +75,31 @@ def fused_landmark_attention(q, k, v, is_mem=None, sm_scale=None, block_size=64,
     n_history_blocks = n_history_kv // block_size
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(q.size(-1))
+    if path == L.PATH_AUTO and block_size != 64:
+        # the tensor-core kernels of lmk_attn_fwd are built for blocks of 64; other block sizes run on the
+        # arbitrary-landmark tensor-core kernels with the regular pattern as flags, where those take the shape
+        from .masked import landmark_attention_masked, masked_attention_supported
+        Lk = k.shape[2]
+        groups = max(Lk // block_size, 1)          # landmarks in front of any query
+        if groups <= 64 and sm_scale > 0 and masked_attention_supported(q, k, groups):
+            return landmark_attention_masked(q, k, v, _regular_flags(q.shape[0], Lk, block_size, q.device), sm_scale,
+                                             groups)
     return FusedLandmarkAttention.apply(q, k, v, n_history_blocks, sm_scale, block_size, path)
+
+
+_FLAGS = {}
+
+
+def _regular_flags(batch, n_keys, block_size, device):
+    """uint8 [batch, n_keys] with a landmark at the end of every block (one row, broadcast over the batch)."""
+    key = (device, n_keys, block_size)
+    row = _FLAGS.get(key)
+    if row is None:
+        if len(_FLAGS) > 64:
+            _FLAGS.clear()
+        row = (torch.arange(n_keys, device=device) % block_size == block_size - 1).to(torch.uint8).view(1, n_keys)
+        _FLAGS[key] = row
+    return row.expand(batch, n_keys)
 
 
 def landmark_sdpa(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=True, scale=None, *,

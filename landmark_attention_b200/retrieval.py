@@ -163,6 +163,40 @@ def selected_attend(q, k_cache, v_cache, kdesc, vdesc, idx, cos=None, sin=None, 
     return out
 
 
+def chunk_prepare(q, k_new, v_new, cos, sin, pos0, chunk_is_mem, block, t_pad, cache=None):
+    """One launch for what a layer does to a chunk's projections before its attention (lmk_chunk_prepare): rotate-half
+    rotary of q and k at positions pos0 .. pos0+T-1 (llama/llama_mem.py:127-149), copies padded with zero rows to t_pad
+    rows, the landmark flags of those rows, and -- with `cache`, a LandmarkKVCache -- the append of the un-rotated keys
+    and values (:424-425).  Returns (q_rot [B,H,T,D], q_pad, k_pad, v_pad [B,H,t_pad,D], flags uint8 [B,t_pad])."""
+    L.require_cuda(q, k_new, v_new, cos, sin)
+    B, H, T, D = q.shape
+    q, k_new, v_new = [t if t.stride(3) == 1 else t.contiguous() for t in (q, k_new, v_new)]
+    assert cos.dtype == q.dtype and cos.is_contiguous() and sin.is_contiguous() and cos.shape[1] == D
+    dev = q.device
+    q_rot = torch.empty((B, H, T, D), dtype=q.dtype, device=dev)
+    q_pad, k_pad, v_pad = [torch.empty((B, H, t_pad, D), dtype=q.dtype, device=dev) for _ in range(3)]
+    flags = torch.empty((B, t_pad), dtype=torch.uint8, device=dev)
+    cf = None
+    if chunk_is_mem is not None:
+        cf = chunk_is_mem.reshape(-1)[:T].to(torch.uint8).contiguous()
+    ck = cv = cst = None
+    cache_pos = 0
+    if cache is not None:
+        if cache.length + T > cache.k.shape[2]:
+            raise ValueError(f"cache capacity {cache.k.shape[2]} exceeded ({cache.length} + {T})")
+        assert cache.k.stride() == cache.v.stride() and cache.k.stride(3) == 1
+        ck, cv, cst, cache_pos = cache.k, cache.v, L.strides3(cache.k), cache.length
+    rc = L.lib().lmk_chunk_prepare(L.ptr(q), L.ptr(k_new), L.ptr(v_new), L.strides3(q), L.strides3(k_new),
+                                   L.strides3(v_new), L.ptr(cos), L.ptr(sin), cos.shape[0], int(pos0), L.ptr(cf),
+                                   int(block), L.ptr(q_rot), L.ptr(q_pad), L.ptr(k_pad), L.ptr(v_pad), L.ptr(flags),
+                                   L.ptr(ck), L.ptr(cv), cst, int(cache_pos), B, H, T, t_pad, D, L.dtype_code(q),
+                                   L.stream_ptr(dev))
+    L.check(rc, "lmk_chunk_prepare")
+    if cache is not None:
+        cache.length += T
+    return q_rot, q_pad, k_pad, v_pad, flags
+
+
 class LandmarkKVCache:
     """Preallocated un-rotated key/value cache [B,H,capacity,D] for chunked inference: `append` copies only the new
     chunk, so a layer never re-copies what it already holds (the reference re-concatenates the whole cache on every call,
@@ -223,14 +257,25 @@ def llama_retrieval_attention(q, k_new, v_new, past_k=None, past_v=None, mem_fre
     C = past_k.shape[2]
     block = mem_freq + 1
     dev = q.device
+    default_positions = position_ids is None
     if position_ids is None:
         position_ids = torch.arange(C, C + T, device=dev)
     if cos is None:
         cos, sin = rotary_tables_half(C + T + 1, D, q.dtype, dev)
     scale = 1.0 / math.sqrt(D)
-    qr = apply_rotary_half(q, cos, sin, position_ids)
-    kr = apply_rotary_half(k_new, cos, sin, position_ids)
     inc = C % block
+    t_pad = ((T + 127) // 128) * 128
+    if fused is None:
+        fused = (not materialize and not return_debug and aggregate is None and inc == 0 and cache_top_k >= 1
+                 and C >= block and q.dtype != torch.float32 and D == 128 and t_pad <= 32768)
+    one_launch = fused and default_positions and aggregate is None and q.dtype != torch.float32
+    if one_launch:
+        # rotary of q and k, padded tiles, landmark flags and the cache append in one kernel
+        qr, qp, kp, vp, im = chunk_prepare(q, k_new, v_new, cos, sin, C, chunk_is_mem, block, t_pad, cache)
+        kr = None
+    else:
+        qr = apply_rotary_half(q, cos, sin, position_ids)
+        kr = apply_rotary_half(k_new, cos, sin, position_ids)
     full = C - inc
     if inc > 0:
         assert T + inc <= block
@@ -245,7 +290,7 @@ def llama_retrieval_attention(q, k_new, v_new, past_k=None, past_v=None, mem_fre
 
     def new_cache():
         if cache is not None:
-            return cache.append(k_new, v_new)
+            return cache.views() if one_launch else cache.append(k_new, v_new)   # chunk_prepare appended already
         return torch.cat((past_k, k_new), dim=2), torch.cat((past_v, v_new), dim=2)
 
     if aggregate == "max_over_tokens":
@@ -267,22 +312,19 @@ def llama_retrieval_attention(q, k_new, v_new, past_k=None, past_v=None, mem_fre
 
     scores = landmark_scores(qr, past_k, kdesc, cos, sin, L.ROTARY_HALF, scale)
     sel = topk_sorted(scores, top_k)
-    if chunk_is_mem is None:
+    if chunk_is_mem is None and not one_launch:
         chunk_is_mem = (position_ids % block == block - 1).view(1, T)
 
-    from .masked import _fwd as masked_fwd, masked_attention_supported
-    t_pad = ((T + 127) // 128) * 128
-    if fused is None:
-        fused = (not materialize and not return_debug and inc == 0 and top_k >= 1 and q.dtype != torch.float32
-                 and D == 128 and t_pad <= 32768)
+    from .masked import _fwd as masked_fwd
     if fused:
         # local part: landmark attention of the chunk over itself on the tensor cores, rows padded to whole tiles
         # (padding keys lie after every real query, so causality hides them); then one kernel for the selected blocks
         # and the merge of the two parts
-        assert inc == 0 and not materialize
-        qp, kp, vp = _pad_rows(qr, t_pad), _pad_rows(kr, t_pad), _pad_rows(v_new, t_pad)
-        im = torch.zeros((B, t_pad), dtype=torch.uint8, device=dev)
-        im[:, :T] = chunk_is_mem.to(torch.uint8).expand(B, T)
+        assert inc == 0 and not materialize and top_k >= 1
+        if not one_launch:
+            qp, kp, vp = _pad_rows(qr, t_pad), _pad_rows(kr, t_pad), _pad_rows(v_new, t_pad)
+            im = torch.zeros((B, t_pad), dtype=torch.uint8, device=dev)
+            im[:, :T] = chunk_is_mem.to(torch.uint8).expand(B, T)
         o_loc, r_loc, _ = masked_fwd(qp, kp, vp, im, scale, 64)
         out = selected_attend(qr, past_k, past_v, kdesc, vdesc, sel, cos, sin, L.ROTARY_HALF, scale, o_loc, r_loc)
         return out, new_cache()

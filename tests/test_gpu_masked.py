@@ -157,3 +157,24 @@ def test_too_many_landmarks_is_reported_not_hidden():
     assert L.device_status() == 431
     with pytest.raises(NotImplementedError):
         P.landmark_attention_masked(q.to(DEV), k.to(DEV), v.to(DEV), im.to(DEV), max_groups=65)
+
+
+@pytest.mark.parametrize("B,H,Lq,Lk,blk", [(1, 2, 512, 512, 32), (2, 2, 256, 384, 16), (1, 2, 1024, 1024, 128),
+                                           (1, 1, 2048, 2048, 32)])
+def test_fused_entry_with_other_block_sizes_runs_on_these_kernels(B, H, Lq, Lk, blk):
+    # fused_landmark_attention(block_size != 64) routes 16-bit head-dim-128 problems to the arbitrary-landmark
+    # tensor-core kernels (regular flags); result against the oracle of the fused operator, with history keys
+    g = torch.Generator().manual_seed(Lk + blk)
+    q = (torch.randn(B, H, Lq, 128, generator=g) * 0.5).to(torch.bfloat16)
+    k, v = [(torch.randn(B, H, Lk, 128, generator=g) * 0.5).to(torch.bfloat16) for _ in range(2)]
+    do = torch.randn(B, H, Lq, 128, generator=g).to(torch.bfloat16)
+    eo, edq, edk, edv = O.landmark_attention_grads(q.float(), k.float(), v.float(), do.float(), blk)
+    qd, kd, vd = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    out = P.fused_landmark_attention(qd, kd, vd, None, block_size=blk)
+    assert "FusedLandmarkAttention" not in type(out.grad_fn).__name__      # not the block-64 / general entry
+    dq, dk, dv = torch.autograd.grad(out, [qd, kd, vd], do.to(DEV))
+    for got, exp in ((out, eo), (dq, edq), (dk, edk), (dv, edv)):
+        got = got.float().cpu()
+        assert torch.isfinite(got).all()
+        assert (got - exp).abs().max().item() < 3e-2 and rel_l2(got, exp) < 1e-2
+    assert L.device_status() == 0

@@ -406,3 +406,33 @@ def test_offloaded_cache_reads_only_selected_blocks_from_host():
     assert off.n_blocks == 14
     assert torch.equal(off.k_host[:, :, :off.length].to(DEV), past[0])
     assert torch.equal(off.lm_keys[:, :, :off.n_blocks], past[0][:, :, blk - 1::blk])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_chunk_prepare_equals_the_tensor_formulation(dtype):
+    # rotary with the same three roundings, zero padding rows, flags, and the append of the un-rotated rows: bit-exact
+    from landmark_attention_b200.retrieval import apply_rotary_half, chunk_prepare
+    torch.manual_seed(21)
+    B, H, T, D, blk, C = 2, 3, 77, 128, 32, 96
+    q, k, v = [torch.randn(B, H, T, D).to(dtype).to(DEV) for _ in range(3)]
+    k = k.transpose(1, 2).contiguous().transpose(1, 2)          # a strided input
+    cos, sin = P.rotary_tables_half(C + T + 1, D, dtype, DEV)
+    cache = P.LandmarkKVCache(B, H, C + T + 5, D, dtype, DEV)
+    cache.k.zero_(); cache.v.zero_()
+    cache.length = C
+    q_rot, q_pad, k_pad, v_pad, flags = chunk_prepare(q, k, v, cos, sin, C, None, blk, 128, cache)
+    pos = torch.arange(C, C + T, device=DEV)
+    eq, ek = apply_rotary_half(q, cos, sin, pos), apply_rotary_half(k, cos, sin, pos)
+    assert torch.equal(q_rot, eq)
+    for got, exp in ((q_pad, eq), (k_pad, ek), (v_pad, v)):
+        assert torch.equal(got[:, :, :T], exp) and not got[:, :, T:].any()
+    ef = torch.zeros(B, 128, dtype=torch.uint8, device=DEV)
+    ef[:, :T] = (pos % blk == blk - 1).to(torch.uint8)
+    assert torch.equal(flags, ef)
+    assert cache.length == C + T
+    assert torch.equal(cache.k[:, :, C:C + T], k) and torch.equal(cache.v[:, :, C:C + T], v)
+    assert not cache.k[:, :, :C].any() and not cache.k[:, :, C + T:].any()
+    # explicit flags, no cache
+    given = torch.rand(1, T, device=DEV) < 0.2
+    _, _, _, _, flags2 = chunk_prepare(q, k, v, cos, sin, C, given, blk, 128)
+    assert torch.equal(flags2[:, :T], given.to(torch.uint8).expand(B, T)) and not flags2[:, T:].any()
