@@ -122,25 +122,49 @@ def prepare_landmark_masks(is_mem_row, attn_mask):
     return mask, is_mem, last
 
 
-def lm_landmark_attention(q, k, v, is_mem_row, sm_scale=None, max_groups=None):
-    """Attention of lm_benchmark's CausalSelfAttention.forward without cache (landmark.py:196-236): q, k rotated,
-    landmarks at arbitrary per-row positions is_mem_row [B, T].
+def lm_landmark_attention(q, k, v, is_mem_row, sm_scale=None, max_groups=None, att_prefix=None, cache_values=None):
+    """Attention of lm_benchmark's CausalSelfAttention.forward (landmark.py:196-243): q, k rotated, landmarks at
+    arbitrary per-row positions is_mem_row [B, T].
 
-    bf16/fp16 with head dim 128 and T a multiple of 128 runs as ONE fused operator on the tensor cores
-    (masked.landmark_attention_masked: no score, mask or probability tensor exists).  Other shapes and fp32 use the
-    unfused route: library matmuls around this package's grouped-softmax kernel, masks as broadcast views."""
+    Without a cache, bf16/fp16 with head dim 128 and T a multiple of 128 runs as ONE fused operator on the tensor
+    cores (masked.landmark_attention_masked: no score, mask or probability tensor exists).  Other shapes and fp32 use
+    the unfused route: library matmuls around this package's grouped-softmax kernel, masks as broadcast views.
+
+    With a cache (the evaluation branch, :182-209 and :236-243): `att_prefix` [B,H,T,P] and `cache_values`
+    {'v': [B,H,T,P,D] or [B,H,P,D], 'is_mem': [B,P] (optional)} are what `MemLMCacheStorage.retrieve_for_query`
+    returns; the prefix columns are visible to every query and go through the same grouped softmax in front of the
+    chunk's own keys.  This branch takes the unfused route."""
     from .masked import DEFAULT_MAX_GROUPS, landmark_attention_masked, masked_attention_supported
     B, H, T, D = q.shape
     if sm_scale is None:
         sm_scale = 1.0 / (D ** 0.5)
+    n_pre = 0 if att_prefix is None else att_prefix.shape[-1]
     fused_groups = DEFAULT_MAX_GROUPS if max_groups is None else int(max_groups)
-    if masked_attention_supported(q, k, fused_groups):
+    if n_pre == 0 and masked_attention_supported(q, k, fused_groups):
         return landmark_attention_masked(q, k, v, is_mem_row, sm_scale, fused_groups)
     att = torch.matmul(q, k.transpose(-2, -1)) * sm_scale
     hidden = torch.ones(T, T, dtype=torch.bool, device=q.device).triu(1)
+    if n_pre:
+        att = torch.cat((att_prefix.to(att.dtype), att), dim=-1)
+        pre_mem = cache_values.get('is_mem')
+        if pre_mem is None:
+            pre_mem = torch.zeros((B, n_pre), dtype=torch.bool, device=q.device)
+        is_mem_row = torch.cat((pre_mem.to(torch.bool), is_mem_row.to(torch.bool)), dim=-1)
+        hidden = torch.cat((torch.zeros((T, n_pre), dtype=torch.bool, device=q.device), hidden), dim=-1)
     mask, is_mem, last = prepare_landmark_masks(is_mem_row, hidden)
     att = att.masked_fill(mask, float("-inf"))
     if max_groups is None:
-        max_groups = min(2048, T + 1)
+        max_groups = min(2048, T + n_pre + 1)
     probs, _ = _GroupedSoftmax.apply(att, is_mem, last, mask, True, max_groups, 0)
-    return torch.matmul(probs.to(v.dtype), v)
+    probs = probs.to(v.dtype)
+    y = torch.matmul(probs[..., n_pre:], v)
+    if n_pre:
+        cache_v = cache_values['v']
+        pp = probs[..., :n_pre]
+        if cache_v.dim() == v.dim():
+            y = y + torch.matmul(pp, cache_v)
+        elif cache_v.dim() == v.dim() + 1:
+            y = y + torch.matmul(pp.unsqueeze(3), cache_v).squeeze(3)
+        else:
+            raise NotImplementedError("cache values must be [B,H,P,D] or [B,H,T,P,D]")
+    return y

@@ -461,15 +461,31 @@ def strip_landmarks(x: torch.Tensor, mem_freq: int, carry_before: int):
 # lm_benchmark attention call site (training path, arbitrary landmark positions)
 # ----------------------------------------------------------------------------
 
-def lm_attention(q, k, v, is_mem_row, sm_scale: Optional[float] = None):
-    """Attention of lm_benchmark's CausalSelfAttention without cache: q,k already rotated.
-    Reference: lm_benchmark/models/landmark.py:196-236 (softmax_func = landmark_grouped_softmax)."""
+def lm_attention(q, k, v, is_mem_row, sm_scale: Optional[float] = None, att_prefix=None, v_prefix=None,
+                 is_mem_prefix=None):
+    """Attention of lm_benchmark's CausalSelfAttention: q,k already rotated.
+    Reference: lm_benchmark/models/landmark.py:196-236 (softmax_func = landmark_grouped_softmax).
+    With a cache (landmark.py:182-209, 236-243): att_prefix [B,H,T,P] are the scaled scores against the retrieved
+    keys, v_prefix [B,H,T,P,D] (or [B,H,P,D]) their values and is_mem_prefix [B,P] their landmark flags; the prefix
+    columns are visible to every query and join the same grouped softmax in front of the chunk's own keys."""
     B, H, T, D = q.shape
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
     att = torch.matmul(q, k.transpose(-2, -1)) * sm_scale
-    causal_hidden = torch.triu(torch.ones(T, T, dtype=torch.bool), diagonal=1)
-    mask, is_mem, last = prepare_landmark_masks(is_mem_row, causal_hidden)
+    hidden = torch.triu(torch.ones(T, T, dtype=torch.bool), diagonal=1)
+    n_pre = 0
+    if att_prefix is not None:
+        n_pre = att_prefix.shape[-1]
+        att = torch.cat((att_prefix, att), dim=-1)                                     # :201-203
+        pre_mem = is_mem_prefix if is_mem_prefix is not None else torch.zeros(B, n_pre, dtype=torch.bool)
+        is_mem_row = torch.cat((pre_mem, is_mem_row), dim=-1)                          # :204-207
+        hidden = torch.cat((torch.zeros(T, n_pre, dtype=torch.bool), hidden), dim=-1)  # :208
+    mask, is_mem, last = prepare_landmark_masks(is_mem_row, hidden)
     att = att.masked_fill(mask, NEG_INF)
     p = grouped_softmax(att, is_mem, last, attn_mask=mask, guards=True)
-    return torch.matmul(p.to(v.dtype), v)
+    y = torch.matmul(p[..., n_pre:].to(v.dtype), v)
+    if n_pre:
+        pp = p[..., :n_pre].to(v.dtype)
+        y = y + (torch.matmul(pp, v_prefix) if v_prefix.dim() == 4                    # :238-243
+                 else torch.matmul(pp.unsqueeze(3), v_prefix).squeeze(3))
+    return y

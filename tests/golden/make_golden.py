@@ -17,6 +17,8 @@ What is recorded, and from which reference code:
                    of landmark.py:210-224, probs + group_prob + grad
   lm_attn.pt       lm_benchmark CausalSelfAttention.forward (landmark.py:171-255), no cache
   memcache_*.pt    MemLMCacheStorage.store_in_cache / retrieve_for_query (mem_cache.py:41-158)
+  lm_attn_cache.pt lm_benchmark CausalSelfAttention.forward with a MemLMCacheStorage attached (landmark.py:182-253):
+                   four chunks, the attention output of each given the blocks retrieved from the earlier ones
                    for the three selection methods; MemLMCache.forward / get_final_logits
   llama_retr_*.pt  LlamaModel.forward -> LlamaAttention.forward cache branch (llama_mem.py:318-430)
 """
@@ -209,6 +211,35 @@ def gen_lm_attn(landmark, rotary):
          gy=gy, dq=qr.grad, dk=kr.grad, dv=v.grad)
 
 
+def gen_lm_attn_cache(landmark, mem_cache, rotary):
+    g = torch.Generator().manual_seed(43)
+    cfg = lm_config()
+    B, H, D, blk = cfg.batch_size, cfg.n_head, cfg.n_embd // cfg.n_head, cfg.mem_cache_freq + 1
+    attn = landmark.CausalSelfAttention(cfg, None)
+    attn.cache_storage = mem_cache.MemLMCacheStorage(cfg, attn)
+    attn.eval()
+    with torch.no_grad():
+        attn.c_attn.weight.copy_(torch.randn(3 * cfg.n_embd, cfg.n_embd, generator=g) * 0.3)
+        attn.c_proj.weight.copy_(torch.eye(cfg.n_embd))
+    enc = rotary.RotaryPositionalEncoder(cfg)
+    _, closure = enc(None)
+    records, pos = [], 0
+    with torch.no_grad():
+        for T in (19, 16, 13, 24):
+            x = torch.randn(B, T, cfg.n_embd, generator=g)
+            is_mem = ((torch.arange(pos, pos + T) % blk) == blk - 1).view(1, T).expand(B, T).clone()
+            start_index = min((pos - pos % blk) // blk, cfg.cache_topk + 1) * blk + pos % blk
+            q, k, v = [t.view(B, T, H, D).transpose(1, 2) for t in attn.c_attn(x).split(cfg.n_embd, dim=2)]
+            qr = closure.adapt_queries(q, start_index=start_index)
+            kr = closure.adapt_keys(k, start_index=start_index)
+            y, _ = attn(x, is_mem, closure, mem_cache.MemLMCacheContext(), start_index)
+            records.append(dict(q_rot=qr.clone(), k_rot=kr.clone(), k=k.clone(), v=v.clone(), is_mem=is_mem,
+                                start_index=start_index, y=y.clone()))
+            pos += T
+    save("lm_attn_cache.pt", records=records, capacity=cfg.mem_cache_size, blk=blk, top_k=cfg.cache_topk,
+         method=cfg.cache_selection_method, max_groups=cfg.max_groups_for_softmax)
+
+
 def gen_memcache(mem_cache, rotary):
     for method in ("per_token_and_head", "max_over_heads", "max_over_tokens"):
         g = torch.Generator().manual_seed(51)
@@ -300,6 +331,7 @@ def main():
     steps = dict(fused=lambda: gen_fused(llama_mem), triton=lambda: gen_triton(fla),
                  gsm_llama=lambda: gen_gsm_llama(llama_mem), gsm_lm=lambda: gen_gsm_lm(landmark),
                  lm_attn=lambda: gen_lm_attn(landmark, rotary), memcache=lambda: gen_memcache(mem_cache, rotary),
+                 lm_attn_cache=lambda: gen_lm_attn_cache(landmark, mem_cache, rotary),
                  llama_retr=lambda: gen_llama_retrieval(llama_mem, LlamaLandmarkConfig))
     for name, fn in steps.items():
         if a.only and name not in a.only.split(","):

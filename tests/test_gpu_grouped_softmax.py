@@ -105,3 +105,25 @@ def test_random_masks_any_length(Lk, density, dtype, guards):
     again = P.landmark_grouped_softmax_lm(xd, -1, is_mem.to(DEV), hidden.to(DEV), last.to(DEV), False, n_lm)[0] \
         if guards else P.landmark_grouped_softmax(xd, -1, is_mem.to(DEV), last.to(DEV), max_groups=n_lm)
     assert torch.equal(again, got)                           # sums are taken in a fixed order
+
+
+def test_lm_call_site_with_cache_against_golden(golden):
+    # CausalSelfAttention.forward with a block cache attached (landmark.py:182-253): four chunks; the cache kernels
+    # supply the prefix scores / values, lm_landmark_attention joins prefix and chunk in one grouped softmax
+    g = golden("lm_attn_cache.pt")
+    r0 = g["records"][0]
+    B, H, _, D = r0["q_rot"].shape
+    cfg = type("C", (), dict(batch_size=B, mem_cache_size=g["capacity"], mem_cache_freq=g["blk"] - 1, n_head=H,
+                             n_embd=H * D, cache_topk=g["top_k"], cache_selection_method=g["method"]))()
+    store = P.MemLMCacheStorage(cfg, None, dtype=torch.float32, device=DEV)
+    widest = 0
+    for r in g["records"]:
+        q, k_rot, k, v, im = [r[n].to(DEV) for n in ("q_rot", "k_rot", "k", "v", "is_mem")]
+        T = q.shape[2]
+        att_prefix, cv = store.retrieve_for_query(q, None, None, r["start_index"])
+        widest = max(widest, att_prefix.shape[-1])
+        y = P.lm_landmark_attention(q, k_rot, v, im, att_prefix=att_prefix, cache_values=cv)
+        y = y.transpose(1, 2).reshape(B, T, H * D)
+        assert (y.cpu() - r["y"]).abs().max().item() < 2e-5
+        store.store_in_cache(k, {"v": v, "is_mem": im})
+    assert widest >= g["top_k"] * g["blk"]

@@ -89,6 +89,23 @@ def test_block_cache(golden, method):
         cache.store(r["k"], r["v"], r["is_mem"])
 
 
+def test_lm_call_site_with_cache(golden):
+    # CausalSelfAttention.forward with a block cache attached: the oracle's cache supplies the prefix, the oracle's
+    # attention joins prefix and chunk in one grouped softmax; four chunks against the reference's outputs
+    g = golden("lm_attn_cache.pt")
+    cache = O.BlockCacheOracle(g["capacity"], g["blk"], g["top_k"], g["method"])
+    saw_blocks = False
+    for r in g["records"]:
+        B, H, T, D = r["q_rot"].shape
+        att, vp, im, _ = cache.retrieve(r["q_rot"], r["start_index"])
+        saw_blocks = saw_blocks or att.shape[-1] >= g["blk"]
+        y = O.lm_attention(r["q_rot"], r["k_rot"], r["v"], r["is_mem"], att_prefix=att, v_prefix=vp, is_mem_prefix=im)
+        y = y.transpose(1, 2).reshape(B, T, H * D)
+        assert (y - r["y"]).abs().max().item() < 1e-5
+        cache.store(r["k"], r["v"], r["is_mem"])
+    assert saw_blocks
+
+
 def test_landmark_id_bookkeeping(golden):
     g = golden("memcache_ids.pt")
     carry, total = 0, 0
