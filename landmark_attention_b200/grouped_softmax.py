@@ -93,14 +93,27 @@ def landmark_grouped_softmax(x, dim, is_mem, last_section_mask, max_groups=None)
 
 def landmark_grouped_softmax_lm(x, dim, is_mem, attn_mask, last_section_mask, return_group_prob, max_mem_cnt,
                                 p_group_dropout=None):
-    """lm_benchmark flavour (lm_benchmark/models/landmark.py:88-119).  Group dropout is a training-time
-    regulariser outside the measured path and is not implemented."""
+    """lm_benchmark flavour (lm_benchmark/models/landmark.py:88-119).
+
+    Group dropout (:110-114, a training-time regulariser): every landmark's group weight is dropped with probability p
+    or scaled by 1/(1-p); last-section keys are untouched.  The kernel computes the probabilities without dropout and
+    the keep factors are applied per (row, group) afterwards -- the same function of x as the reference's formulation,
+    with this package's own random draw (one `torch.rand` of shape [B,H,Lq,max_mem_cnt-1] from the default generator)."""
     _check_dim(x, dim)
-    if p_group_dropout is not None:
-        raise NotImplementedError("p_group_dropout is not supported")
     max_groups = min(2048, max(int(max_mem_cnt), 2))
+    drop = p_group_dropout is not None and p_group_dropout > 0
     probs, gp = _GroupedSoftmax.apply(x, is_mem, last_section_mask, attn_mask, True, max_groups,
-                                      int(max_mem_cnt) if return_group_prob else 0)
+                                      int(max_mem_cnt) if (return_group_prob or drop) else 0)
+    if drop:
+        p = float(p_group_dropout)
+        B, H, Lq, Lk = probs.shape
+        keep = (torch.rand((B, H, Lq, int(max_mem_cnt) - 1), device=probs.device) >= p).to(probs.dtype) / (1.0 - p)
+        group = torch.cumsum(is_mem.expand(B, H, Lq, Lk).to(torch.int64), dim=-1).clamp_(max=int(max_mem_cnt) - 2)
+        factor = torch.gather(keep, -1, group)
+        bucket = is_mem | last_section_mask | attn_mask
+        probs = torch.where(bucket, probs, probs * factor)
+        if return_group_prob:
+            gp = torch.cat((gp[..., :-1] * keep, gp[..., -1:] / (1.0 - p)), dim=-1)
     return probs, (gp if return_group_prob else None)
 
 

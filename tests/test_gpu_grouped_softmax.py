@@ -127,3 +127,27 @@ def test_lm_call_site_with_cache_against_golden(golden):
         assert (y.cpu() - r["y"]).abs().max().item() < 2e-5
         store.store_in_cache(k, {"v": v, "is_mem": im})
     assert widest >= g["top_k"] * g["blk"]
+
+
+def test_group_dropout_scales_whole_groups():
+    # landmark.py:110-114: each landmark's group weight is dropped or scaled by 1/(1-p); last-section keys untouched.
+    # Same draw as the implementation (one torch.rand from the default generator), applied to the oracle's result.
+    B, H, T, blk, p, mmc = 2, 2, 96, 8, 0.4, 16
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(B, H, T, T, generator=g)
+    hidden = torch.ones(T, T, dtype=torch.bool).triu(1)
+    mask, is_mem, last = O.prepare_landmark_masks(O.regular_is_mem(T, blk).view(1, T).expand(B, T), hidden)
+    x = x.masked_fill(mask, float("-inf"))
+    base = O.grouped_softmax(x, is_mem, last, attn_mask=mask, guards=True)
+    xd = x.to(DEV).requires_grad_(True)
+    torch.manual_seed(77)
+    got, gp = P.landmark_grouped_softmax_lm(xd, -1, is_mem.to(DEV), mask.to(DEV), last.to(DEV), True, mmc, p_group_dropout=p)
+    torch.manual_seed(77)
+    keep = (torch.rand((B, H, T, mmc - 1), device=DEV) >= p).float().cpu() / (1 - p)
+    group = torch.cumsum(is_mem.expand(B, H, T, T).long(), -1).clamp(max=mmc - 2)
+    exp = torch.where(is_mem | last | mask, base, base * torch.gather(keep, -1, group))
+    assert (got.detach().cpu() - exp).abs().max().item() < 1e-6
+    assert 0.2 < (keep == 0).float().mean().item() < 0.6                       # groups were dropped indeed
+    assert (gp[..., -1].cpu() - (base * last).sum(-1) / (1 - p)).abs().max().item() < 1e-5
+    (gx,) = torch.autograd.grad(got.sum(), [xd])                                 # differentiable through the factors
+    assert torch.isfinite(gx).all()
