@@ -178,3 +178,27 @@ def test_fused_entry_with_other_block_sizes_runs_on_these_kernels(B, H, Lq, Lk, 
         assert torch.isfinite(got).all()
         assert (got - exp).abs().max().item() < 3e-2 and rel_l2(got, exp) < 1e-2
     assert L.device_status() == 0
+
+
+@pytest.mark.parametrize("D,blk,Lq,Lk", [(64, 64, 256, 384), (64, 32, 256, 256), (96, 64, 128, 128), (32, 16, 128, 192)])
+def test_fused_entry_with_smaller_head_dims_runs_on_tensor_cores(D, blk, Lq, Lk):
+    # 16-bit head dims below 128 are zero-padded to 128 and run on the tensor-core kernels (block 64: lmk_attn_fwd/bwd,
+    # other blocks: the arbitrary-landmark kernels); the default scale stays 1/sqrt(D) of the real head dim
+    g = torch.Generator().manual_seed(D + blk)
+    B, H = 2, 2
+    q = (torch.randn(B, H, Lq, D, generator=g) * 0.5).to(torch.bfloat16)
+    k, v = [(torch.randn(B, H, Lk, D, generator=g) * 0.5).to(torch.bfloat16) for _ in range(2)]
+    do = torch.randn(B, H, Lq, D, generator=g).to(torch.bfloat16)
+    eo, edq, edk, edv = O.landmark_attention_grads(q.float(), k.float(), v.float(), do.float(), blk)
+    qd, kd, vd = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    out = P.fused_landmark_attention(qd, kd, vd, None, block_size=blk)
+    assert out.shape == (B, H, Lq, D)
+    assert "FusedLandmarkAttention" not in type(out.grad_fn).__name__          # a slice of the padded problem's output
+    dq, dk, dv = torch.autograd.grad(out, [qd, kd, vd], do.to(DEV))
+    general = P.fused_landmark_attention(qd, kd, vd, None, block_size=blk, path=P.PATH_GENERAL)
+    assert (out.float() - general.float()).abs().max().item() < 2e-2
+    for got, exp in ((out, eo), (dq, edq), (dk, edk), (dv, edv)):
+        got = got.float().cpu()
+        assert got.shape == exp.shape and torch.isfinite(got).all()
+        assert (got - exp).abs().max().item() < 3e-2 and rel_l2(got, exp) < 1e-2
+    assert L.device_status() == 0
