@@ -275,7 +275,7 @@ def bench_strong(P, world, rank, dev, flush, steps, peaks):
     g_fwd, g_bwd, _, _ = _capture_step(P, q, k, v, do, w["block"])
     _, _, tot, _ = _time_graph_steps(g_fwd, g_bwd, flush, steps, world)
     ms = max_over_ranks(statistics.fmean(tot), world, dev)
-    chunks = 4 if Hs % 4 == 0 else (2 if Hs % 2 == 0 else 1)
+    chunks = 2 if Hs % 2 == 0 else 1
     pipe = P.HostAttentionPipeline(1, Hs, w["L"], w["L"], w["D"], torch.bfloat16, w["block"], chunks=chunks, device=dev)
     outs = [torch.empty(1, Hs, w["L"], w["D"], dtype=torch.bfloat16).pin_memory() for _ in range(4)]
     for _ in range(2):
@@ -284,7 +284,8 @@ def bench_strong(P, world, rank, dev, flush, steps, peaks):
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(steps):
-        pipe.run(*host, *outs)
+        last = pipe.run(*host, *outs, wait=False)
+    torch.cuda.current_stream().wait_event(last)
     b.record()
     torch.cuda.synchronize(); barrier(world)
     e2e_ms = max_over_ranks(a.elapsed_time(b) / steps, world, dev)
@@ -532,28 +533,60 @@ def run_ours(args, world, rank, local):
 
     # end to end through the public API with HOST buffers: pinned inputs in, outputs and gradients back to pinned host
     # memory, all inside the timed region.  HostAttentionPipeline cuts the heads into chunks and overlaps the copies
-    # in both directions with the kernels on three streams.
+    # in both directions with the kernels on three streams; consecutive steps overlap as well (run(wait=False): the
+    # inputs of step i+1 go in while the results of step i come out), which is how a loop over problems calls it.
     outs_host = [torch.empty(B, H, Lq, D, dtype=torch.bfloat16).pin_memory() for _ in range(4)]
-    pipe = P.HostAttentionPipeline(B, H, Lq, Lq, D, torch.bfloat16, blk, chunks=4, device=dev)
+    pipe = P.HostAttentionPipeline(B, H, Lq, Lq, D, torch.bfloat16, blk, chunks=2, device=dev)
 
-    def e2e_step():
-        pipe.run(host[0], host[1], host[2], host[3], *outs_host)
+    def e2e_loop(n, wait):
+        last = None
+        for _ in range(n):
+            last = pipe.run(host[0], host[1], host[2], host[3], *outs_host, wait=wait)
+        torch.cuda.current_stream().wait_event(last)       # the last copy of the last step
 
-    for _ in range(2):
-        e2e_step()
+    e2e_loop(2, True)
     torch.cuda.synchronize()
     ref_out, ref_grads = step()
     for got, exp in zip(outs_host, (ref_out, *ref_grads)):
         if not torch.equal(got, exp.detach().cpu()):
             raise SystemExit("host pipeline and device-resident call disagree")
-    barrier(world); torch.cuda.synchronize()
-    a, b_ = ev(), ev()
-    a.record()
-    for _ in range(args.steps):
-        e2e_step()
-    b_.record()
-    torch.cuda.synchronize(); barrier(world)
-    e2e_ms = max_over_ranks(a.elapsed_time(b_) / args.steps, world, dev)
+    e2e_times = {}
+    for name, wait in (("one_step_at_a_time", True), ("pipelined", False)):
+        e2e_loop(2, wait)
+        barrier(world); torch.cuda.synchronize()
+        a, b_ = ev(), ev()
+        a.record()
+        e2e_loop(args.steps, wait)
+        b_.record()
+        torch.cuda.synchronize(); barrier(world)
+        e2e_times[name] = max_over_ranks(a.elapsed_time(b_) / args.steps, world, dev)
+    for got, exp in zip(outs_host, (ref_out, *ref_grads)):
+        if not torch.equal(got, exp.detach().cpu()):
+            raise SystemExit("pipelined host steps and device-resident call disagree")
+    e2e_ms = e2e_times["pipelined"]
+    # what the host link gives with both directions busy (two plain copies of 64 MiB on two streams, pinned memory):
+    # the floor of an end-to-end step is its bytes in one direction over this rate
+    n_link = 64 << 20
+    h_in, h_out = [torch.empty(n_link, dtype=torch.uint8).pin_memory() for _ in range(2)]
+    d_in, d_out = [torch.empty(n_link, dtype=torch.uint8, device=dev) for _ in range(2)]
+    s_a, s_b = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    link_ms = None
+    for timed in (False, True):
+        torch.cuda.synchronize()
+        a, b_ = ev(), ev()
+        a.record()
+        s_a.wait_stream(torch.cuda.current_stream()); s_b.wait_stream(torch.cuda.current_stream())
+        for _ in range(5):
+            with torch.cuda.stream(s_a):
+                d_in.copy_(h_in, non_blocking=True)
+            with torch.cuda.stream(s_b):
+                h_out.copy_(d_out, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(s_a); torch.cuda.current_stream().wait_stream(s_b)
+        b_.record()
+        torch.cuda.synchronize()
+        link_ms = a.elapsed_time(b_) / 5
+    link_gbs = n_link / (link_ms * 1e-3) / 1e9
+    del h_in, h_out, d_in, d_out
     clocks = sampler.stop() if rank == 0 else None
     tensor_bytes = B * H * Lq * D * 2
 
@@ -608,7 +641,12 @@ def run_ours(args, world, rank, local):
                   "what": "public API on device-resident tensors, no CUDA graph, L2 flushed before each step"},
         "sustained": sustained,
         "e2e": {"value": world * flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": 4 * tensor_bytes, "d2h_bytes_per_step": 4 * tensor_bytes},
+                "h2d_bytes_per_step": 4 * tensor_bytes, "d2h_bytes_per_step": 4 * tensor_bytes,
+                "how": "HostAttentionPipeline.run(wait=False) per step: pinned q, k, v, dO in, o, dq, dk, dv out, two "
+                       "head chunks, consecutive steps overlapped (copies of both directions and the kernels)",
+                "ms_per_step_one_step_at_a_time": e2e_times["one_step_at_a_time"],
+                "host_link_gbs_per_direction_both_busy": link_gbs,
+                "host_link_floor_ms": 4 * tensor_bytes / (link_gbs * 1e9) * 1e3},
         "gpu_launches": args.steps * 3,      # forward, dQ (+ delta), dK/dV
         "clocks": clocks, "wall_s": wall,
     }

@@ -24,7 +24,7 @@ class HostAttentionPipeline:
         self.scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(D)
         self.dev = torch.device(device)
         self.dtype = dtype
-        n_buf = min(chunks, 3)
+        n_buf = 4                                  # device buffer sets, used in rotation across chunks and steps
         mk = lambda L_: torch.empty((B, self.hc, L_, D), dtype=dtype, device=self.dev)
         self.bufs = [dict(q=mk(Lq), k=mk(Lk), v=mk(Lk), do=mk(Lq), o=mk(Lq), dq=mk(Lq), dk=mk(Lk), dv=mk(Lk),
                           l=torch.empty((B * self.hc, Lq), dtype=torch.float32, device=self.dev),
@@ -36,14 +36,20 @@ class HostAttentionPipeline:
         self.code = code
         self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(3))
 
-    def run(self, q, k, v, do, o, dq, dk, dv, use_graph=False):
+    def run(self, q, k, v, do, o, dq, dk, dv, use_graph=False, wait=True):
         """All eight arguments are pinned host tensors [B, H, L, D]; returns after enqueueing (call
         torch.cuda.synchronize() before reading the outputs).
+
+        wait=True makes the current stream wait for the step's last device-to-host copy, so that work enqueued on it
+        afterwards sees the outputs.  wait=False leaves the step on the pipeline's own streams and returns the event of
+        its last copy: consecutive steps then overlap (the host-to-device copies of step i+1 run while step i's results
+        are still leaving the device; the device buffers are handed over through events), which is how a loop over
+        many problems should call it; wait on the returned event, or synchronise the device, before reading.
 
         With use_graph=True the step is captured into a CUDA graph after one eager run (keyed by the host buffers'
         addresses) and replayed; on PCIe-bound shapes this measures the same as the eager path, which is the default."""
         if not use_graph:
-            return self._enqueue(q, k, v, do, o, dq, dk, dv)
+            return self._enqueue(q, k, v, do, o, dq, dk, dv, wait)
         key = tuple(t.data_ptr() for t in (q, k, v, do, o, dq, dk, dv))
         if getattr(self, "_graph_key", None) != key:
             self._enqueue(q, k, v, do, o, dq, dk, dv)          # eager once: validates arguments, warms everything up
@@ -60,21 +66,27 @@ class HostAttentionPipeline:
         self._graph.replay()
         return None
 
-    def _enqueue(self, q, k, v, do, o, dq, dk, dv):
+    def _enqueue(self, q, k, v, do, o, dq, dk, dv, wait=True):
         lib = L.lib()
         cur = torch.cuda.current_stream(self.dev)
         for s in (self.s_in, self.s_run, self.s_out):
             s.wait_stream(cur)
         nb = len(self.bufs)
+        capturing = torch.cuda.is_current_stream_capturing()
+        if capturing or not hasattr(self, "_free"):
+            free, first = [None] * nb, 0           # per device buffer set: its last results have left the device
+        else:
+            free, first = self._free, self._next
         copied = [None] * self.chunks
         done = [None] * self.chunks
         drained = [None] * self.chunks
         for c in range(self.chunks):
-            buf, ws = self.bufs[c % nb], self.ws[c % nb]
+            bi = (first + c) % nb
+            buf, ws = self.bufs[bi], self.ws[bi]
             hs = slice(c * self.hc, (c + 1) * self.hc)
             with torch.cuda.stream(self.s_in):
-                if c >= nb:                        # the buffer's previous results must have left the device
-                    self.s_in.wait_event(drained[c - nb])
+                if free[bi] is not None:           # the buffer's previous results must have left the device
+                    self.s_in.wait_event(free[bi])
                 for name, src in (("q", q), ("k", k), ("v", v), ("do", do)):
                     buf[name].copy_(src[:, hs], non_blocking=True)
                 copied[c] = torch.cuda.Event()
@@ -100,5 +112,9 @@ class HostAttentionPipeline:
                     dst[:, hs].copy_(buf[name], non_blocking=True)
                 drained[c] = torch.cuda.Event()
                 drained[c].record(self.s_out)
-        cur.wait_stream(self.s_out)
+                free[bi] = drained[c]
+        if not capturing:
+            self._free, self._next = free, (first + self.chunks) % nb
+        if wait or capturing:
+            cur.wait_stream(self.s_out)
         return drained[-1]

@@ -23,3 +23,26 @@ def test_host_pipeline_matches_device_call(chunks):
     grads = torch.autograd.grad(o, [q, k, v], host[3].cuda())
     for got, exp in zip(outs, (o, *grads)):
         assert torch.equal(got, exp.detach().cpu())
+
+
+@pytest.mark.parametrize("chunks", [1, 2, 4])
+def test_overlapped_steps_keep_their_problems_apart(chunks):
+    # run(wait=False): consecutive steps share the rotating device buffers through events; five different problems in a
+    # row, each with its own pinned outputs, must all come out as the device-resident call computes them
+    g = torch.Generator().manual_seed(22)
+    B, H, L, D, n = 1, 8, 256, 128, 5
+    pipe = P.HostAttentionPipeline(B, H, L, L, D, torch.bfloat16, 64, chunks=chunks)
+    problems, results = [], []
+    for _ in range(n):
+        problems.append([(torch.randn(B, H, L, D, generator=g) * 0.5).to(torch.bfloat16).pin_memory() for _ in range(4)])
+        results.append([torch.zeros(B, H, L, D, dtype=torch.bfloat16).pin_memory() for _ in range(4)])
+    last = None
+    for host, outs in zip(problems, results):
+        last = pipe.run(*host, *outs, wait=False)
+    last.synchronize()                                   # the copies leave in order: the last one covers them all
+    for host, outs in zip(problems, results):
+        q, k, v = [t.cuda().requires_grad_(True) for t in host[:3]]
+        o = P.fused_landmark_attention(q, k, v, None)
+        grads = torch.autograd.grad(o, [q, k, v], host[3].cuda())
+        for got, exp in zip(outs, (o, *grads)):
+            assert torch.equal(got, exp.detach().cpu())
