@@ -370,11 +370,24 @@ def bench_grouped_softmax(P, L, dev, peaks):
         t_f = time_it(fwd)
         probs = fwd()
         t_b = time_it(lambda: torch.autograd.grad(probs, x, grad, retain_graph=True))
+        # the same softmax from the row flags alone (no [T,T] masks; rows read up to their last visible key)
+        causal = lambda: P.landmark_grouped_softmax_causal(x, is_mem_row, mg)
+        t_cf = time_it(causal)
+        probs_c = causal()
+        if (probs_c - probs).abs().max().item() > 1e-6:
+            raise SystemExit("grouped softmax: mask-free and mask-based forms disagree")
+        t_cb = time_it(lambda: torch.autograd.grad(probs_c, x, grad, retain_graph=True))
         nbytes = x.numel() * 4
         res[name] = {"fwd_ms": t_f, "bwd_ms": t_b, "fwd_gbs": 2 * nbytes / (t_f * 1e-3) / 1e9,
                      "bwd_gbs": 3 * nbytes / (t_b * 1e-3) / 1e9,
                      "fwd_frac": 2 * nbytes / (t_f * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                     "bwd_frac": 3 * nbytes / (t_b * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+                     "bwd_frac": 3 * nbytes / (t_b * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                     "mask_free": {"fwd_ms": t_cf, "bwd_ms": t_cb,
+                                   "fwd_frac": 2 * nbytes / (t_cf * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                   "bwd_frac": 3 * nbytes / (t_cb * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                   "bytes": "same convention (all of x read, all of the output written); the kernel "
+                                            "reads only the visible part of each row"}}
+        del probs_c
         del x, grad, probs
         torch.cuda.empty_cache()
     return {"bound": "hbm", "peak": peaks["hbm_gbs"], "unit": "GB/s", "launch": "public API, eager, fp32 logits",

@@ -196,6 +196,23 @@ int lmk_grouped_softmax_bwd(const void* x, const int64_t x_strides[3],
                             const float* grad_probs, float* grad_x,
                             int B, int H, int Lq, int Lk, int dtype, int guards, int max_groups, void* stream);
 
+/*
+ * The same softmax for the lm_benchmark call site without any [Lq,Lk] mask: the mask block of
+ * lm_benchmark/models/landmark.py:210-224 (causal rule "query i sees keys 0 .. i + Lk - Lq", last section, the masked
+ * landmark of the query's own block) is derived inside the kernel from one flag per (batch row, key), hidden scores
+ * count as -inf whatever x holds there (the masked_fill of :224), and rows are only read up to their last visible key.
+ * lm_benchmark flavour (guards).  Rows of at most 4096 keys; longer ones return LMK_ERR_UNSUPPORTED (build the masks and
+ * call lmk_grouped_softmax_fwd).
+ *   x [B,H,Lq,Lk] as above; is_mem_row: bool bytes, row b at is_mem_row + b * is_mem_stride; probs / grad_probs /
+ *   grad_x: fp32 dense [B,H,Lq,Lk].
+ */
+int lmk_grouped_softmax_causal_fwd(const void* x, const int64_t x_strides[3], const uint8_t* is_mem_row,
+                                   int64_t is_mem_stride, float* probs, int B, int H, int Lq, int Lk, int dtype,
+                                   int max_groups, void* stream);
+int lmk_grouped_softmax_causal_bwd(const void* x, const int64_t x_strides[3], const uint8_t* is_mem_row,
+                                   int64_t is_mem_stride, const float* grad_probs, float* grad_x, int B, int H, int Lq,
+                                   int Lk, int dtype, int max_groups, void* stream);
+
 /* Rotary conventions for the retrieval kernels. */
 enum {
   LMK_ROTARY_NONE = 0,

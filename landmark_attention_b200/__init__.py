@@ -7,7 +7,8 @@ from ._lib import PATH_AUTO, PATH_GENERAL, PATH_TCGEN05, ROTARY_HALF, ROTARY_INT
 from .fused import (FusedLandmarkAttention, attn_forward_with_stats, fused_landmark_attention,  # noqa: F401
                     landmark_sdpa)
 from .host_pipeline import HostAttentionPipeline  # noqa: F401
-from .grouped_softmax import (landmark_grouped_softmax, landmark_grouped_softmax_lm,  # noqa: F401
+from .grouped_softmax import (landmark_grouped_softmax, landmark_grouped_softmax_causal,  # noqa: F401
+                              landmark_grouped_softmax_lm,
                               lm_landmark_attention, prepare_landmark_masks)
 from .masked import landmark_attention_masked, masked_attention_supported  # noqa: F401
 from .mem_cache import MemLMCache, MemLMCacheStorage  # noqa: F401

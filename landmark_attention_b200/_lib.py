@@ -58,6 +58,10 @@ PROTOTYPES = {
     "lmk_grouped_softmax_bwd": (c_int, [c_void_p, POINTER(c_int64), c_void_p, POINTER(c_int64), c_void_p,
                                         POINTER(c_int64), c_void_p, POINTER(c_int64), c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "lmk_grouped_softmax_causal_fwd": (c_int, [c_void_p, POINTER(c_int64), c_void_p, c_int64, c_void_p, c_int, c_int,
+                                               c_int, c_int, c_int, c_int, c_void_p]),
+    "lmk_grouped_softmax_causal_bwd": (c_int, [c_void_p, POINTER(c_int64), c_void_p, c_int64, c_void_p, c_void_p, c_int,
+                                               c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "lmk_cache_store": (c_int, [c_void_p, c_void_p, POINTER(c_int64), c_void_p, c_void_p, POINTER(CacheDesc),
                                 POINTER(CacheDesc), c_void_p, POINTER(c_int64), c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p]),

@@ -27,6 +27,10 @@ struct GsParams {
   const float* gprobs;
   float* gx;
   int B, H, Lq, Lk, guards, max_groups;
+  // causal mode of the rows kernel: the three masks are derived from one flag per (batch row, key) and the rule
+  // "query i sees keys 0 .. i + Lk - Lq" (mask block of lm_benchmark/models/landmark.py:210-224); hidden scores count
+  // as -inf whatever x holds there
+  const uint8_t* row_flags; int64_t row_flags_stride; int causal;
 };
 
 struct Elem {
@@ -435,7 +439,7 @@ __device__ __forceinline__ void fold_chunk(float head, float tail, int nlm, int 
   __syncwarp();
 }
 
-template <typename T, bool kBackward>
+template <typename T, bool kBackward, bool kCausal>
 __global__ void __launch_bounds__(kGsWarps * 32) grouped_softmax_rows_kernel(GsParams p, int n_chunks) {
   extern __shared__ __align__(16) float gs_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -464,16 +468,52 @@ __global__ void __launch_bounds__(kGsWarps * 32) grouped_softmax_rows_kernel(GsP
   const bool guards = p.guards != 0;
 
   const T* xrow = reinterpret_cast<const T*>(p.x) + b * p.xs[0] + h * p.xs[1] + i * p.xs[2];
-  stage_row<T>(xrow, p.Lk, n_chunks, lane, xbuf);          // asynchronous copies, awaited below
+  constexpr bool causal = kCausal;
+  const int pi = i + p.Lk - p.Lq;                   // causal mode: the last key this query sees
+  const int n_live = causal ? min(n_chunks, pi / kFastChunk + 1) : n_chunks;   // chunks with a visible key
+  stage_row<T>(xrow, p.Lk, n_live, lane, xbuf);            // asynchronous copies, awaited below
   MaskRow mm, ml, mh;
-  mm.init(p.is_mem + b * p.ms[0] + h * p.ms[1] + i * p.ms[2], p.ms[3]);
-  ml.init(p.last + b * p.ls[0] + h * p.ls[1] + i * p.ls[2], p.ls[3]);
-  mh.init(p.hidden ? p.hidden + b * p.hs[0] + h * p.hs[1] + i * p.hs[2] : nullptr, p.hs[3]);
+  int p_last = -1;                                  // causal mode: the last landmark in front of key pi
+  if (causal) {
+    mm.init(p.row_flags + b * p.row_flags_stride, 1);
+    ml.init(nullptr, 0);
+    mh.init(nullptr, 0);
+    for (int j0 = (max(pi - 1, 0) / kFastChunk) * kFastChunk; j0 >= 0 && p_last < 0; j0 -= kFastChunk) {
+      const int j = j0 + lane * 8;
+      const uint2 m = mm.load8(j, min(max(min(p.Lk, pi) - j, 0), 8));      // keys in front of pi only
+      const uint64_t w = ((uint64_t)m.y << 32) | m.x;
+      int best = w ? j + (63 - __clzll((long long)w)) / 8 : -1;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+      p_last = best;
+    }
+  } else {
+    mm.init(p.is_mem + b * p.ms[0] + h * p.ms[1] + i * p.ms[2], p.ms[3]);
+    ml.init(p.last + b * p.ls[0] + h * p.ls[1] + i * p.ls[2], p.ls[3]);
+    mh.init(p.hidden ? p.hidden + b * p.hs[0] + h * p.hs[1] + i * p.hs[2] : nullptr, p.hs[3]);
+  }
+  auto low_bytes = [](int n) -> uint64_t { return n >= 8 ? ~0ull : ((1ull << (8 * n)) - 1ull); };
   auto load_flags = [&](int k) -> RawFlags {
     const int j = k * kFastChunk + lane * 8;
     const int n_in = min(max(p.Lk - j, 0), 8);
-    const uint2 m = mm.load8(j, n_in), l = ml.load8(j, n_in), hd = mh.load8(j, n_in);
     RawFlags f;
+    if (causal) {
+      constexpr uint64_t kOnes = 0x0101010101010101ull;
+      const uint2 m = mm.load8(j, n_in);
+      const uint64_t m64 = ((uint64_t)m.y << 32) | m.x;
+      const uint64_t inside = kOnes & low_bytes(n_in);
+      const uint64_t vis = inside & low_bytes(min(max(pi - j + 1, 0), 8));       // keys 0 .. pi
+      const uint64_t front = kOnes & low_bytes(min(max(pi - j, 0), 8));           // keys in front of pi
+      const uint64_t open = kOnes & ~low_bytes(min(max(p_last + 1 - j, 0), 8));   // keys behind the last landmark
+      const uint64_t mem = m64 & vis & front;        // a landmark at pi itself is masked like a hidden key
+      const uint64_t last = vis & ~m64 & open;
+      const uint64_t hid = kOnes & ~(mem | last | (vis & ~m64));
+      const uint64_t w = mem | (last << 1) | (hid << 2) | (inside << 3);
+      f.lo = (uint32_t)w;
+      f.hi = (uint32_t)(w >> 32);
+      return f;
+    }
+    const uint2 m = mm.load8(j, n_in), l = ml.load8(j, n_in), hd = mh.load8(j, n_in);
     f.lo = m.x | (l.x << 1) | (hd.x << 2);
     f.hi = m.y | (l.y << 1) | (hd.y << 2);
     if (n_in == 8) {
@@ -504,10 +544,20 @@ __global__ void __launch_bounds__(kGsWarps * 32) grouped_softmax_rows_kernel(GsP
     int base = 0;
     RawFlags raw = raw0;
     for (int k = 0; k < n_chunks; ++k) {
+      if (k >= n_live) {                            // causal mode: nothing visible from here on, nothing was read
+        meta[k * 32] = Meta{0u, (uint32_t)base | (1u << 23)};
+        continue;
+      }
       RawFlags nraw = raw;
-      if (k + 1 < n_chunks) nraw = load_flags(k + 1);
+      if (k + 1 < n_live) nraw = load_flags(k + 1);
       float x[8];
       stage_get<T>(xbuf + k * kFastChunk, lane, x);
+      if (causal && k == n_live - 1) {              // hidden scores count as -inf whatever the tensor holds
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          if (((v < 4 ? raw.lo : raw.hi) >> (8 * (v & 3) + 2)) & 1u) x[v] = -INFINITY;
+        row_put(xbuf + k * kFastChunk, lane, x);
+      }
       // all keys of the lane hidden, none a landmark or in the last section
       const bool shut = (raw.lo & raw.hi & 0x04040404u) == 0x04040404u && ((raw.lo | raw.hi) & 0x03030303u) == 0u;
       if (__all_sync(0xffffffffu, shut)) {
@@ -746,14 +796,22 @@ int launch(const GsParams& p, int dtype, cudaStream_t st) {
   if (rows == 0 || p.Lk == 0) return LMK_OK;
   unsigned grid = (unsigned)((rows + kGsWarps - 1) / kGsWarps);
   const bool fast = p.Lk <= kFastMaxLk && fast_smem_bytes(p.Lk, p.max_groups) <= kFastMaxSmem;
+  if (p.causal && !fast)
+    return fail(LMK_ERR_UNSUPPORTED, "grouped_softmax_causal: rows of %d keys with %d groups do not fit the row kernel "
+                                     "(at most %d keys); build the masks and use lmk_grouped_softmax_fwd", p.Lk,
+                p.max_groups, kFastMaxLk);
   const int n_chunks = (p.Lk + kFastChunk - 1) / kFastChunk;
   size_t smem = fast ? fast_smem_bytes(p.Lk, p.max_groups) : sizeof(float) * 4 * (size_t)p.max_groups * kGsWarps;
 #define LMK_GS_LAUNCH(T)                                                                                     \
   do {                                                                                                       \
-    if (fast) {                                                                                              \
-      LMK_CUDA(cudaFuncSetAttribute(grouped_softmax_rows_kernel<T, kBackward>,                               \
+    if (fast && p.causal) {                                                                                  \
+      LMK_CUDA(cudaFuncSetAttribute(grouped_softmax_rows_kernel<T, kBackward, true>,                         \
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                \
-      grouped_softmax_rows_kernel<T, kBackward><<<grid, kGsWarps * 32, smem, st>>>(p, n_chunks);             \
+      grouped_softmax_rows_kernel<T, kBackward, true><<<grid, kGsWarps * 32, smem, st>>>(p, n_chunks);       \
+    } else if (fast) {                                                                                       \
+      LMK_CUDA(cudaFuncSetAttribute(grouped_softmax_rows_kernel<T, kBackward, false>,                        \
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                \
+      grouped_softmax_rows_kernel<T, kBackward, false><<<grid, kGsWarps * 32, smem, st>>>(p, n_chunks);      \
     } else {                                                                                                 \
       LMK_CUDA(cudaFuncSetAttribute(grouped_softmax_kernel<T, kBackward>,                                    \
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                \
@@ -820,6 +878,44 @@ extern "C" int lmk_grouped_softmax_bwd(const void* x, const int64_t x_strides[3]
                      B, H, Lq, Lk, dtype, guards, max_groups);
   if (rc != LMK_OK) return rc;
   LMK_CHECK_ARG(grad_probs && grad_x, "grouped_softmax_bwd: null gradient pointer");
+  p.gprobs = grad_probs;
+  p.gx = grad_x;
+  return lmk::launch<true>(p, dtype, (cudaStream_t)stream);
+}
+
+// Mask block + grouped softmax of the lm_benchmark call site (lm_benchmark/models/landmark.py:210-232) from one flag
+// per (batch row, key): query i sees keys 0 .. i + Lk - Lq; hidden scores count as -inf.
+static int fill_causal(lmk::GsParams& p, const void* x, const int64_t* xs, const uint8_t* is_mem_row, int64_t row_stride,
+                       int B, int H, int Lq, int Lk, int dtype, int max_groups) {
+  LMK_CHECK_ARG(x && xs && is_mem_row, "grouped_softmax_causal: null pointer");
+  LMK_CHECK_ARG(B >= 0 && H >= 0 && Lq >= 0 && Lk >= Lq, "grouped_softmax_causal: need Lk >= Lq >= 0");
+  LMK_CHECK_ARG(dtype == LMK_F32 || dtype == LMK_F16 || dtype == LMK_BF16, "grouped_softmax_causal: bad dtype %d", dtype);
+  LMK_CHECK_ARG(max_groups >= 1 && max_groups <= 2048, "grouped_softmax_causal: max_groups %d outside [1, 2048]", max_groups);
+  p.x = x;
+  for (int i = 0; i < 3; ++i) p.xs[i] = xs[i];
+  p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk; p.guards = 1; p.max_groups = max_groups;
+  p.row_flags = is_mem_row; p.row_flags_stride = row_stride; p.causal = 1;
+  return LMK_OK;
+}
+
+extern "C" int lmk_grouped_softmax_causal_fwd(const void* x, const int64_t x_strides[3], const uint8_t* is_mem_row,
+                                              int64_t is_mem_stride, float* probs, int B, int H, int Lq, int Lk,
+                                              int dtype, int max_groups, void* stream) {
+  lmk::GsParams p{};
+  int rc = fill_causal(p, x, x_strides, is_mem_row, is_mem_stride, B, H, Lq, Lk, dtype, max_groups);
+  if (rc != LMK_OK) return rc;
+  LMK_CHECK_ARG(probs != nullptr, "grouped_softmax_causal_fwd: probs is null");
+  p.probs = probs;
+  return lmk::launch<false>(p, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int lmk_grouped_softmax_causal_bwd(const void* x, const int64_t x_strides[3], const uint8_t* is_mem_row,
+                                              int64_t is_mem_stride, const float* grad_probs, float* grad_x, int B,
+                                              int H, int Lq, int Lk, int dtype, int max_groups, void* stream) {
+  lmk::GsParams p{};
+  int rc = fill_causal(p, x, x_strides, is_mem_row, is_mem_stride, B, H, Lq, Lk, dtype, max_groups);
+  if (rc != LMK_OK) return rc;
+  LMK_CHECK_ARG(grad_probs && grad_x, "grouped_softmax_causal_bwd: null gradient pointer");
   p.gprobs = grad_probs;
   p.gx = grad_x;
   return lmk::launch<true>(p, dtype, (cudaStream_t)stream);

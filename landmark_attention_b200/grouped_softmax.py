@@ -75,6 +75,57 @@ class _GroupedSoftmax(torch.autograd.Function):
         return gx.to(x.dtype), None, None, None, None, None, None
 
 
+_CAUSAL_MAX_KEYS = 4096      # rows the mask-free kernel takes (include/b200lmk.h, lmk_grouped_softmax_causal_fwd)
+
+
+class _GroupedSoftmaxCausal(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, is_mem_row, max_groups):
+        L.require_cuda(x, is_mem_row)
+        if x.stride(3) != 1:
+            x = x.contiguous()
+        B, H, Lq, Lk = x.shape
+        flags = _as_u8(is_mem_row)
+        flags = flags if flags.stride(-1) == 1 else flags.contiguous()
+        probs = torch.empty((B, H, Lq, Lk), device=x.device, dtype=torch.float32)
+        rc = L.lib().lmk_grouped_softmax_causal_fwd(L.ptr(x), L.strides3(x), L.ptr(flags), flags.stride(0), L.ptr(probs),
+                                                    B, H, Lq, Lk, L.dtype_code(x), max_groups, L.stream_ptr(x.device))
+        L.check(rc, "lmk_grouped_softmax_causal_fwd")
+        ctx.save_for_backward(x, flags)
+        ctx.max_groups = max_groups
+        return probs
+
+    @staticmethod
+    def backward(ctx, gprobs):
+        x, flags = ctx.saved_tensors
+        B, H, Lq, Lk = x.shape
+        gprobs = gprobs.to(torch.float32).contiguous()
+        gx = torch.empty((B, H, Lq, Lk), device=x.device, dtype=torch.float32)
+        rc = L.lib().lmk_grouped_softmax_causal_bwd(L.ptr(x), L.strides3(x), L.ptr(flags), flags.stride(0), L.ptr(gprobs),
+                                                    L.ptr(gx), B, H, Lq, Lk, L.dtype_code(x), ctx.max_groups,
+                                                    L.stream_ptr(x.device))
+        L.check(rc, "lmk_grouped_softmax_causal_bwd")
+        return gx.to(x.dtype), None, None
+
+
+def landmark_grouped_softmax_causal(x, is_mem_row, max_mem_cnt=None):
+    """Mask block, masked_fill and grouped softmax of lm_benchmark's call site (lm_benchmark/models/landmark.py:210-232)
+    from the RAW scores x [B,H,Lq,Lk] and one landmark flag per (batch row, key), is_mem_row [B,Lk]: query i sees keys
+    0 .. i + Lk - Lq (a cache prefix of Lk - Lq columns is visible to every query).  No [Lq,Lk] mask is built or read,
+    hidden scores need not be filled with -inf beforehand, and rows are only read up to their last visible key.
+    fp32 probabilities, differentiable w.r.t. x.  Rows longer than 4096 keys go through the masks."""
+    B, H, Lq, Lk = x.shape
+    if max_mem_cnt is None:
+        max_mem_cnt = min(2048, Lk + 1)
+    max_groups = min(2048, max(int(max_mem_cnt), 2))
+    if Lk <= _CAUSAL_MAX_KEYS and (Lk + 255) // 256 * 1280 * 4 + 64 * max_groups <= 96 * 1024:
+        return _GroupedSoftmaxCausal.apply(x, is_mem_row, max_groups)
+    hidden = torch.ones(Lq, Lk, dtype=torch.bool, device=x.device).triu(Lk - Lq + 1)
+    mask, is_mem, last = prepare_landmark_masks(is_mem_row, hidden)
+    probs, _ = _GroupedSoftmax.apply(x.masked_fill(mask, float("-inf")), is_mem, last, mask, True, max_groups, 0)
+    return probs
+
+
 def _check_dim(x, dim):
     if dim not in (-1, x.dim() - 1):
         raise NotImplementedError("the grouped softmax runs over the last dimension")
@@ -156,19 +207,15 @@ def lm_landmark_attention(q, k, v, is_mem_row, sm_scale=None, max_groups=None, a
     if n_pre == 0 and masked_attention_supported(q, k, fused_groups):
         return landmark_attention_masked(q, k, v, is_mem_row, sm_scale, fused_groups)
     att = torch.matmul(q, k.transpose(-2, -1)) * sm_scale
-    hidden = torch.ones(T, T, dtype=torch.bool, device=q.device).triu(1)
     if n_pre:
         att = torch.cat((att_prefix.to(att.dtype), att), dim=-1)
         pre_mem = cache_values.get('is_mem')
         if pre_mem is None:
             pre_mem = torch.zeros((B, n_pre), dtype=torch.bool, device=q.device)
         is_mem_row = torch.cat((pre_mem.to(torch.bool), is_mem_row.to(torch.bool)), dim=-1)
-        hidden = torch.cat((torch.zeros((T, n_pre), dtype=torch.bool, device=q.device), hidden), dim=-1)
-    mask, is_mem, last = prepare_landmark_masks(is_mem_row, hidden)
-    att = att.masked_fill(mask, float("-inf"))
-    if max_groups is None:
-        max_groups = min(2048, T + n_pre + 1)
-    probs, _ = _GroupedSoftmax.apply(att, is_mem, last, mask, True, max_groups, 0)
+    # mask block + masked_fill + grouped softmax in one kernel, from the raw scores and the row flags
+    probs = landmark_grouped_softmax_causal(att, is_mem_row, max_groups if max_groups is not None
+                                            else min(2048, T + n_pre + 1))
     probs = probs.to(v.dtype)
     y = torch.matmul(probs[..., n_pre:], v)
     if n_pre:

@@ -151,3 +151,28 @@ def test_group_dropout_scales_whole_groups():
     assert (gp[..., -1].cpu() - (base * last).sum(-1) / (1 - p)).abs().max().item() < 1e-5
     (gx,) = torch.autograd.grad(got.sum(), [xd])                                 # differentiable through the factors
     assert torch.isfinite(gx).all()
+
+
+@pytest.mark.parametrize("B,H,Lq,Lk,dtype", [(2, 2, 512, 512, torch.float32), (2, 3, 200, 333, torch.float32),
+                                             (1, 2, 257, 1024, torch.bfloat16), (2, 1, 64, 64, torch.float16),
+                                             (1, 1, 300, 4096, torch.float32), (1, 1, 40, 4500, torch.float32)])
+def test_causal_form_needs_no_masks(B, H, Lq, Lk, dtype):
+    # landmark_grouped_softmax_causal(raw scores, row flags) against the oracle's mask block + masked_fill + grouped
+    # softmax (landmark.py:210-232); landmarks at random positions incl. the query's own key, a visible prefix of
+    # Lk - Lq keys, garbage (not -inf) at the hidden positions, forward and backward
+    g = torch.Generator().manual_seed(Lq * 7 + Lk)
+    flags = torch.rand(B, Lk, generator=g) < 0.06
+    x = (torch.randn(B, H, Lq, Lk, generator=g) * 3).to(dtype)
+    hidden = torch.ones(Lq, Lk, dtype=torch.bool).triu(Lk - Lq + 1)
+    mask, is_mem, last = O.prepare_landmark_masks(flags, hidden)
+    xo = x.float().detach().requires_grad_(True)
+    exp = O.grouped_softmax(xo.masked_fill(mask, float("-inf")), is_mem, last, attn_mask=mask, guards=True)
+    gp = torch.randn(B, H, Lq, Lk, generator=g)
+    (gx_exp,) = torch.autograd.grad(exp, [xo], gp)
+    xd = x.to(DEV).detach().requires_grad_(True)
+    got = P.landmark_grouped_softmax_causal(xd, flags.to(DEV), int(flags.sum(-1).max()) + 2)
+    assert (got.detach().cpu() - exp.detach()).abs().max().item() < 2e-6
+    (gx,) = torch.autograd.grad(got, [xd], gp.to(DEV))
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert (gx.float().cpu() - gx_exp).abs().max().item() < tol
+    assert not gx.float().cpu()[..., hidden].any()              # nothing flows to hidden scores
