@@ -446,7 +446,7 @@ def bench_config3(P, L, world, rank, local, dev, args, peaks):
         "flops": "7*B*H*T^2*D", "kernel_launches_per_call": 3}
     del q, k, v, do
     torch.manual_seed(5)               # same initial weights on every rank (DDP broadcasts rank 0's anyway)
-    model = bench_lm.LandmarkGPT(cfg, P.lm_landmark_attention).to(dev)
+    model = bench_lm.LandmarkGPT(cfg, P.lm_landmark_attention, P.rotary_apply).to(dev)
     n_params = sum(p.numel() for p in model.parameters())
     if world > 1:
         from torch.nn.parallel import DistributedDataParallel as DDP

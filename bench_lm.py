@@ -61,26 +61,30 @@ def apply_rotary(x, cos, sin):
 
 
 class Attention(nn.Module):
-    def __init__(self, n_embd, n_head, max_groups, attention_fn):
+    def __init__(self, n_embd, n_head, max_groups, attention_fn, rotary_fn=None):
         super().__init__()
         self.c_attn = nn.Linear(n_embd, 3 * n_embd, bias=False)
         self.c_proj = nn.Linear(n_embd, n_embd, bias=False)
         self.n_head, self.n_embd, self.max_groups, self.attention_fn = n_head, n_embd, max_groups, attention_fn
+        self.rotary_fn = rotary_fn
 
     def forward(self, x, is_mem, cos, sin):
         B, T, C = x.size()
         q, k, v = self.c_attn(x).split(self.n_embd, dim=2)
         q, k, v = [t.view(B, T, self.n_head, C // self.n_head).transpose(1, 2) for t in (q, k, v)]
-        q, k = apply_rotary(q, cos, sin), apply_rotary(k, cos, sin)
+        if self.rotary_fn is not None and q.is_cuda:
+            q, k = self.rotary_fn(q, k, cos.to(q.dtype), sin.to(q.dtype))
+        else:
+            q, k = apply_rotary(q, cos, sin), apply_rotary(k, cos, sin)
         y = self.attention_fn(q, k, v, is_mem, max_groups=self.max_groups)
         return self.c_proj(y.transpose(1, 2).contiguous().view(B, T, C))
 
 
 class Block(nn.Module):
-    def __init__(self, n_embd, n_head, max_groups, attention_fn):
+    def __init__(self, n_embd, n_head, max_groups, attention_fn, rotary_fn=None):
         super().__init__()
         self.ln_1 = nn.LayerNorm(n_embd, bias=False)
-        self.attn = Attention(n_embd, n_head, max_groups, attention_fn)
+        self.attn = Attention(n_embd, n_head, max_groups, attention_fn, rotary_fn)
         self.ln_2 = nn.LayerNorm(n_embd, bias=False)
         self.c_fc = nn.Linear(n_embd, 4 * n_embd, bias=False)
         self.c_proj = nn.Linear(4 * n_embd, n_embd, bias=False)
@@ -91,12 +95,12 @@ class Block(nn.Module):
 
 
 class LandmarkGPT(nn.Module):
-    def __init__(self, cfg, attention_fn):
+    def __init__(self, cfg, attention_fn, rotary_fn=None):
         super().__init__()
         self.cfg = cfg
         self.wte = nn.Embedding(cfg["vocab_size"], cfg["n_embd"])
-        self.h = nn.ModuleList([Block(cfg["n_embd"], cfg["n_head"], cfg["max_groups_for_softmax"], attention_fn)
-                                for _ in range(cfg["n_layer"])])
+        self.h = nn.ModuleList([Block(cfg["n_embd"], cfg["n_head"], cfg["max_groups_for_softmax"], attention_fn,
+                                      rotary_fn) for _ in range(cfg["n_layer"])])
         self.ln_f = nn.LayerNorm(cfg["n_embd"], bias=False)
         self.lm_head = nn.Linear(cfg["n_embd"], cfg["vocab_size"], bias=False)
         self.wte.weight = self.lm_head.weight

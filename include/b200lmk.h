@@ -275,6 +275,20 @@ int lmk_chunk_prepare(const void* q, const void* k, const void* v, const int64_t
                       int D, int dtype, void* stream);
 
 /*
+ * Rotary position embedding of the queries and keys of one layer in one launch: out = x * cos + rotate(x) * sin at
+ * positions pos0 + t, t = 0 .. T-1 (clamped to n_pos - 1).  rotary = LMK_ROTARY_HALF: rotate(x) = (-x[d + D/2], x[d])
+ * (llama/llama_mem.py:127-149); LMK_ROTARY_INTERLEAVED: pairs (x0, x1) -> (-x1, x0)
+ * (lm_benchmark/models/positional_encoders/rotary_utils.py:17-31, adapt_queries / adapt_keys of rotary.py).
+ * inverse != 0 rotates by the negative angle, which is the gradient of the forward call.  16-bit types round the two
+ * products and the sum as the tensor formulation does.
+ *   q, k (k nullable together with k_out) [B,H,T,D], element strides {batch, head, row}, last dim contiguous;
+ *   cos_table, sin_table [n_pos, D] of the same dtype; q_out, k_out dense [B,H,T,D].
+ */
+int lmk_rotary_apply(const void* q, const void* k, const int64_t q_strides[3], const int64_t k_strides[3],
+                     const void* cos_table, const void* sin_table, int n_pos, int64_t pos0, int rotary, int inverse,
+                     void* q_out, void* k_out, int B, int H, int T, int D, int dtype, void* stream);
+
+/*
  * Landmark scores: scores[b,h,t,n] = sm_scale * q[b,h,t,:] . rot(K[b,h,n,block-1,:], slot position of n).
  * Replaces llama/llama_mem.py:357-367 and lm_benchmark/models/caches/mem_cache.py:51-61.
  *   q [B,H,T,D] dense (already rotated), k_cache per desc, cos/sin tables [n_pos, D] in `dtype` (NULL with

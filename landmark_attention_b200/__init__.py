@@ -13,5 +13,5 @@ from .grouped_softmax import (landmark_grouped_softmax, landmark_grouped_softmax
 from .masked import landmark_attention_masked, masked_attention_supported  # noqa: F401
 from .mem_cache import MemLMCache, MemLMCacheStorage  # noqa: F401
 from .retrieval import (LandmarkKVCache, OffloadedLandmarkCache, chunk_prepare, gather_kv, landmark_scores, llama_retrieval_attention, make_desc,  # noqa: F401
-                        rotary_tables_half, rotary_tables_interleaved, selected_attend, selected_logits, selected_pv,
+                        rotary_apply, rotary_tables_half, rotary_tables_interleaved, selected_attend, selected_logits, selected_pv,
                         topk_sorted)

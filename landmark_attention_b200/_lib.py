@@ -65,6 +65,8 @@ PROTOTYPES = {
     "lmk_cache_store": (c_int, [c_void_p, c_void_p, POINTER(c_int64), c_void_p, c_void_p, POINTER(CacheDesc),
                                 POINTER(CacheDesc), c_void_p, POINTER(c_int64), c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p]),
+    "lmk_rotary_apply": (c_int, [c_void_p, c_void_p, POINTER(c_int64), POINTER(c_int64), c_void_p, c_void_p, c_int,
+                                 c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "lmk_chunk_prepare": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(c_int64), POINTER(c_int64), POINTER(c_int64),
                                   c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_void_p, POINTER(c_int64), c_int64, c_int, c_int,

@@ -149,6 +149,72 @@ __global__ void __launch_bounds__(128) cache_store_kernel(const uint4* __restric
   }
 }
 
+
+// Rotary position embedding of a [B,H,T,D] tensor pair (queries and keys of one layer) in one launch, both rotary
+// flavours, forward or inverse (the inverse rotation is the gradient of the forward one).  16-bit types use packed
+// arithmetic with the three roundings of the tensor formulation x * cos + rotate(x) * sin.
+struct RotParams {
+  const void* in[2];
+  void* out[2];
+  int64_t st[2][3];                     // element strides {batch, head, row} of the inputs; outputs are dense
+  const void *cos_t, *sin_t;
+  int n_pos;
+  int64_t pos0;
+  int mode, inverse, n_tensors;
+  int H, T, D;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) rotary_pair_kernel(RotParams p) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int vpr = p.D / VEC;                                 // vectors per row
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= (int64_t)p.T * vpr) return;
+  const int t = (int)(e / vpr), c = (int)(e - (int64_t)t * vpr);
+  const int bh = blockIdx.y, b = bh / p.H, h = bh - b * p.H;
+  const int64_t pos = min(p.pos0 + t, (int64_t)p.n_pos - 1);
+  const int half = p.D / 2;
+  // the partner elements: interleaved pairs live in the same vector; rotate-half pairs d with d +- D/2
+  const bool lower = c * VEC < half;
+  const int pc = p.mode == LMK_ROTARY_HALF ? (lower ? c + vpr / 2 : c - vpr / 2) : c;
+  const uint4 cs = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.cos_t) + pos * p.D + c * VEC);
+  uint4 sn = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.sin_t) + pos * p.D + c * VEC);
+  for (int i = 0; i < p.n_tensors; ++i) {
+    const T* src = static_cast<const T*>(p.in[i]) + b * p.st[i][0] + h * p.st[i][1] + t * p.st[i][2];
+    const uint4 x = *reinterpret_cast<const uint4*>(src + c * VEC);
+    const uint4 y = *reinterpret_cast<const uint4*>(src + pc * VEC);
+    uint4 o;
+    if constexpr (sizeof(T) == 2) {
+      const uint32_t* xw = reinterpret_cast<const uint32_t*>(&x);
+      const uint32_t* yw = reinterpret_cast<const uint32_t*>(&y);
+      const uint32_t *cw = reinterpret_cast<const uint32_t*>(&cs), *sw = reinterpret_cast<const uint32_t*>(&sn);
+      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        uint32_t rot;                   // rotate(x) at this position
+        if (p.mode == LMK_ROTARY_HALF) rot = lower ? (yw[u] ^ 0x80008000u) : yw[u];
+        else rot = __byte_perm(xw[u], xw[u], 0x1032) ^ 0x00008000u;       // (x0, x1) -> (-x1, x0)
+        const uint32_t s = p.inverse ? (sw[u] ^ 0x80008000u) : sw[u];
+        ow[u] = Pair16<T>::add(Pair16<T>::mul(xw[u], cw[u]), Pair16<T>::mul(rot, s));
+      }
+    } else {
+      const float* xf = reinterpret_cast<const float*>(&x);
+      const float* yf = reinterpret_cast<const float*>(&y);
+      const float *cf = reinterpret_cast<const float*>(&cs), *sf = reinterpret_cast<const float*>(&sn);
+      float* of = reinterpret_cast<float*>(&o);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float rot;
+        if (p.mode == LMK_ROTARY_HALF) rot = lower ? -yf[u] : yf[u];
+        else rot = (u & 1) ? xf[u - 1] : -xf[u + 1];
+        const float s = p.inverse ? -sf[u] : sf[u];
+        of[u] = xf[u] * cf[u] + rot * s;
+      }
+    }
+    *reinterpret_cast<uint4*>(static_cast<T*>(p.out[i]) + (((int64_t)bh * p.T + t) * p.D) + c * VEC) = o;
+  }
+}
+
 }  // namespace
 }  // namespace lmk
 
@@ -236,6 +302,46 @@ extern "C" int lmk_chunk_prepare(const void* q, const void* k, const void* v, co
   dim3 grid((t_pad + rows_per_cta - 1) / rows_per_cta, B * H);
   if (dtype == LMK_BF16) chunk_prepare_kernel<__nv_bfloat16><<<grid, 128, 0, (cudaStream_t)stream>>>(p);
   else chunk_prepare_kernel<__half><<<grid, 128, 0, (cudaStream_t)stream>>>(p);
+  LMK_CUDA(cudaGetLastError());
+  return LMK_OK;
+}
+
+extern "C" int lmk_rotary_apply(const void* q, const void* k, const int64_t q_strides[3], const int64_t k_strides[3],
+                                const void* cos_table, const void* sin_table, int n_pos, int64_t pos0, int rotary,
+                                int inverse, void* q_out, void* k_out, int B, int H, int T, int D, int dtype,
+                                void* stream) {
+  using namespace lmk;
+  LMK_CHECK_ARG(q && q_strides && q_out && cos_table && sin_table, "rotary_apply: null pointer");
+  LMK_CHECK_ARG((k == nullptr) == (k_out == nullptr) && (k == nullptr || k_strides != nullptr),
+                "rotary_apply: k, k_strides and k_out go together");
+  LMK_CHECK_ARG(dtype == LMK_F32 || dtype == LMK_F16 || dtype == LMK_BF16, "rotary_apply: bad dtype %d", dtype);
+  LMK_CHECK_ARG(rotary == LMK_ROTARY_HALF || rotary == LMK_ROTARY_INTERLEAVED, "rotary_apply: bad rotary mode %d", rotary);
+  const int vec = dtype == LMK_F32 ? 4 : 8;
+  LMK_CHECK_ARG(B >= 0 && H >= 1 && T >= 0 && D >= 2 * vec && D % (2 * vec) == 0,
+                "rotary_apply: head dim %d must be a multiple of %d", D, 2 * vec);
+  LMK_CHECK_ARG(n_pos >= 1 && pos0 >= 0, "rotary_apply: bad positions");
+  uintptr_t align = (uintptr_t)q | (uintptr_t)k | (uintptr_t)q_out | (uintptr_t)k_out | (uintptr_t)cos_table |
+                    (uintptr_t)sin_table;
+  LMK_CHECK_ARG((align & 15) == 0, "rotary_apply: pointers must be 16-byte aligned");
+  for (int i = 0; i < 3; ++i)
+    LMK_CHECK_ARG(q_strides[i] % vec == 0 && (k == nullptr || k_strides[i] % vec == 0),
+                  "rotary_apply: strides must be multiples of %d elements", vec);
+  if (B == 0 || T == 0) return LMK_OK;
+  LMK_CHECK_ARG((int64_t)B * H <= 65535, "rotary_apply: grid too large");
+  RotParams p{};
+  p.in[0] = q; p.in[1] = k; p.out[0] = q_out; p.out[1] = k_out;
+  for (int i = 0; i < 3; ++i) {
+    p.st[0][i] = q_strides[i];
+    p.st[1][i] = k ? k_strides[i] : 0;
+  }
+  p.cos_t = cos_table; p.sin_t = sin_table; p.n_pos = n_pos; p.pos0 = pos0;
+  p.mode = rotary; p.inverse = inverse != 0; p.n_tensors = k ? 2 : 1;
+  p.H = H; p.T = T; p.D = D;
+  const int64_t vecs = (int64_t)T * (D / vec);
+  dim3 grid((unsigned)((vecs + 255) / 256), B * H);
+  if (dtype == LMK_BF16) rotary_pair_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+  else if (dtype == LMK_F16) rotary_pair_kernel<__half><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+  else rotary_pair_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
   LMK_CUDA(cudaGetLastError());
   return LMK_OK;
 }

@@ -28,6 +28,43 @@ def rotary_tables_interleaved(n_pos, dim, dtype, device):
     return ang.cos().to(dtype).contiguous(), ang.sin().to(dtype).contiguous()
 
 
+class _RotaryPair(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, cos, sin, pos0, mode):
+        ctx.save_for_backward(cos, sin)
+        ctx.pos0, ctx.mode = pos0, mode
+        return _rotary_launch(q, k, cos, sin, pos0, mode, False)
+
+    @staticmethod
+    def backward(ctx, gq, gk):
+        cos, sin = ctx.saved_tensors
+        dq, dk = _rotary_launch(gq, gk, cos, sin, ctx.pos0, ctx.mode, True)      # rotation by the negative angle
+        return dq, dk, None, None, None, None
+
+
+def _rotary_launch(q, k, cos, sin, pos0, mode, inverse):
+    L.require_cuda(q, k, cos, sin)
+    B, H, T, D = q.shape
+    q, k = [t if t.stride(3) == 1 else t.contiguous() for t in (q, k)]
+    assert k.shape == q.shape and q.dtype == k.dtype == cos.dtype == sin.dtype
+    assert cos.is_contiguous() and sin.is_contiguous() and cos.shape[1] == D
+    qo, ko = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device), torch.empty((B, H, T, D), dtype=q.dtype, device=q.device)
+    rc = L.lib().lmk_rotary_apply(L.ptr(q), L.ptr(k), L.strides3(q), L.strides3(k), L.ptr(cos), L.ptr(sin), cos.shape[0],
+                                  int(pos0), mode, int(inverse), L.ptr(qo), L.ptr(ko), B, H, T, D, L.dtype_code(q),
+                                  L.stream_ptr(q.device))
+    L.check(rc, "lmk_rotary_apply")
+    return qo, ko
+
+
+def rotary_apply(q, k, cos, sin, pos0=0, interleaved=True):
+    """Rotary position embedding of q and k [B,H,T,D] (any batch/head/row strides) at positions pos0 .. pos0+T-1 in one
+    launch, differentiable (the backward pass is the inverse rotation, one launch as well).  interleaved=True is
+    lm_benchmark's adapt_queries / adapt_keys (positional_encoders/rotary.py:35-55 with rotary_utils.py:17-31);
+    False is LLaMA's rotate-half (llama/llama_mem.py:127-149).  cos, sin: tables [n_pos, D] of q's dtype
+    (rotary_tables_interleaved / rotary_tables_half).  Returns dense (q_rot, k_rot)."""
+    return _RotaryPair.apply(q, k, cos, sin, int(pos0), L.ROTARY_INTERLEAVED if interleaved else L.ROTARY_HALF)
+
+
 def apply_rotary_half(x, cos, sin, positions):
     """x*cos + rotate_half(x)*sin with tables gathered at `positions` (llama/llama_mem.py:127-149)."""
     c, s = cos[positions], sin[positions]

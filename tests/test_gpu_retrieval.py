@@ -436,3 +436,38 @@ def test_chunk_prepare_equals_the_tensor_formulation(dtype):
     given = torch.rand(1, T, device=DEV) < 0.2
     _, _, _, _, flags2 = chunk_prepare(q, k, v, cos, sin, C, given, blk, 128)
     assert torch.equal(flags2[:, :T], given.to(torch.uint8).expand(B, T)) and not flags2[:, T:].any()
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_rotary_apply_equals_the_tensor_formulation(dtype, interleaved):
+    # q and k of one layer in one launch, strided [B,T,H,D] projections viewed as [B,H,T,D]; 16-bit results bit-exact
+    # against x * cos + rotate(x) * sin in the tensor dtype; the backward pass against autograd of that formulation
+    torch.manual_seed(31)
+    B, H, T, D, pos0 = 2, 3, 70, 64, 5
+    qkv = torch.randn(B, T, 3 * H * D).to(dtype).to(DEV)
+    q, k, _ = [t.view(B, T, H, D).transpose(1, 2) for t in qkv.split(H * D, dim=2)]
+    tables = P.rotary_tables_interleaved if interleaved else P.rotary_tables_half
+    cos, sin = tables(pos0 + T, D, dtype, DEV)
+    c, s = cos[pos0:pos0 + T], sin[pos0:pos0 + T]
+
+    def rotate(x):
+        if interleaved:
+            xr = x.reshape(*x.shape[:-1], -1, 2)
+            return torch.stack((-xr[..., 1], xr[..., 0]), dim=-1).reshape(x.shape)
+        return torch.cat((-x[..., D // 2:], x[..., : D // 2]), dim=-1)
+
+    qd, kd = q.detach().clone().requires_grad_(True), k.detach().clone().requires_grad_(True)
+    eq, ek = qd * c + rotate(qd) * s, kd * c + rotate(kd) * s
+    qg, kg = q.detach().requires_grad_(True), k.detach().requires_grad_(True)
+    gq, gk_ = P.rotary_apply(qg, kg, cos, sin, pos0, interleaved=interleaved)
+    if dtype == torch.float32:
+        assert (gq - eq).abs().max().item() < 1e-6 and (gk_ - ek).abs().max().item() < 1e-6
+    else:
+        assert torch.equal(gq, eq) and torch.equal(gk_, ek)
+    wq, wk = torch.randn_like(eq), torch.randn_like(ek)
+    e_dq, e_dk = torch.autograd.grad((eq.float() * wq.float()).sum() + (ek.float() * wk.float()).sum(), [qd, kd])
+    g_dq, g_dk = torch.autograd.grad((gq.float() * wq.float()).sum() + (gk_.float() * wk.float()).sum(), [qg, kg])
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    assert (g_dq.float() - e_dq.float()).abs().max().item() < tol
+    assert (g_dk.float() - e_dk.float()).abs().max().item() < tol
