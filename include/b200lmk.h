@@ -175,7 +175,8 @@ int lmk_attn_mask_bwd(const void* q, const void* k, const void* v, const uint8_t
  *   probs: fp32 dense [B,H,Lq,Lk].  group_prob (nullable): fp32 dense [B,H,Lq,max_mem_cnt]
  *     (slot g = probability of the landmark closing group g, last slot = total last-section probability).
  *   guards != 0 selects the lm_benchmark flavour (all -inf group -> 0 instead of NaN).
- *   max_groups: upper bound on 1 + number of landmarks in any row (<= 2048).
+ *   max_groups: upper bound on 1 + number of landmarks in any row (<= 2048); a row with max_groups or more
+ *     landmarks records 501 in the device status word (lmk_device_status) and its surplus groups get probability 0.
  */
 int lmk_grouped_softmax_fwd(const void* x, const int64_t x_strides[3],
                             const uint8_t* is_mem, const int64_t is_mem_strides[4],

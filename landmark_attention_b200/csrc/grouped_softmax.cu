@@ -10,6 +10,7 @@
 // Reference semantics: llama/llama_mem.py:168-243 (guards = 0) and lm_benchmark/models/landmark.py:37-119
 // (guards = 1: an all -inf group yields 0 instead of NaN, :48,:54).
 #include "common.cuh"
+#include "attn_params.h"
 
 namespace lmk {
 namespace {
@@ -31,7 +32,10 @@ struct GsParams {
   // "query i sees keys 0 .. i + Lk - Lq" (mask block of lm_benchmark/models/landmark.py:210-224); hidden scores count
   // as -inf whatever x holds there
   const uint8_t* row_flags; int64_t row_flags_stride; int causal;
+  int* status;          // device status word: set to kErrSoftmaxGroups when a row holds max_groups or more landmarks
 };
+
+enum { kErrSoftmaxGroups = 501 };
 
 struct Elem {
   float x;
@@ -130,6 +134,7 @@ __global__ void __launch_bounds__(kGsWarps * 32) grouped_softmax_kernel(GsParams
     if (seg_tail(e.c, lane) && e.c < G) gmax[e.c] = fmaxf(gmax[e.c], v);
     __syncwarp();
   }
+  if (lane == 0 && rd.base >= G && p.status != nullptr) atomicCAS(p.status, 0, kErrSoftmaxGroups);
   bmax = warp_max(bmax);
   if (guards && isinf(bmax)) bmax = 0.f;
 
@@ -612,6 +617,7 @@ __global__ void __launch_bounds__(kGsWarps * 32) grouped_softmax_rows_kernel(GsP
       fold_chunk<true>(nlm ? head : run, run, nlm, c0, flags, gmax, G, lane);
       raw = nraw;
     }
+    if (lane == 0 && base >= G && p.status != nullptr) atomicCAS(p.status, 0, kErrSoftmaxGroups);
   }
   bmax = warp_max(bmax);
   if (guards && isinf(bmax)) bmax = 0.f;
@@ -794,6 +800,8 @@ template <bool kBackward>
 int launch(const GsParams& p, int dtype, cudaStream_t st) {
   const int64_t rows = (int64_t)p.B * p.H * p.Lq;
   if (rows == 0 || p.Lk == 0) return LMK_OK;
+  GsParams& pw = const_cast<GsParams&>(p);
+  pw.status = device_status_word();
   unsigned grid = (unsigned)((rows + kGsWarps - 1) / kGsWarps);
   const bool fast = p.Lk <= kFastMaxLk && fast_smem_bytes(p.Lk, p.max_groups) <= kFastMaxSmem;
   if (p.causal && !fast)

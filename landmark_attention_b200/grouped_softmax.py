@@ -133,11 +133,12 @@ def _check_dim(x, dim):
 
 def landmark_grouped_softmax(x, dim, is_mem, last_section_mask, max_groups=None):
     """llama flavour (llama/llama_mem.py:222-243).  The reference hard-codes room for 63 landmarks per row
-    (max_mem_cnt = 64, :228); here `max_groups` (default: from the row length, at most 2048) bounds 1 + the number of
-    landmarks in a row."""
+    (max_mem_cnt = 64, :228); here `max_groups` bounds 1 + the number of landmarks in a row.  Default: the row length + 1,
+    capped at 256 so that rows of up to 4096 keys stay on the fast kernel; a row with more landmarks than that sets
+    the device status word (501, see `_lib.device_status`) instead of passing unnoticed -- give `max_groups` then."""
     _check_dim(x, dim)
     if max_groups is None:
-        max_groups = min(2048, x.shape[-1] + 1)
+        max_groups = min(256, x.shape[-1] + 1)
     probs, _ = _GroupedSoftmax.apply(x, is_mem, last_section_mask, None, False, max_groups, 0)
     return probs
 

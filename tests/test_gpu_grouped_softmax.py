@@ -176,3 +176,27 @@ def test_causal_form_needs_no_masks(B, H, Lq, Lk, dtype):
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     assert (gx.float().cpu() - gx_exp).abs().max().item() < tol
     assert not gx.float().cpu()[..., hidden].any()              # nothing flows to hidden scores
+
+
+def test_too_many_landmarks_for_max_groups_are_reported():
+    # max_groups bounds 1 + landmarks per row; a row beyond it must not pass unnoticed: device status word 501
+    from landmark_attention_b200 import _lib as L
+    g = torch.Generator().manual_seed(4)
+    B, H, Lq, Lk = 1, 1, 4, 300
+    is_mem = torch.zeros(B, 1, Lq, Lk, dtype=torch.bool)
+    is_mem[..., 9::10] = True                                   # 30 landmarks
+    last = torch.zeros_like(is_mem)
+    last[..., 0] = True
+    x = torch.randn(B, H, Lq, Lk, generator=g).to(DEV)
+    L.device_status()
+    P.landmark_grouped_softmax(x, -1, is_mem.to(DEV), last.to(DEV), max_groups=31)
+    assert L.device_status() == 0
+    P.landmark_grouped_softmax(x, -1, is_mem.to(DEV), last.to(DEV), max_groups=30)
+    assert L.device_status() == 501
+    assert L.device_status() == 0                               # reading clears it
+    flags = torch.zeros(B, Lk, dtype=torch.bool)
+    flags[:, 9::10] = True
+    P.landmark_grouped_softmax_causal(x, flags.to(DEV), 30)     # the last query sees 29 landmarks in front of its own key
+    assert L.device_status() == 0
+    P.landmark_grouped_softmax_causal(x, flags.to(DEV), 29)
+    assert L.device_status() == 501
