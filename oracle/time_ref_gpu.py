@@ -1,7 +1,7 @@
 """Time the reference's own GPU code (staged under oracle/_ref/, see make_ref.py) on this machine's GPU.
 TEST INFRASTRUCTURE ONLY: it runs none of this repository's kernels.
 
-    python oracle/time_ref_gpu.py [--out gpurun_out/ref_gpu.json] [--sweep]
+    python oracle/time_ref_gpu.py [--out ref_gpu.json] [--sweep]
 
 What is timed (CUDA events, seeded inputs of the benchmark's shapes):
   * the reference's Triton kernels through its public `fused_landmark_attention` (forward, forward+backward) at the
@@ -48,7 +48,7 @@ def flops(B, H, L, D):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "ref_gpu.json"))
+    ap.add_argument("--out", default="ref_gpu.json", help="where the JSON record goes (default: the working directory)")
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--retrieval", action="store_true",
                     help="also time the reference's own LlamaAttention.forward cache branch (llama/llama_mem.py:318-430) for "
@@ -65,7 +65,8 @@ def main():
         res["env"]["triton"] = repr(e)
 
     def save():
-        os.makedirs(os.path.dirname(a.out), exist_ok=True)
+        if os.path.dirname(a.out):
+            os.makedirs(os.path.dirname(a.out), exist_ok=True)
         with open(a.out, "w") as f:
             json.dump(res, f, indent=1, default=str)
 
