@@ -76,6 +76,14 @@ def fused_landmark_attention(q, k, v, is_mem=None, sm_scale=None, block_size=64,
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(q.size(-1))
     D = q.shape[-1]
+    if (path == L.PATH_AUTO and q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and D <= 128 and D % 8 == 0
+            and q.shape[2] % 128 != 0 and n_history_kv % 64 == 0):
+        # lengths that are not whole 128-row tiles: rows of zeros appended to q, k and v come after every real query,
+        # so causality hides the extra keys and the extra query rows are dropped again
+        extra = -q.shape[2] % 128
+        if _tensor_core_route(q.shape[0], q.shape[1], q.shape[2] + extra, k.shape[2] + extra, block_size, q.dtype):
+            qp, kp, vp = [torch.nn.functional.pad(t, (0, 0, 0, extra)) for t in (q, k, v)]
+            return fused_landmark_attention(qp, kp, vp, None, sm_scale, block_size, path)[:, :, :q.shape[2]]
     if (path == L.PATH_AUTO and D < 128 and D % 8 == 0 and q.is_cuda and q.dtype in (torch.bfloat16, torch.float16)
             and _tensor_core_route(q.shape[0], q.shape[1], q.shape[2], k.shape[2], block_size, q.dtype)):
         # head dims below 128: zero columns change neither q k^T nor the real columns of p v, and the tensor-core

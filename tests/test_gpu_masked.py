@@ -202,3 +202,28 @@ def test_fused_entry_with_smaller_head_dims_runs_on_tensor_cores(D, blk, Lq, Lk)
         assert got.shape == exp.shape and torch.isfinite(got).all()
         assert (got - exp).abs().max().item() < 3e-2 and rel_l2(got, exp) < 1e-2
     assert L.device_status() == 0
+
+
+@pytest.mark.parametrize("D,blk,Lq,Lk", [(128, 64, 200, 200), (128, 64, 130, 258), (64, 64, 1000, 1000), (128, 32, 100, 164)])
+def test_fused_entry_with_ragged_lengths_runs_on_tensor_cores(D, blk, Lq, Lk):
+    # 16-bit problems whose lengths are not whole tiles are padded with zero rows at the end (hidden by causality) and
+    # run on the tensor-core kernels; forward and backward against the oracle on the unpadded problem
+    g = torch.Generator().manual_seed(Lq + Lk)
+    B, H = 1, 2
+    q = (torch.randn(B, H, Lq, D, generator=g) * 0.5).to(torch.bfloat16)
+    k, v = [(torch.randn(B, H, Lk, D, generator=g) * 0.5).to(torch.bfloat16) for _ in range(2)]
+    do = torch.randn(B, H, Lq, D, generator=g).to(torch.bfloat16)
+    pad = -Lk % blk                                   # the oracle works on whole blocks: same trick, on its side
+    kf, vf = [torch.nn.functional.pad(t.float(), (0, 0, 0, pad)) for t in (k, v)]
+    qf, dof = [torch.nn.functional.pad(t.float(), (0, 0, 0, pad)) for t in (q, do)]
+    eo, edq, edk, edv = O.landmark_attention_grads(qf, kf, vf, dof, blk)
+    eo, edq, edk, edv = eo[:, :, :Lq], edq[:, :, :Lq], edk[:, :, :Lk], edv[:, :, :Lk]
+    qd, kd, vd = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    out = P.fused_landmark_attention(qd, kd, vd, None, block_size=blk)
+    assert out.shape == (B, H, Lq, D) and "FusedLandmarkAttention" not in type(out.grad_fn).__name__
+    dq, dk, dv = torch.autograd.grad(out, [qd, kd, vd], do.to(DEV))
+    for got, exp in ((out, eo), (dq, edq), (dk, edk), (dv, edv)):
+        got = got.float().cpu()
+        assert got.shape == exp.shape and torch.isfinite(got).all()
+        assert (got - exp).abs().max().item() < 3e-2 and rel_l2(got, exp) < 1e-2
+    assert L.device_status() == 0
