@@ -759,7 +759,8 @@ extern "C" int lmk_landmark_scores(const void* q, const void* k_cache, const lmk
   const int64_t rows = (int64_t)B * H * T;
   if (workspace != nullptr && scores_sm100_supported(D, dtype, T, desc->n_blocks) &&
       workspace_bytes >= scores_sm100_workspace(B, H, desc->n_blocks) && ((uintptr_t)workspace % 256 == 0) &&
-      ((uintptr_t)q % 16 == 0)) {
+      (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)cos_table | (uintptr_t)sin_table) % 16 == 0) &&
+      desc->stride_b % 8 == 0 && desc->stride_h % 8 == 0 && desc->stride_block % 8 == 0 && desc->stride_row % 8 == 0) {
     rc = scores_sm100(q, k_cache, *desc, cos_table, sin_table, n_pos, rotary, scores, B, H, T, sm_scale, dtype,
                       workspace, st);
     if (rc != LMK_OK) return rc;

@@ -24,35 +24,79 @@ __host__ __device__ __forceinline__ int logical_age2(int phys, int ring_start, i
 
 constexpr int kRotPerCta = 16;
 
+template <typename T> struct Pk16;      // two 16-bit values in one register, rounded like the tensor formulation
+template <> struct Pk16<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
+  static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
+};
+template <> struct Pk16<__half> {
+  static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
+  static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
+};
+
+// Sixteen landmark rows per CTA, eight threads per row: each thread takes one 16-byte vector of the low half of the
+// row and its partner of the high half, so every load of the CTA is in flight at once.
 template <typename T>
 __global__ void __launch_bounds__(128) rotate_landmarks_kernel(const T* __restrict__ kc, lmk_cache_desc desc,
                                                                const T* __restrict__ cos_t, const T* __restrict__ sin_t,
                                                                int n_pos, int rotary, T* __restrict__ out, int H) {
-  constexpr int D = 128;
+  constexpr int D = 128, HALF = 64;
   const int bh = blockIdx.y, b = bh / H, h = bh - b * H;
-  const int d = threadIdx.x;
   const int N = desc.n_blocks, blk = desc.block;
-  for (int n = blockIdx.x * kRotPerCta; n < min(N, (int)(blockIdx.x + 1) * kRotPerCta); ++n) {
+  const int n = blockIdx.x * kRotPerCta + (threadIdx.x >> 3), d0 = (threadIdx.x & 7) * 8;
+  if (n >= N) return;
   const T* row = kc + b * desc.stride_b + h * desc.stride_h + (int64_t)n * desc.stride_block +
                  (int64_t)(blk - 1) * desc.stride_row;
-  float x = to_f32(row[d]);
-  float val = x;
+  uint4 lo = *reinterpret_cast<const uint4*>(row + d0), hi = *reinterpret_cast<const uint4*>(row + HALF + d0);
   if (rotary != LMK_ROTARY_NONE) {
     const int logical = logical_age2(n, desc.ring_start, N);
     const int first_recent = N - desc.top_k;
     const int slot = logical >= first_recent ? logical - first_recent + 1 : 0;
     int pos = desc.pos_base + slot * blk + blk - 1;
     pos = max(0, min(pos, n_pos - 1));
-    const float c = to_f32(cos_t[(int64_t)pos * D + d]), s = to_f32(sin_t[(int64_t)pos * D + d]);
-    float partner;
-    if (rotary == LMK_ROTARY_HALF) partner = d < D / 2 ? -to_f32(row[d + D / 2]) : to_f32(row[d - D / 2]);
-    else partner = (d & 1) ? to_f32(row[d - 1]) : -to_f32(row[d + 1]);
-    const float a = to_f32(from_f32<T>(__fmul_rn(x, c)));
-    const float bb = to_f32(from_f32<T>(__fmul_rn(partner, s)));
-    val = to_f32(from_f32<T>(__fadd_rn(a, bb)));
+    const uint4 cl = *reinterpret_cast<const uint4*>(cos_t + (int64_t)pos * D + d0);
+    const uint4 ch = *reinterpret_cast<const uint4*>(cos_t + (int64_t)pos * D + HALF + d0);
+    const uint4 sl = *reinterpret_cast<const uint4*>(sin_t + (int64_t)pos * D + d0);
+    const uint4 sh = *reinterpret_cast<const uint4*>(sin_t + (int64_t)pos * D + HALF + d0);
+    const uint32_t *l = reinterpret_cast<const uint32_t*>(&lo), *hh = reinterpret_cast<const uint32_t*>(&hi);
+    const uint32_t *c0 = reinterpret_cast<const uint32_t*>(&cl), *c1 = reinterpret_cast<const uint32_t*>(&ch);
+    const uint32_t *s0 = reinterpret_cast<const uint32_t*>(&sl), *s1 = reinterpret_cast<const uint32_t*>(&sh);
+    uint32_t ol[4], oh[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      uint32_t pl, ph;                 // rotate(x) for the low and the high vector
+      if (rotary == LMK_ROTARY_HALF) {
+        pl = hh[u] ^ 0x80008000u;      // (-x[d + D/2], x[d])
+        ph = l[u];
+      } else {
+        pl = __byte_perm(l[u], l[u], 0x1032) ^ 0x00008000u;      // pairs (x0, x1) -> (-x1, x0)
+        ph = __byte_perm(hh[u], hh[u], 0x1032) ^ 0x00008000u;
+      }
+      ol[u] = Pk16<T>::add(Pk16<T>::mul(l[u], c0[u]), Pk16<T>::mul(pl, s0[u]));
+      oh[u] = Pk16<T>::add(Pk16<T>::mul(hh[u], c1[u]), Pk16<T>::mul(ph, s1[u]));
+    }
+    lo = make_uint4(ol[0], ol[1], ol[2], ol[3]);
+    hi = make_uint4(oh[0], oh[1], oh[2], oh[3]);
   }
-  out[((int64_t)bh * N + n) * D + d] = from_f32<T>(val);
-  }
+  T* dst = out + ((int64_t)bh * N + n) * D;
+  *reinterpret_cast<uint4*>(dst + d0) = lo;
+  *reinterpret_cast<uint4*>(dst + HALF + d0) = hi;
 }
 
 struct ScoreSmem {
