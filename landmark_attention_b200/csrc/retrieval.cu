@@ -241,6 +241,111 @@ __global__ void __launch_bounds__(128) topk_sorted_kernel(const float* __restric
   select_topk_sorted(vals, n, k, ring_start, vec4, idx + row * k);
 }
 
+// Rows of at most 1024 scores (whole float4 groups, 16-byte aligned): the row stays in registers, 32 values per lane.
+// A lower bound T of the k-th largest score comes from the lanes' maxima (the k largest lane maxima are k different
+// scores, so the k-th of them cannot exceed the k-th largest score); every score >= T becomes a candidate in shared
+// memory -- a handful -- and the k rounds of arg-max (value, then lower index: the same order as select_topk_sorted)
+// run over the candidates only.  Rows with too many candidates (long runs of equal scores) take the general selection.
+constexpr int kTopkRegCand = 64;
+
+__global__ void __launch_bounds__(128, 8) topk_sorted_rows_kernel(const float* __restrict__ scores,
+                                                               int32_t* __restrict__ idx, int64_t rows,
+                                                               int64_t inner_count, int64_t outer_stride,
+                                                               int64_t inner_stride, int n, int k, int ring_start) {
+  extern __shared__ __align__(16) float tk_smem[];          // per warp: n floats (general selection) + candidates
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row = (int64_t)blockIdx.x * 4 + warp;
+  if (row >= rows) return;
+  float* vals = tk_smem + (size_t)warp * (n + 2 * kTopkRegCand);
+  float* cand_v = vals + n;
+  int* cand_i = reinterpret_cast<int*>(cand_v + kTopkRegCand);
+  const int64_t outer = row / inner_count, inner = row - outer * inner_count;
+  const float4* src4 = reinterpret_cast<const float4*>(scores + outer * outer_stride + inner * inner_stride);
+  const int n4 = n >> 2;
+  float v[32];
+#pragma unroll
+  for (int m = 0; m < 8; ++m) {
+    const int j = lane + 32 * m;
+    float4 f = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    if (j < n4) f = src4[j];
+    v[4 * m] = (f.x != f.x) ? -INFINITY : f.x;              // NaN scores rank lowest
+    v[4 * m + 1] = (f.y != f.y) ? -INFINITY : f.y;
+    v[4 * m + 2] = (f.z != f.z) ? -INFINITY : f.z;
+    v[4 * m + 3] = (f.w != f.w) ? -INFINITY : f.w;
+  }
+  float cur = v[0];
+#pragma unroll
+  for (int e = 1; e < 32; ++e) cur = fmaxf(cur, v[e]);
+  float T = -INFINITY;
+  for (int it = 0; it < k; ++it) {                          // k-th largest of the 32 lane maxima
+    T = warp_max(cur);
+    const unsigned holders = __ballot_sync(0xffffffffu, cur == T);
+    if (lane == __ffs(holders) - 1) cur = -INFINITY;
+  }
+  int cnt = 0;
+#pragma unroll
+  for (int e = 0; e < 32; ++e) cnt += (v[e] >= T && (lane + 32 * (e >> 2)) < n4) ? 1 : 0;
+  int inc = cnt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int u = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += u;
+  }
+  const int total = __shfl_sync(0xffffffffu, inc, 31);
+  if (total > kTopkRegCand) {                               // uniform: the general selection on the staged row
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      const int j = lane + 32 * m;
+      if (j < n4) reinterpret_cast<float4*>(vals)[j] = make_float4(v[4 * m], v[4 * m + 1], v[4 * m + 2], v[4 * m + 3]);
+    }
+    __syncwarp();
+    select_topk_sorted(vals, n, k, ring_start, true, idx + row * k);
+    return;
+  }
+  int off = inc - cnt;
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    const int j = lane + 32 * (e >> 2);
+    if (v[e] >= T && j < n4) {
+      cand_v[off] = v[e];
+      cand_i[off] = 4 * j + (e & 3);
+      ++off;
+    }
+  }
+  __syncwarp();
+  // two candidates per lane at most; k rounds of arg-max, ties to the lower index
+  float c0 = lane < total ? cand_v[lane] : -INFINITY, c1 = lane + 32 < total ? cand_v[lane + 32] : -INFINITY;
+  int i0 = lane < total ? cand_i[lane] : 0x7fffffff, i1 = lane + 32 < total ? cand_i[lane + 32] : 0x7fffffff;
+  int mine = -1;
+  for (int it = 0; it < k; ++it) {
+    float best = c0;
+    int bi = i0;
+    if (i1 != 0x7fffffff && (i0 == 0x7fffffff || c1 > best || (c1 == best && i1 < bi))) {
+      best = c1;
+      bi = i1;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (lane == it) mine = bi;
+    if (i0 == bi) i0 = 0x7fffffff;                          // taken
+    if (i1 == bi) i1 = 0x7fffffff;
+  }
+  int age = (lane < k) ? logical_age(mine, ring_start, n) : 0x7fffffff;
+  int rank = 0;
+  for (int u = 0; u < k; ++u) {
+    const int a = __shfl_sync(0xffffffffu, age, u);
+    rank += (a < age) ? 1 : 0;
+  }
+  if (lane < k) idx[row * k + rank] = mine;
+}
+
 // The aggregated selection modes (maximum over `reduce` score rows first): one CTA of 1024 threads per output row.
 // Few rows exist in these modes (batch * heads, or batch * tokens), so each CTA must pull its share of the scores at
 // several hundred GB/s on its own: 16-byte loads, the reduce range split over `parts` thread groups with four
@@ -820,6 +925,14 @@ extern "C" int lmk_topk_sorted(const float* scores, int32_t* idx_out, int64_t ou
     topk_reduce_sorted_kernel<<<(unsigned)rows, 1024, rsmem, (cudaStream_t)stream>>>(
         scores, idx_out, inner_count, outer_stride, inner_stride, reduce, reduce_stride, n, k, ring_start, vec4 ? 1 : 0,
         parts);
+    LMK_CUDA(cudaGetLastError());
+    return LMK_OK;
+  }
+  if (n <= 1024 && (n & 3) == 0 && k <= 32 &&
+      (((uintptr_t)scores | (uintptr_t)(outer_stride * 4) | (uintptr_t)(inner_stride * 4)) & 15) == 0) {
+    const size_t rsm = sizeof(float) * 4 * ((size_t)n + 2 * kTopkRegCand);
+    topk_sorted_rows_kernel<<<(unsigned)((rows + 3) / 4), 128, rsm, (cudaStream_t)stream>>>(
+        scores, idx_out, rows, inner_count, outer_stride, inner_stride, n, k, ring_start);
     LMK_CUDA(cudaGetLastError());
     return LMK_OK;
   }

@@ -471,3 +471,25 @@ def test_rotary_apply_equals_the_tensor_formulation(dtype, interleaved):
     tol = 1e-5 if dtype == torch.float32 else 3e-2
     assert (g_dq.float() - e_dq.float()).abs().max().item() < tol
     assert (g_dk.float() - e_dk.float()).abs().max().item() < tol
+
+
+@pytest.mark.parametrize("n,k", [(1024, 4), (1000, 7), (256, 32), (64, 1), (1024, 16)])
+def test_topk_register_rows_ties_runs_and_ring(n, k):
+    # rows of at most 1024 scores take the register-resident selection (threshold from the lanes' maxima, a few
+    # candidates); runs of equal scores overflow the candidate buffer and must fall back to the general selection with
+    # the same result; bf16-rounded scores (many exact ties), -inf / NaN tails and a ring start are covered
+    g = torch.Generator(device=DEV).manual_seed(n * 31 + k)
+    s = torch.randn(3, 2, 9, n, device=DEV, generator=g)
+    s[0] = s[0].to(torch.bfloat16).float() * 0.25                # coarse values: ties everywhere
+    s[1, 0, 0] = 0.5                                             # all equal: lowest indices win
+    s[1, 0, 1, : n // 2] = 3.0                                   # a run longer than the candidate buffer
+    s[1, 0, 2, 5:] = float("-inf")
+    s[1, 0, 3, 3:] = float("nan")
+    exp = torch.where(s != s, torch.full_like(s, float("-inf")), s)
+    # reference order: value descending, index ascending (a stable sort on the negated values)
+    order = torch.sort(-exp, dim=-1, stable=True).indices[..., :k]
+    for ring in (0, n // 3):
+        got = P.topk_sorted(s, k, ring_start=ring).long()
+        logical = torch.where(order < ring, order + n - ring, order - ring).sort(dim=-1).values
+        want = torch.where(logical >= n - ring, logical - (n - ring), logical + ring)
+        assert torch.equal(got, want), f"ring {ring}"
