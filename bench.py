@@ -563,16 +563,21 @@ def run_ours(args, world, rank, local):
     for got, exp in zip(outs_host, (ref_out, *ref_grads)):
         if not torch.equal(got, exp.detach().cpu()):
             raise SystemExit("host pipeline and device-resident call disagree")
-    e2e_times = {}
-    for name, wait in (("one_step_at_a_time", True), ("pipelined", False)):
-        e2e_loop(2, wait)
-        barrier(world); torch.cuda.synchronize()
-        a, b_ = ev(), ev()
-        a.record()
-        e2e_loop(args.steps, wait)
-        b_.record()
-        torch.cuda.synchronize(); barrier(world)
-        e2e_times[name] = max_over_ranks(a.elapsed_time(b_) / args.steps, world, dev)
+    e2e_times, e2e_repeats = {}, []
+    for name, wait, repeats in (("one_step_at_a_time", True, 1), ("pipelined", False, 3)):
+        runs = []
+        for _ in range(repeats):       # the host link is shared with other tenants: three runs of K steps, the median counts
+            e2e_loop(2, wait)
+            barrier(world); torch.cuda.synchronize()
+            a, b_ = ev(), ev()
+            a.record()
+            e2e_loop(args.steps, wait)
+            b_.record()
+            torch.cuda.synchronize(); barrier(world)
+            runs.append(max_over_ranks(a.elapsed_time(b_) / args.steps, world, dev))
+        e2e_times[name] = statistics.median(runs)
+        if not wait:
+            e2e_repeats = runs
     for got, exp in zip(outs_host, (ref_out, *ref_grads)):
         if not torch.equal(got, exp.detach().cpu()):
             raise SystemExit("pipelined host steps and device-resident call disagree")
@@ -658,6 +663,7 @@ def run_ours(args, world, rank, local):
                 "how": "HostAttentionPipeline.run(wait=False) per step: pinned q, k, v, dO in, o, dq, dk, dv out, two "
                        "head chunks, consecutive steps overlapped (copies of both directions and the kernels)",
                 "ms_per_step_one_step_at_a_time": e2e_times["one_step_at_a_time"],
+                "ms_per_step_runs": e2e_repeats,       # three runs of `steps` steps each; ms_per_step is their median
                 "host_link_gbs_per_direction_both_busy": link_gbs,
                 "host_link_floor_ms": 4 * tensor_bytes / (link_gbs * 1e9) * 1e3},
         "gpu_launches": args.steps * 3,      # forward, dQ (+ delta), dK/dV
