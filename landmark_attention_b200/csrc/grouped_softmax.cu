@@ -720,12 +720,24 @@ __global__ void __launch_bounds__(kGsWarps * 32) grouped_softmax_rows_kernel(GsP
     const bool ovec = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     // pass 3: c_g = sum_j inner_j * grad_j per group, total = sum_j P_j * grad_j over the row
     float total = 0.f;
-    for (int k = 0; k < n_chunks; ++k) {
-      const Meta mt = meta[k * 32];
-      if (mt.dead()) continue;
-      float x[8], g[8];
+    // the gradients of the next live chunk are requested before the current one is worked on
+    auto load_grad = [&](int k, float (&g)[8]) {
       const int j = k * kFastChunk + lane * 8;
       load8f(gr + j, gvec, min(max(p.Lk - j, 0), 8), g);
+    };
+    Meta mnext = meta[0];
+    float gn[8];
+    if (!mnext.dead()) load_grad(0, gn);
+    for (int k = 0; k < n_chunks; ++k) {
+      const Meta mt = mnext;
+      float x[8], g[8];
+#pragma unroll
+      for (int v = 0; v < 8; ++v) g[v] = gn[v];
+      if (k + 1 < n_chunks) {
+        mnext = meta[(k + 1) * 32];
+        if (!mnext.dead()) load_grad(k + 1, gn);
+      }
+      if (mt.dead()) continue;
       row_get(xbuf + k * kFastChunk, lane, x);
       const uint32_t F = mt.flags;
       const int c0 = mt.c0();
@@ -754,18 +766,25 @@ __global__ void __launch_bounds__(kGsWarps * 32) grouped_softmax_rows_kernel(GsP
     }
     total = warp_sum(total);
     // pass 4: gradients
+    mnext = meta[0];
+    if (!mnext.dead()) load_grad(0, gn);
     for (int k = 0; k < n_chunks; ++k) {
-      const Meta mt = meta[k * 32];
+      const Meta mt = mnext;
       const int j = k * kFastChunk + lane * 8;
       const int n_in = min(max(p.Lk - j, 0), 8);
       float x[8], g[8];
+#pragma unroll
+      for (int v = 0; v < 8; ++v) g[v] = gn[v];
+      if (k + 1 < n_chunks) {
+        mnext = meta[(k + 1) * 32];
+        if (!mnext.dead()) load_grad(k + 1, gn);
+      }
       if (mt.dead()) {
 #pragma unroll
         for (int v = 0; v < 8; ++v) x[v] = 0.f;
         store8f(out + j, ovec, n_in, x);
         continue;
       }
-      load8f(gr + j, gvec, n_in, g);
       row_get(xbuf + k * kFastChunk, lane, x);
       const uint32_t F = mt.flags;
       int c = mt.c0();
