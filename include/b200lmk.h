@@ -218,7 +218,10 @@ int lmk_grouped_softmax_causal_bwd(const void* x, const int64_t x_strides[3], co
 enum {
   LMK_ROTARY_NONE = 0,
   LMK_ROTARY_HALF = 1,       /* pairs (d, d+D/2): llama/llama_mem.py:127-149 */
-  LMK_ROTARY_INTERLEAVED = 2 /* pairs (2d, 2d+1): lm_benchmark/models/positional_encoders/rotary_utils.py:17-31 */
+  LMK_ROTARY_INTERLEAVED = 2, /* pairs (2d, 2d+1): lm_benchmark/models/positional_encoders/rotary_utils.py:17-31 */
+  LMK_ROTARY_HALF_SYM = 3     /* LMK_ROTARY_HALF with the caller's promise that cos[p][d] == cos[p][d + D/2] and the same
+                                 for sin (tables built as cat(freqs, freqs), llama/llama_mem.py:104-108): the second
+                                 halves are not read.  Accepted by lmk_selected_attend only. */
 };
 
 /*

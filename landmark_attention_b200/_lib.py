@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("B200LMK_LIB") or os.path.join(os.path.dirname(os.path
 LMK_F32, LMK_F16, LMK_BF16 = 0, 1, 2
 LMK_OK, LMK_ERR_INVALID, LMK_ERR_UNSUPPORTED, LMK_ERR_CUDA, LMK_ERR_WORKSPACE, LMK_ERR_DEVICE = 0, -1, -2, -3, -4, -5
 PATH_AUTO, PATH_GENERAL, PATH_TCGEN05 = 0, 1, 2
-ROTARY_NONE, ROTARY_HALF, ROTARY_INTERLEAVED = 0, 1, 2
+ROTARY_NONE, ROTARY_HALF, ROTARY_INTERLEAVED, ROTARY_HALF_SYM = 0, 1, 2, 3
 
 _DTYPES = {torch.float32: LMK_F32, torch.float16: LMK_F16, torch.bfloat16: LMK_BF16}
 

@@ -3,6 +3,7 @@
 // Reference call sites: LlamaAttention.forward cache branch (llama/llama_mem.py:357-398, 408-410) and
 // MemLMCacheStorage.retrieve_for_query (lm_benchmark/models/caches/mem_cache.py:51-98).  Both rotate cached keys at
 // "slot" positions: the newest top_k blocks occupy slots 1..top_k, every older block shares slot 0.
+#include <type_traits>
 #include "common.cuh"
 #include "scores_sm100.h"
 
@@ -744,6 +745,8 @@ __global__ void __launch_bounds__(128, 8) selected_attend_kernel(const T* __rest
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane % LP, rsub = lane / LP, d0 = sub * VEC;
   const int blk = kd.block, N = kd.n_blocks, top_k = kd.top_k;
+  const bool sym = rotary == LMK_ROTARY_HALF_SYM;      // equal table halves: the second ones are not read
+  if (sym) rotary = LMK_ROTARY_HALF;
   float* lg = att_smem;                         // [top_k][blk] logits, then probabilities inside the block
   float* osel = lg + ((top_k * blk + 3) & ~3);  // [top_k][D]
   float* xsel = osel + top_k * D;               // [top_k] landmark logits, log2 domain
@@ -765,6 +768,91 @@ __global__ void __launch_bounds__(128, 8) selected_attend_kernel(const T* __rest
     const int pos0 = kd.pos_base + (i + (recent ? 1 : 0)) * blk;
     const T* ksrc = kbase + (int64_t)sel * kd.stride_block + d0;
     float* lrow = lg + i * blk;
+    if constexpr (sizeof(T) == 2 && LPR == 16) {
+      // D = 128 in a 16-bit type: the logits of 16 rows at a time as mma.sync m16n8k16 tiles.  Thread (g, t) of the
+      // warp loads the 16-byte vectors [32 c + 8 t, +8) of rows g and g + 8 (c = 0..3), rotates them on packed pairs
+      // as above, and feeds their registers straight to the A fragments: a dot product does not depend on the order
+      // of the features, so "k index 2t, 2t+1, 2t+8, 2t+9" may stand for any four features as long as the query's B
+      // fragment (column 0 only) holds the same ones.  The sums over the features happen inside the instruction.
+      const int g8 = lane >> 2, t4 = lane & 3;
+      const T* qrow = q + ((int64_t)bh * Tq + t) * D;
+      const T* kblk = kbase + (int64_t)sel * kd.stride_block;
+      for (int m = 0; m < blk; m += 16) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const int ra = m + g8, rb = ra + 8;
+        const T* ka = kblk + (int64_t)min(ra, blk - 1) * kd.stride_row + 8 * t4;
+        const T* kb2 = kblk + (int64_t)min(rb, blk - 1) * kd.stride_row + 8 * t4;
+        const int pa = max(0, min(pos0 + min(ra, blk - 1), n_pos - 1)), pb = max(0, min(pos0 + min(rb, blk - 1), n_pos - 1));
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {           // chunk cc of the low half with its partner cc + 2 of the high half
+          uint32_t xa[2][4], xb[2][4];             // [low / high][register]
+          ld16(ka + 32 * cc, xa[0]);
+          ld16(ka + 32 * cc + HALF, xa[1]);
+          ld16(kb2 + 32 * cc, xb[0]);
+          ld16(kb2 + 32 * cc + HALF, xb[1]);
+          if (rotary != LMK_ROTARY_NONE) {
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+              uint32_t (&x)[2][4] = rr == 0 ? xa : xb;
+              const int64_t po = (int64_t)(rr == 0 ? pa : pb) * D + 32 * cc + 8 * t4;
+              uint32_t cl[4], ch[4], sl[4], sh[4];
+              ld16(cos_t + po, cl);
+              ld16(sin_t + po, sl);
+              if (sym) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  ch[u] = cl[u];
+                  sh[u] = sl[u];
+                }
+              } else {
+                ld16(cos_t + po + HALF, ch);
+                ld16(sin_t + po + HALF, sh);
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                uint32_t pl, ph;
+                if (rotary == LMK_ROTARY_HALF) {
+                  pl = x[1][u] ^ 0x80008000u;
+                  ph = x[0][u];
+                } else {
+                  pl = __byte_perm(x[0][u], x[0][u], 0x1032) ^ 0x00008000u;
+                  ph = __byte_perm(x[1][u], x[1][u], 0x1032) ^ 0x00008000u;
+                }
+                const uint32_t lo = Packed<T>::add(Packed<T>::mul(x[0][u], cl[u]), Packed<T>::mul(pl, sl[u]));
+                const uint32_t hi = Packed<T>::add(Packed<T>::mul(x[1][u], ch[u]), Packed<T>::mul(ph, sh[u]));
+                x[0][u] = lo;
+                x[1][u] = hi;
+              }
+            }
+          }
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {          // low chunk cc, then high chunk cc + 2
+            uint32_t qf[4] = {0u, 0u, 0u, 0u};      // the query's features of this chunk: column 0 of B only
+            if (g8 == 0) ld16(qrow + 32 * cc + hh * HALF + 8 * t4, qf);
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                             "{%0,%1,%2,%3};"
+                             : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                             : "r"(xa[hh][2 * h2]), "r"(xb[hh][2 * h2]), "r"(xa[hh][2 * h2 + 1]), "r"(xb[hh][2 * h2 + 1]),
+                               "r"(qf[2 * h2]), "r"(qf[2 * h2 + 1]));
+              } else {
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                             "{%0,%1,%2,%3};"
+                             : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                             : "r"(xa[hh][2 * h2]), "r"(xb[hh][2 * h2]), "r"(xa[hh][2 * h2 + 1]), "r"(xb[hh][2 * h2 + 1]),
+                               "r"(qf[2 * h2]), "r"(qf[2 * h2 + 1]));
+              }
+            }
+          }
+        }
+        if (t4 == 0) {                              // column 0 of the result: rows g and g + 8
+          if (ra < blk) lrow[ra] = acc[0] * scale * kL2e;
+          if (rb < blk) lrow[rb] = acc[2] * scale * kL2e;
+        }
+      }
+    } else
     for (int r0 = 0; r0 < blk; r0 += RPS) {
       const int r = r0 + rsub;
       float acc = 0.f;
@@ -1103,7 +1191,8 @@ extern "C" int lmk_selected_attend(const void* q, const void* k_cache, const lmk
                       d->stride_b % vec == 0, "selected_attend: cache strides must be multiples of %d elements", vec);
   LMK_CHECK_ARG(rotary == LMK_ROTARY_NONE || (cos_table && sin_table && n_pos >= 1),
                 "selected_attend: rotary needs cos/sin tables");
-  LMK_CHECK_ARG(rotary == LMK_ROTARY_NONE || rotary == LMK_ROTARY_HALF || rotary == LMK_ROTARY_INTERLEAVED,
+  LMK_CHECK_ARG(rotary == LMK_ROTARY_NONE || rotary == LMK_ROTARY_HALF || rotary == LMK_ROTARY_INTERLEAVED ||
+                    rotary == LMK_ROTARY_HALF_SYM,
                 "selected_attend: unknown rotary mode %d", rotary);
   LMK_CHECK_ARG(kdesc->top_k >= 1, "selected_attend: top_k must be at least 1");
   if (B == 0 || T == 0) return LMK_OK;

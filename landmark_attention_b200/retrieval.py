@@ -172,6 +172,28 @@ def selected_pv(probs, v_cache, vdesc, idx, col0=0, dim=None):
     return out
 
 
+_SYMMETRIC = {}       # (id(cos), id(sin)) -> (weakref to cos, weakref to sin, versions, verdict)
+
+
+def _halves_equal(cos, sin, check=True):
+    """Whether cos[p, d] == cos[p, d + D/2] and the same for sin (tables built as cat(freqs, freqs), as LLaMA's rotary
+    embedding does).  One device comparison per pair of table tensors, remembered while those tensor objects live and
+    are not written to; check=False only looks the verdict up (None if unknown)."""
+    import weakref
+    key = (id(cos), id(sin))
+    hit = _SYMMETRIC.get(key)
+    if hit is not None and hit[0]() is cos and hit[1]() is sin and hit[2] == (cos._version, sin._version):
+        return hit[3]
+    if not check:
+        return None
+    h = cos.shape[1] // 2
+    verdict = bool(torch.equal(cos[:, :h], cos[:, h:]) and torch.equal(sin[:, :h], sin[:, h:]))
+    if len(_SYMMETRIC) > 64:
+        _SYMMETRIC.clear()
+    _SYMMETRIC[key] = (weakref.ref(cos), weakref.ref(sin), (cos._version, sin._version), verdict)
+    return verdict
+
+
 def selected_attend(q, k_cache, v_cache, kdesc, vdesc, idx, cos=None, sin=None, rotary=L.ROTARY_NONE, sm_scale=None,
                     o_local=None, R_local=None):
     """Attention of every query over ITS selected blocks in one kernel, merged with the attention over the local keys.
@@ -192,6 +214,8 @@ def selected_attend(q, k_cache, v_cache, kdesc, vdesc, idx, cos=None, sin=None, 
         assert o_local.shape == (B, H, local_rows, D) and R_local.shape == (B * H, local_rows)
     out = torch.empty((B, H, T, D), device=q.device, dtype=q.dtype)
     n_pos = 0 if cos is None else cos.shape[0]
+    if rotary == L.ROTARY_HALF and _halves_equal(cos, sin, check=not torch.cuda.is_current_stream_capturing()):
+        rotary = L.ROTARY_HALF_SYM              # the kernel then reads half of the table bytes
     rc = L.lib().lmk_selected_attend(L.ptr(q), L.ptr(k_cache), ctypes.byref(kdesc), L.ptr(v_cache), ctypes.byref(vdesc),
                                      L.ptr(idx), L.ptr(cos), L.ptr(sin), n_pos, rotary, L.ptr(o_local), L.ptr(R_local),
                                      local_rows, L.ptr(out), B, H, T, D, float(sm_scale), L.dtype_code(q),

@@ -493,3 +493,25 @@ def test_topk_register_rows_ties_runs_and_ring(n, k):
         logical = torch.where(order < ring, order + n - ring, order - ring).sort(dim=-1).values
         want = torch.where(logical >= n - ring, logical - (n - ring), logical + ring)
         assert torch.equal(got, want), f"ring {ring}"
+
+
+def test_selected_attend_with_equal_table_halves_reads_half_of_them():
+    # tables built as cat(freqs, freqs) take LMK_ROTARY_HALF_SYM (second halves not read): same output bit for bit as
+    # the general rotate-half mode; tables without that property stay on the general mode
+    from landmark_attention_b200 import retrieval as R
+    torch.manual_seed(5)
+    B, H, T, D, blk, nblk, top_k = 1, 2, 130, 128, 32, 40, 4
+    C = nblk * blk
+    q = (torch.randn(B, H, T, D) * 0.5).to(torch.bfloat16).to(DEV)
+    pk, pv = [torch.randn(B, H, C, D).to(torch.bfloat16).to(DEV) for _ in range(2)]
+    cos, sin = P.rotary_tables_half(C + T + 1, D, torch.bfloat16, DEV)
+    st = pk.stride()
+    kdesc = L.CacheDesc(st[0], st[1], st[2] * blk, st[2], nblk, 0, blk, top_k, C - (top_k + 1) * blk)
+    sel = P.topk_sorted(P.landmark_scores(q, pk, kdesc, cos, sin, L.ROTARY_HALF), top_k)
+    assert R._halves_equal(cos, sin)
+    got = P.selected_attend(q, pk, pv, kdesc, kdesc, sel, cos, sin, L.ROTARY_HALF)          # upgraded to the SYM mode
+    cos2, sin2 = cos.clone(), sin.clone()
+    cos2[0, D // 2:] += 0.5                                                                   # position 0 is never used
+    assert not R._halves_equal(cos2, sin2)
+    ref = P.selected_attend(q, pk, pv, kdesc, kdesc, sel, cos2, sin2, L.ROTARY_HALF)        # general mode
+    assert torch.equal(got, ref)
