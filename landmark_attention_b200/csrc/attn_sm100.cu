@@ -379,8 +379,9 @@ constexpr int kFwd2Stages = 5;
 constexpr int kFwd2Threads = 352;
 enum { kErrFwd2Producer = 111, kErrFwd2Mma = 112, kErrFwd2Softmax = 113, kErrFwd2Epilogue = 114 };
 
-// one in this many pairs of exponentials uses ex2_poly2 (measured: 4 beats 2, 3 and "never" at L = 2048 and L = 8192)
-constexpr int kFwdPolyEvery = 4;
+// one in this many pairs of exponentials uses ex2_poly2 (measured at L = 8192: 2 -> 544 us, 4 -> 523, 8 -> 515, 64 -> 508;
+// no difference at L = 2048: the special-function pipe is not what the forward kernel waits for)
+constexpr int kFwdPolyEvery = 64;
 
 struct Fwd2Smem {
   uint64_t q_full;
